@@ -1,0 +1,77 @@
+/* C ABI of libstrata_b200.so — hand-written sm_100a kernels for the Strata transformer-block
+ * hot path and the cubed-sphere tile halo exchange.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name starts with "h_".
+ *   - bf16 tensors are passed as void*; leading dimensions ("ld*") and strides are in
+ *     ELEMENTS, not bytes.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Calls are asynchronous on `stream`. The return value reports argument / launch
+ *     errors only: 0 = ok, negative = error (see strata_error_string). Failures detected on
+ *     the device (a bounded wait that ran out) are recorded in a device status word read
+ *     back with strata_device_status().
+ *   - Unless stated otherwise no entry point allocates device memory; scratch is passed in.
+ *
+ * The reference implements this path in Python on top of third-party kernels; each entry
+ * point cites the reference call it stands in for (path inside the reference project).
+ */
+#ifndef STRATA_B200_H
+#define STRATA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STRATA_OK 0
+#define STRATA_ERR_ARG (-1)         /* invalid shape / pointer / alignment */
+#define STRATA_ERR_UNSUPPORTED (-2) /* configuration this build has no kernel for */
+#define STRATA_ERR_NO_DEVICE (-3)   /* no sm_100 device current */
+#define STRATA_ERR_TENSORMAP (-20)  /* cuTensorMapEncodeTiled refused the operand layout */
+/* <= -1000: -(cudaError_t) - 1000 from a launch or runtime call */
+
+/* Epilogue selector of strata_linear_bf16. */
+#define STRATA_EPI_BIAS 0     /* y = x W^T + b */
+#define STRATA_EPI_GELU 1     /* y = gelu_tanh(x W^T + b) */
+#define STRATA_EPI_RESIDUAL 2 /* y = x W^T + b + aux */
+#define STRATA_EPI_GATE 4     /* y = aux * sigmoid(x W^T + b) */
+
+int strata_abi_version(void);
+const char* strata_error_string(int code);
+
+/* Reads (and, if reset != 0, clears) the device status word of the current device.
+ * Synchronises the device. *h_status: 0 = ok, 101..105 = a bounded wait timed out. */
+int strata_device_status(int* h_status, int reset);
+
+/* Non-affine LayerNorm over channels: y[m,:] = (x[m,:] - mean) * rsqrt(var + eps).
+ * Replaces the block's norm1/norm2 (physicsnemo StrataTransformer3DBlock; the parameter
+ * manifests tests/regression_data/ *.param_order.txt list no norm parameters). */
+int strata_layernorm_bf16(const void* x, int64_t ldx, void* y, int64_t ldy, int M, int C,
+                          float eps, void* stream);
+
+/* y[M,N] = epilogue(x[M,K] W[N,K]^T + bias). W is an nn.Linear weight ([out,in]); bias is
+ * fp32 [N] or NULL; aux is the bf16 residual / gated operand or NULL.
+ * Replaces nn.Linear calls of the block: attn.proj, attn.gate_proj, mlp.layers.0 (+ the
+ * tanh GELU of screamcast/strata_wrappers.py:76-100), mlp.layers.2. */
+int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                       void* y, int64_t ldy, int M, int N, int K, int epilogue, const void* aux,
+                       int64_t ldaux, void* stream);
+
+/* qkv[M,3C] = x[M,C] Wqkv[3C,C]^T + b with, fused in the epilogue, optional per-head RMS
+ * norm of q and k and the 2-D rotary embedding of q and k by the token's (cos,sin) row.
+ * rope_cos/rope_sin: fp32 [n_tiles, hw, head_dim/2]; row m of x is token
+ * (tile = m / tokens_per_tile, horizontal cell = m % hw). Column layout of qkv:
+ * [q heads | k heads | v heads], each head head_dim wide (nn.Linear(C,3C) reshaped
+ * [.., 3, heads, head_dim]). Pass rope_cos = NULL for no rotation.
+ * Replaces attn.qkv + qk norm + stereographic/axial RoPE + head split of the block
+ * (tables: screamcast/strata_wrappers.py:636-642). */
+int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                         void* qkv, int64_t ldqkv, int M, int C, int head_dim,
+                         const float* rope_cos, const float* rope_sin, int tokens_per_tile, int hw,
+                         int qk_norm, float qk_eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRATA_B200_H */

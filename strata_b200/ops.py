@@ -1,0 +1,124 @@
+"""Tensor-level wrappers over the C ABI (device pointers + current CUDA stream).
+
+Each function checks dtypes/devices on the Python side, passes raw pointers to
+libstrata_b200.so and raises on any error code. Nothing here computes on the host and
+nothing falls back to PyTorch kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+EPI_BIAS = 0
+EPI_GELU = 1
+EPI_RESIDUAL = 2
+EPI_GATE = 4
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda_bf16(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise _lib.StrataLibraryError(
+            f"{name} must be a CUDA tensor: strata_b200 has no CPU path")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+
+
+def _as_rows(t: torch.Tensor, name: str) -> tuple[torch.Tensor, int, int, int]:
+    """View t as [M, C] with unit inner stride; returns (tensor, M, C, ld)."""
+    if t.dim() < 2:
+        raise ValueError(f"{name} must have at least 2 dims")
+    c = t.shape[-1]
+    t2 = t.reshape(-1, c)
+    if t2.stride(-1) != 1:
+        t2 = t2.contiguous()
+    ld = t2.stride(0) if t2.shape[0] > 1 else max(t2.stride(0), c)
+    return t2, t2.shape[0], c, ld
+
+
+def _f32_or_none(t, name):
+    if t is None:
+        return None
+    if t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32")
+    return t.contiguous()
+
+
+def layernorm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Non-affine LayerNorm over the last dim (bf16 in, bf16 out)."""
+    _require_cuda_bf16(x, "x")
+    x2, M, C, ld = _as_rows(x, "x")
+    y = torch.empty((M, C), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_layernorm_bf16(x2.data_ptr(), ld, y.data_ptr(), C, M, C,
+                                                     float(eps), _stream_ptr(x)),
+                   "strata_layernorm_bf16")
+    return y.reshape(x.shape)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           epilogue: int = EPI_BIAS, aux: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """y = epilogue(x @ weight.T + bias); weight is [N, K] (nn.Linear layout), bias fp32."""
+    _require_cuda_bf16(x, "x")
+    _require_cuda_bf16(weight, "weight")
+    x2, M, K, ldx = _as_rows(x, "x")
+    if weight.dim() != 2 or weight.shape[1] != K:
+        raise ValueError(f"weight must be [N, {K}], got {tuple(weight.shape)}")
+    w = weight if weight.stride(1) == 1 else weight.contiguous()
+    N = w.shape[0]
+    bias = _f32_or_none(bias, "bias")
+    aux_ptr, ldaux = None, 0
+    if epilogue in (EPI_RESIDUAL, EPI_GATE):
+        if aux is None:
+            raise ValueError("this epilogue needs `aux`")
+        _require_cuda_bf16(aux, "aux")
+        a2, Ma, Na, ldaux = _as_rows(aux, "aux")
+        if (Ma, Na) != (M, N):
+            raise ValueError(f"aux must be [{M}, {N}], got [{Ma}, {Na}]")
+        aux_ptr = a2.data_ptr()
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        _require_cuda_bf16(out, "out")
+        if out.shape != (M, N) or out.stride(1) != 1:
+            raise ValueError("out must be [M, N] with unit inner stride")
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_linear_bf16(
+            x2.data_ptr(), ldx, w.data_ptr(), w.stride(0),
+            None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0), M, N, K,
+            int(epilogue), aux_ptr, ldaux, _stream_ptr(x)), "strata_linear_bf16")
+    return out if x.dim() == 2 else out.reshape(*x.shape[:-1], N)
+
+
+def qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, head_dim: int,
+             rope_cos: torch.Tensor | None, rope_sin: torch.Tensor | None, tokens_per_tile: int,
+             hw: int, qk_norm: bool = False, qk_eps: float = 1e-6) -> torch.Tensor:
+    """Fused QKV projection + optional qk RMS norm + rotary embedding; returns [M, 3C]."""
+    _require_cuda_bf16(x, "x")
+    _require_cuda_bf16(weight, "weight")
+    x2, M, C, ldx = _as_rows(x, "x")
+    if weight.shape != (3 * C, C):
+        raise ValueError(f"qkv weight must be [{3 * C}, {C}], got {tuple(weight.shape)}")
+    w = weight if weight.stride(1) == 1 else weight.contiguous()
+    bias = _f32_or_none(bias, "bias")
+    rope_cos = _f32_or_none(rope_cos, "rope_cos")
+    rope_sin = _f32_or_none(rope_sin, "rope_sin")
+    if rope_cos is not None:
+        n_tiles = M // max(tokens_per_tile, 1)
+        want = (n_tiles, hw, head_dim // 2)
+        if tuple(rope_cos.shape) != want or tuple(rope_sin.shape) != want:
+            raise ValueError(f"rope tables must be {want}, got {tuple(rope_cos.shape)}")
+    out = torch.empty((M, 3 * C), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_qkv_rope_bf16(
+            x2.data_ptr(), ldx, w.data_ptr(), w.stride(0),
+            None if bias is None else bias.data_ptr(), out.data_ptr(), 3 * C, M, C, head_dim,
+            None if rope_cos is None else rope_cos.data_ptr(),
+            None if rope_sin is None else rope_sin.data_ptr(), int(tokens_per_tile), int(hw),
+            1 if qk_norm else 0, float(qk_eps), _stream_ptr(x)), "strata_qkv_rope_bf16")
+    return out
