@@ -71,6 +71,19 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
                          const float* rope_cos, const float* rope_sin, int tokens_per_tile, int hw,
                          int qk_norm, float qk_eps, void* stream);
 
+/* 3-D neighbourhood attention forward (non-causal, dilation 1, head_dim 64).
+ * q, k, v, out are token-major: element (b,d,h,w,head,c) lives at
+ * base + token*ld + head*head_dim + c with token = ((b*D + d)*H + h)*W + w, so q/k/v may be
+ * column slices of one packed [M,3C] qkv matrix (ld = 3C) and out a [M,C] matrix.
+ * Window of query i along an axis of length L: [s, s+k) with s = clamp(i - k/2, 0, L-k).
+ * scale <= 0 selects head_dim^-0.5. Requires kd<=D, kh<=H, kw<=W, odd kw <= 15, kh <= 15.
+ * Replaces NATTEN na3d as called by the physicsnemo Strata block (backend selector
+ * screamcast/config.py:99, passed at screamcast/strata_wrappers.py:331). */
+int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                         int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W,
+                         int heads, int head_dim, int kd, int kh, int kw, float scale,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

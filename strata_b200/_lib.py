@@ -29,6 +29,9 @@ _SIGNATURES = {
     "strata_qkv_rope_bf16": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
                                      c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_int, c_float, c_void_p]),
+    "strata_na3d_fwd_bf16": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                     c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_int, c_float, c_void_p]),
 }
 
 

@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "gemm_tcgen05.cuh"
 #include "layernorm.cuh"
+#include "na3d.cuh"
 
 using namespace strata;
 
@@ -145,6 +146,31 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
   if (!rope_cos && !qk_norm) return launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
   if (!rope_cos) return STRATA_ERR_UNSUPPORTED;  // qk norm without rotation: not on the path
   return launch_gemm<EPI_QKV_ROPE>(A, ldx, W, ldw, p, sms, as_stream(stream));
+}
+
+int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                         int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W,
+                         int heads, int head_dim, int kd, int kh, int kw, float scale,
+                         void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!q || !k || !v || !out || B < 0 || D <= 0 || H <= 0 || W <= 0 || heads <= 0)
+    return STRATA_ERR_ARG;
+  if (head_dim != 64) return STRATA_ERR_UNSUPPORTED;
+  const int64_t C = static_cast<int64_t>(heads) * head_dim;
+  if (ldq < C || ldk < C || ldv < C || ldo < C) return STRATA_ERR_ARG;
+  if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8) return STRATA_ERR_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return STRATA_ERR_ARG;
+  if (kd < 1 || kh < 1 || kw < 1 || kd > D || kh > H || kw > W) return STRATA_ERR_ARG;
+  if (B == 0) return STRATA_OK;
+  const float sc = scale > 0.f ? scale : 1.0f / sqrtf(static_cast<float>(head_dim));
+  int r = launch_na3d(static_cast<const __nv_bfloat16*>(q), ldq,
+                      static_cast<const __nv_bfloat16*>(k), ldk,
+                      static_cast<const __nv_bfloat16*>(v), ldv, static_cast<__nv_bfloat16*>(out),
+                      ldo, B, D, H, W, heads, kd, kh, kw, sc, as_stream(stream));
+  if (r == -1) return STRATA_ERR_ARG;
+  if (r == -2) return STRATA_ERR_UNSUPPORTED;
+  return r;
 }
 
 }  // extern "C"

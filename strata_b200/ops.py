@@ -122,3 +122,38 @@ def qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, h
             None if rope_sin is None else rope_sin.data_ptr(), int(tokens_per_tile), int(hw),
             1 if qk_norm else 0, float(qk_eps), _stream_ptr(x)), "strata_qkv_rope_bf16")
     return out
+
+
+def _token_major(t: torch.Tensor, name: str) -> int:
+    """Check a [B,D,H,W,heads,hd] view is token-major; return its token stride."""
+    if t.dim() != 6:
+        raise ValueError(f"{name} must be [B, D, H, W, heads, head_dim]")
+    B, D, H, W, nh, hd = t.shape
+    sb, sd, sh, sw, sn, sc = t.stride()
+    ld = sw
+    ok = sc == 1 and sn == hd and sh == W * ld and sd == H * W * ld and (B == 1 or sb == D * H * W * ld)
+    if not ok:
+        raise ValueError(f"{name} is not token-major (strides {t.stride()}); call .contiguous()")
+    return ld
+
+
+def na3d(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel, scale: float | None = None,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """3-D neighbourhood attention. q, k, v: [B, D, H, W, heads, 64] bf16 (token-major views,
+    e.g. slices of a packed qkv tensor). Returns [B, D, H, W, heads, 64]."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _require_cuda_bf16(t, n)
+    if not (q.shape == k.shape == v.shape):
+        raise ValueError("q, k, v must have the same shape")
+    B, D, H, W, nh, hd = q.shape
+    kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(x) for x in kernel)
+    ldq, ldk, ldv = _token_major(q, "q"), _token_major(k, "k"), _token_major(v, "v")
+    if out is None:
+        out = torch.empty((B, D, H, W, nh, hd), dtype=torch.bfloat16, device=q.device)
+    ldo = _token_major(out, "out")
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().strata_na3d_fwd_bf16(
+            q.data_ptr(), ldq, k.data_ptr(), ldk, v.data_ptr(), ldv, out.data_ptr(), ldo,
+            B, D, H, W, nh, hd, kd, kh, kw, float(scale) if scale else 0.0, _stream_ptr(q)),
+            "strata_na3d_fwd_bf16")
+    return out
