@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the Strata transformer-block hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[1]): one bf16 Strata backbone block forward over a batch of
+4 tiles of 16 x 64 x 64 tokens, dim 512, 8 heads x 64, 3-D neighbourhood kernel (3,9,9),
+stereographic RoPE, MLP ratio 4 tanh-GELU; N(0,1) activations, trunc-normal(0.02) weights,
+all synthetic. A "step" is one block forward over the batch. With N > 1 GPUs every rank
+runs its own batch of 4 tiles (tiles are the sharding unit; weak scaling).
+
+Prints ONE JSON line: metric "block_tokens_per_s" (whole job), the roofline of the dominant
+kernel, a CPU baseline (the fp32 oracle restatement timed on the host cores), the end-to-end
+number through the C ABI with host buffers, clocks sampled during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(workload="strata_block_fwd_bf16", tiles_per_gpu=4, token_grid=[16, 64, 64],
+                dim=512, heads=8, head_dim=64, kernel=[3, 9, 9], mlp_ratio=4, rope="stereographic",
+                gated=False, qk_norm=False, l2="inputs_exceed_l2 (2.9 GB touched per step)")
+CPU_SAMPLE = dict(tiles=2, token_grid=[8, 32, 32])   # bounded sample of the same workload
+
+
+def flops_per_token(C, kernel, ratio=4.0):
+    K = kernel[0] * kernel[1] * kernel[2]
+    return 6 * C * C + 4 * K * C + 2 * C * C + 4 * ratio * C * C
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+def cpu_block_tokens_per_s(steps: int, warmup: int, threads: int | None = None):
+    """Times the fp32 oracle block (CPU restatement of the reference block; physicsnemo and
+    NATTEN are not installable here) on a bounded sample of the workload."""
+    import torch
+    from oracle import block_oracle as bo
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    C, heads, kernel = WORKLOAD["dim"], WORKLOAD["heads"], tuple(WORKLOAD["kernel"])
+    D, H, W = CPU_SAMPLE["token_grid"]
+    n = CPU_SAMPLE["tiles"]
+    p = bo.init_block_params(C, seed=0)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(n, D * H * W, C, generator=g)
+    lat = torch.linspace(0.2, 0.7, H).view(1, H, 1).expand(n, H, W)
+    lon = torch.linspace(0.1, 0.6, W).view(1, 1, W).expand(n, H, W)
+    cos, sin = bo.stereographic_rope_tables(lat, lon, C // heads, 1, bo.default_rope_length_scale(1))
+    run = lambda: bo.block_forward(x, p, grid=(D, H, W), num_heads=heads, kernel=kernel,
+                                   rope_cos=cos, rope_sin=sin)
+    with torch.no_grad():
+        for _ in range(warmup):
+            run()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            run()
+        dt = (time.perf_counter() - t0) / steps
+    tokens = n * D * H * W
+    return tokens / dt, dt * 1e3, threads, f"{n} tile of {D}x{H}x{W} tokens, dim {C}, kernel {list(kernel)}, fp32"
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    warm = 1
+    tps, ms, threads, sample = cpu_block_tokens_per_s(steps, warm)
+    line = {
+        "impl": "reference", "metric": "block_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": WORKLOAD,
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference block (physicsnemo / NATTEN unavailable here)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [r.split(", ") for r in Path(self.tmp.name).read_text().strip().splitlines() if r]
+        os.unlink(self.tmp.name)
+        sm, reasons = [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                out["sm_max_mhz"] = float(r[2])
+            except ValueError:
+                continue
+            for nm, val in zip(names, r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(nm)
+        if sm:
+            # median over the busiest half of the samples (the sampler also sees idle time)
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from strata_b200 import ops, rope, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); "
+                         "use --impl reference for the CPU baseline")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    C, heads, kernel = WORKLOAD["dim"], WORKLOAD["heads"], tuple(WORKLOAD["kernel"])
+    D, H, W = WORKLOAD["token_grid"]
+    n_tiles = WORKLOAD["tiles_per_gpu"]
+    hidden = C * WORKLOAD["mlp_ratio"]
+    T = D * H * W
+    M = n_tiles * T
+
+    g = torch.Generator().manual_seed(1234 + rank)
+    def tn(*shape):
+        w = torch.empty(*shape)
+        torch.nn.init.trunc_normal_(w, std=0.02, a=-0.04, b=0.04, generator=g)
+        return w
+    weights = {
+        "w_qkv": tn(3 * C, C), "w_proj": tn(C, C), "w_fc1": tn(hidden, C), "w_fc2": tn(C, hidden)}
+    weights = {k: v.to(dev, torch.bfloat16).contiguous() for k, v in weights.items()}
+    for k, n in (("b_qkv", 3 * C), ("b_proj", C), ("b_fc1", hidden), ("b_fc2", C)):
+        weights[k] = torch.zeros(n, device=dev, dtype=torch.float32)
+    x_host = torch.randn(n_tiles, T, C, generator=g).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    x = x_host.to(dev)
+    y = torch.empty_like(x)
+    lat = (torch.linspace(0.2, 0.7, H).view(1, H, 1) - 0.3 * torch.arange(n_tiles).view(-1, 1, 1)
+           ).expand(n_tiles, H, W)
+    lon = (torch.linspace(0.1, 0.6, W).view(1, 1, W) + 0.7 * (torch.arange(n_tiles) + n_tiles * rank
+                                                                ).view(-1, 1, 1)).expand(n_tiles, H, W)
+    pos = torch.stack([lat, lon], dim=1).to(dev)
+    cos, sin = rope.stereographic_rope_tables(pos, C // heads, 1, rope.default_rope_length_scale(1))
+    cos, sin = cos.contiguous(), sin.contiguous()
+    ws = torch.empty(ops.block_workspace_bytes(M, C, hidden), dtype=torch.uint8, device=dev)
+
+    def step(inp, out):
+        ops.block_forward(inp, weights, grid=(D, H, W), num_heads=heads, kernel=kernel,
+                          rope_cos=cos, rope_sin=sin, workspace=ws, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step(x, y)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(lambda: step(x, y), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = _lib.device_status()
+    ms_step = ms_total / args.steps
+    tokens_job = M * world
+    value = tokens_job / (ms_step * 1e-3)
+
+    # end to end: host buffers in, host buffers out, through the same C-ABI call
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        step(x, y)
+        y_host.copy_(y, non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(2, min(args.steps, 10))
+    ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_value = tokens_job / (ms_e2e * 1e-3)
+
+    # per-kernel breakdown (same sequence as strata_block_forward_bf16, one event pair each)
+    breakdown = kernel_breakdown(torch, ops, x, weights, cos, sin, (D, H, W), heads, kernel, hidden)
+
+    if rank == 0:
+        tf_peak, hbm_peak, peak_kind = measured_peaks()
+        fpt = flops_per_token(C, kernel)
+        dom = max(breakdown, key=lambda k: k["ms"])
+        if dom["bound"] == "tensor":
+            achieved, peak, unit = dom["flop"] / (dom["ms"] * 1e-3) / 1e12, tf_peak, "TFLOP/s"
+        else:
+            achieved, peak, unit = dom["bytes"] / (dom["ms"] * 1e-3) / 1e9, hbm_peak, "GB/s"
+        cpu_tps, cpu_ms, cores, sample = cpu_block_tokens_per_s(2, 1)
+        line = {
+            "metric": "block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": WORKLOAD,
+            "block_tflops": fpt * tokens_job / (ms_step * 1e-3) / 1e12,
+            "block_frac_of_bf16_peak": fpt * M / (ms_step * 1e-3) / 1e12 / tf_peak,
+            "roofline": {"kernel": dom["name"], "bound": "tensor" if dom["bound"] == "tensor" else "hbm",
+                         "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                         "peak_source": peak_kind + " (burst)", "traffic": dom.get("traffic")},
+            "kernels": [{k: v for k, v in b.items() if k in ("name", "ms", "bound", "frac")}
+                        for b in breakdown],
+            "cpu_baseline": {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2 * world,
+                    "d2h_bytes_per_step": y_host.numel() * 2 * world},
+            "gpu_launches": 7 * args.steps, "device_status": status, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidden, iters=5):
+    """Times each kernel of the block alone (CUDA events on the launching stream) and attaches
+    its algorithmic flops / bytes and roofline fraction."""
+    tf_peak, hbm_peak, _ = measured_peaks()
+    D, H, W = grid
+    n_tiles, T, C = x.shape
+    M = n_tiles * T
+    x2 = x.reshape(M, C)
+    xn = ops.layernorm(x2)
+    qkv = ops.qkv_rope(xn, weights["w_qkv"], weights["b_qkv"], C // heads, cos, sin, T, H * W)
+    q6 = qkv.view(n_tiles, D, H, W, 3, heads, C // heads)
+    attn = torch.empty(n_tiles, D, H, W, heads, C // heads, dtype=torch.bfloat16, device=x.device)
+    x1 = torch.empty_like(x2)
+    hbuf = torch.empty(M, hidden, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty_like(x2)
+    K = kernel[0] * kernel[1] * kernel[2]
+    items = [
+        ("layernorm_rows", lambda: ops.layernorm(x2), "hbm", 0, 4 * M * C),
+        ("gemm_qkv_rope", lambda: ops.qkv_rope(xn, weights["w_qkv"], weights["b_qkv"], C // heads,
+                                               cos, sin, T, H * W), "tensor", 6 * C * C * M, 8 * M * C),
+        ("na3d_fwd", lambda: ops.na3d(q6[..., 0, :, :], q6[..., 1, :, :], q6[..., 2, :, :], kernel,
+                                      out=attn), "tensor", 4 * K * C * M, 8 * M * C),
+        ("gemm_proj_residual", lambda: ops.linear(attn.view(M, C), weights["w_proj"], weights["b_proj"],
+                                                  ops.EPI_RESIDUAL, x2, out=x1), "tensor",
+         2 * C * C * M, 6 * M * C),
+        ("gemm_fc1_gelu", lambda: ops.linear(xn, weights["w_fc1"], weights["b_fc1"], ops.EPI_GELU,
+                                             out=hbuf), "tensor", 2 * C * hidden * M, 2 * M * (C + hidden)),
+        ("gemm_fc2_residual", lambda: ops.linear(hbuf, weights["w_fc2"], weights["b_fc2"],
+                                                 ops.EPI_RESIDUAL, x1, out=y), "tensor",
+         2 * C * hidden * M, 2 * M * (hidden + 2 * C)),
+    ]
+    out = []
+    for name, fn, bound, flop, nbytes in items:
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        frac = (flop / (ms * 1e-3) / 1e12 / tf_peak) if bound == "tensor" else (
+            nbytes / (ms * 1e-3) / 1e9 / hbm_peak)
+        out.append({"name": name, "ms": ms, "bound": bound, "flop": flop, "bytes": nbytes,
+                    "frac": frac, "traffic": None})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="strata_b200", choices=["strata_b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

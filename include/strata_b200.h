@@ -84,6 +84,43 @@ int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
                          int heads, int head_dim, int kd, int kh, int kw, float scale,
                          void* stream);
 
+/* Weights of one backbone block, all DEVICE pointers. w_*: bf16 nn.Linear weights [out,in]
+ * (row-major, contiguous); b_*: fp32 biases or NULL. w_gate/b_gate NULL = ungated block.
+ * Names follow the reference's parameter manifest
+ * (tests/regression_data/ *.param_order.txt: attn.qkv, attn.proj, attn.gate_proj,
+ * mlp.layers.0, mlp.layers.2). */
+typedef struct strata_block_weights {
+  const void* w_qkv;   /* [3C, C] */
+  const float* b_qkv;  /* [3C] */
+  const void* w_proj;  /* [C, C] */
+  const float* b_proj;
+  const void* w_gate;  /* [C, C] or NULL */
+  const float* b_gate;
+  const void* w_fc1;   /* [hidden, C] */
+  const float* b_fc1;
+  const void* w_fc2;   /* [C, hidden] */
+  const float* b_fc2;
+} strata_block_weights;
+
+/* Scratch bytes strata_block_forward_bf16 needs for M tokens. */
+int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden);
+
+/* One Strata backbone block forward over n_tiles tiles of D*H*W tokens (tokens in d,h,w order,
+ * C channels innermost, bf16):
+ *   xn = LN(x); qkv = rope(xn Wqkv^T + b); a = NA3D(q,k,v); [a *= sigmoid(xn Wg^T + bg)]
+ *   x1 = x + a Wp^T + bp; y = x1 + fc2(gelu_tanh(fc1(LN(x1))))
+ * x and y are [n_tiles*D*H*W, C]; y may alias x. rope tables as in strata_qkv_rope_bf16
+ * (NULL = no rotation). workspace: strata_block_workspace_bytes(M, C, hidden) bytes of device
+ * scratch, 256-byte aligned, owned by the caller. Seven (eight if gated) kernels are launched
+ * on `stream`.
+ * Replaces one physicsnemo StrataTransformer3D block as driven by
+ * screamcast/strata_wrappers.py:314-341,414 (self.strata(x, pos=pos)). */
+int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H, int W, int C,
+                              int heads, int hidden, int kd, int kh, int kw,
+                              const strata_block_weights* h_weights, const float* rope_cos,
+                              const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ error, the call raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER, Structure
 from pathlib import Path
 
 _LIB_PATH = Path(__file__).resolve().parent / "libstrata_b200.so"
@@ -15,6 +15,12 @@ _lib = None
 
 class StrataLibraryError(RuntimeError):
     pass
+
+
+class BlockWeights(Structure):
+    """struct strata_block_weights (device pointers)."""
+    _fields_ = [(n, c_void_p) for n in ("w_qkv", "b_qkv", "w_proj", "b_proj", "w_gate", "b_gate",
+                                        "w_fc1", "b_fc1", "w_fc2", "b_fc2")]
 
 
 _SIGNATURES = {
@@ -32,6 +38,11 @@ _SIGNATURES = {
     "strata_na3d_fwd_bf16": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                      c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_float, c_void_p]),
+    "strata_block_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),
+    "strata_block_forward_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_int, POINTER(BlockWeights),
+                                          c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
+                                          c_int64, c_void_p]),
 }
 
 

@@ -69,6 +69,7 @@ int strata_layernorm_bf16(const void* x, int64_t ldx, void* y, int64_t ldy, int 
                           float eps, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (M == 0) return STRATA_OK;
   if (!x || !y || M < 0 || !aligned16(x) || !aligned16(y)) return STRATA_ERR_ARG;
   int r = launch_layernorm(static_cast<const __nv_bfloat16*>(x), ldx,
                            static_cast<__nv_bfloat16*>(y), ldy, M, C, eps, sms, as_stream(stream));
@@ -80,6 +81,7 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
                        int64_t ldaux, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (M == 0 && N > 0 && K > 0) return STRATA_OK;
   if (!x || !w || !y || M < 0 || N <= 0 || K <= 0) return STRATA_ERR_ARG;
   if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldx < K || ldw < K || ldy < N)
     return STRATA_ERR_ARG;
@@ -114,6 +116,7 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
                          int qk_norm, float qk_eps, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (M == 0 && C > 0) return STRATA_OK;
   if (!x || !w || !qkv || M < 0 || C <= 0) return STRATA_ERR_ARG;
   if (head_dim != 32 && head_dim != 64) return STRATA_ERR_UNSUPPORTED;
   if (C % 64 != 0 || C % head_dim != 0) return STRATA_ERR_UNSUPPORTED;
@@ -171,6 +174,63 @@ int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
   if (r == -1) return STRATA_ERR_ARG;
   if (r == -2) return STRATA_ERR_UNSUPPORTED;
   return r;
+}
+
+int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden) {
+  if (M < 0 || C <= 0 || hidden <= 0) return -1;
+  // xn [M,C] | qkv [M,3C] | attn [M,C] | x1 [M,C] | h [M,hidden], each rounded to 256 bytes
+  auto r256 = [](int64_t b) { return (b + 255) / 256 * 256; };
+  return r256(M * C * 2) * 3 + r256(M * 3 * C * 2) + r256(M * static_cast<int64_t>(hidden) * 2);
+}
+
+int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H, int W, int C,
+                              int heads, int hidden, int kd, int kh, int kw,
+                              const strata_block_weights* wts, const float* rope_cos,
+                              const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
+                              void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !y || !wts || !workspace || n_tiles < 0 || D <= 0 || H <= 0 || W <= 0)
+    return STRATA_ERR_ARG;
+  if (heads <= 0 || C % heads != 0) return STRATA_ERR_ARG;
+  const int hd = C / heads;
+  if (hd != 64) return STRATA_ERR_UNSUPPORTED;
+  const int64_t M64 = static_cast<int64_t>(n_tiles) * D * H * W;
+  if (M64 > 0x7fffffffLL) return STRATA_ERR_ARG;
+  const int M = static_cast<int>(M64);
+  if (workspace_bytes < strata_block_workspace_bytes(M, C, hidden)) return STRATA_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return STRATA_ERR_ARG;
+  if (!wts->w_qkv || !wts->w_proj || !wts->w_fc1 || !wts->w_fc2) return STRATA_ERR_ARG;
+  if (M == 0) return STRATA_OK;
+  auto r256 = [](int64_t b) { return (b + 255) / 256 * 256; };
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* xn = ws;               ws += r256(M64 * C * 2);
+  void* qkv = ws;              ws += r256(M64 * 3 * C * 2);
+  void* attn = ws;             ws += r256(M64 * C * 2);
+  void* x1 = ws;               ws += r256(M64 * C * 2);
+  void* hbuf = ws;
+  const int tokens_per_tile = D * H * W;
+  int r;
+  if ((r = strata_layernorm_bf16(x, C, xn, C, M, C, ln_eps, stream)) != 0) return r;
+  if ((r = strata_qkv_rope_bf16(xn, C, wts->w_qkv, C, wts->b_qkv, qkv, 3 * C, M, C, hd, rope_cos,
+                                rope_sin, tokens_per_tile, H * W, qk_norm, qk_eps, stream)) != 0)
+    return r;
+  const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(qkv);
+  if ((r = strata_na3d_fwd_bf16(qp, 3 * C, qp + C, 3 * C, qp + 2 * C, 3 * C, attn, C, n_tiles, D, H,
+                                W, heads, hd, kd, kh, kw, 0.f, stream)) != 0)
+    return r;
+  if (wts->w_gate) {
+    if ((r = strata_linear_bf16(xn, C, wts->w_gate, C, wts->b_gate, attn, C, M, C, C,
+                                STRATA_EPI_GATE, attn, C, stream)) != 0)
+      return r;
+  }
+  if ((r = strata_linear_bf16(attn, C, wts->w_proj, C, wts->b_proj, x1, C, M, C, C,
+                              STRATA_EPI_RESIDUAL, x, C, stream)) != 0)
+    return r;
+  if ((r = strata_layernorm_bf16(x1, C, xn, C, M, C, ln_eps, stream)) != 0) return r;
+  if ((r = strata_linear_bf16(xn, C, wts->w_fc1, C, wts->b_fc1, hbuf, hidden, M, hidden, C,
+                              STRATA_EPI_GELU, nullptr, 0, stream)) != 0)
+    return r;
+  return strata_linear_bf16(hbuf, hidden, wts->w_fc2, hidden, wts->b_fc2, y, C, M, C, hidden,
+                            STRATA_EPI_RESIDUAL, x1, C, stream);
 }
 
 }  // extern "C"

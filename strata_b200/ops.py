@@ -157,3 +157,66 @@ def na3d(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel, scale: float
             B, D, H, W, nh, hd, kd, kh, kw, float(scale) if scale else 0.0, _stream_ptr(q)),
             "strata_na3d_fwd_bf16")
     return out
+
+
+def block_workspace_bytes(M: int, C: int, hidden: int) -> int:
+    return int(_lib.load().strata_block_workspace_bytes(int(M), int(C), int(hidden)))
+
+
+def block_forward(x: torch.Tensor, weights: dict, *, grid, num_heads: int, kernel,
+                  rope_cos: torch.Tensor | None, rope_sin: torch.Tensor | None,
+                  qk_norm: bool = False, ln_eps: float = 1e-6, qk_eps: float = 1e-6,
+                  workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """One backbone block through strata_block_forward_bf16.
+
+    x: [n_tiles, D*H*W, C] bf16 contiguous. weights: bf16 'w_*' [out,in] and fp32 'b_*'
+    tensors keyed qkv/proj/gate/fc1/fc2 (gate optional). workspace: uint8 scratch of at least
+    block_workspace_bytes(M, C, hidden) bytes (allocated here when None).
+    """
+    _require_cuda_bf16(x, "x")
+    if x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous [n_tiles, D*H*W, C] tensor")
+    D, H, W = grid
+    n_tiles, T, C = x.shape
+    if T != D * H * W:
+        raise ValueError(f"x has {T} tokens per tile, grid {grid} has {D * H * W}")
+    kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(v) for v in kernel)
+    hidden = weights["w_fc1"].shape[0]
+    M = n_tiles * T
+    need = block_workspace_bytes(M, C, hidden)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    if workspace.numel() * workspace.element_size() < need:
+        raise ValueError(f"workspace too small: need {need} bytes")
+    if out is None:
+        out = torch.empty_like(x)
+    wstruct = _lib.BlockWeights()
+    keep = []
+    for name in ("qkv", "proj", "gate", "fc1", "fc2"):
+        w = weights.get(f"w_{name}")
+        b = weights.get(f"b_{name}")
+        if w is not None:
+            _require_cuda_bf16(w, f"w_{name}")
+            if not w.is_contiguous():
+                raise ValueError(f"w_{name} must be contiguous")
+            keep.append(w)
+        if b is not None:
+            if b.dtype != torch.float32 or not b.is_contiguous() or not b.is_cuda:
+                raise TypeError(f"b_{name} must be a contiguous CUDA float32 tensor")
+            keep.append(b)
+        setattr(wstruct, f"w_{name}", None if w is None else w.data_ptr())
+        setattr(wstruct, f"b_{name}", None if b is None else b.data_ptr())
+    rc = _f32_or_none(rope_cos, "rope_cos")
+    rs = _f32_or_none(rope_sin, "rope_sin")
+    if rc is not None and tuple(rc.shape) != (n_tiles, H * W, (C // num_heads) // 2):
+        raise ValueError(f"rope tables must be {(n_tiles, H * W, (C // num_heads) // 2)}, "
+                         f"got {tuple(rc.shape)}")
+    import ctypes
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_block_forward_bf16(
+            x.data_ptr(), out.data_ptr(), n_tiles, D, H, W, C, num_heads, hidden, kd, kh, kw,
+            ctypes.byref(wstruct), None if rc is None else rc.data_ptr(),
+            None if rs is None else rs.data_ptr(), 1 if qk_norm else 0, float(ln_eps),
+            float(qk_eps), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+            _stream_ptr(x)), "strata_block_forward_bf16")
+    return out

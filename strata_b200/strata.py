@@ -1,0 +1,238 @@
+"""StrataTransformer3D — the backbone the reference composes under `self.strata`
+(screamcast/strata_wrappers.py:314-341), rebuilt on the sm_100a kernels of this package.
+
+The module tree, parameter names, shapes and order follow the reference's parameter
+manifest (tests/regression_data/sweep1_*.param_order.txt):
+
+    patch_embed.proj.{weight,bias}                 Conv3d, kernel = stride = patch_size
+    blocks.{i}.attn.qkv.{weight,bias}              Linear(C, 3C)
+    blocks.{i}.attn.proj.{weight,bias}             Linear(C, C)
+    blocks.{i}.attn.gate_proj.{weight,bias}        Linear(C, C), only if gated_attention
+    blocks.{i}.mlp.layers.0.{weight,bias}          Linear(C, ratio*C)
+    blocks.{i}.mlp.layers.2.{weight,bias}          Linear(ratio*C, C)
+    final_layer.linear.{weight,bias}               Linear(C, pv*ph*ph*out_channels)
+
+so checkpoints keyed `strata.*` load unchanged. The blocks run in bf16 through
+libstrata_b200.so (fused QKV+RoPE GEMM, 3-D neighbourhood attention, GELU / residual GEMM
+epilogues); there is no PyTorch fallback for them. The patch embedding and the final
+projection are once-per-forward library calls (cuDNN conv / cuBLAS), as in the reference.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops, rope
+
+
+def _triple(v):
+    return (int(v),) * 3 if isinstance(v, int) else tuple(int(t) for t in v)
+
+
+class PatchEmbed3D(nn.Module):
+    """[B, C_in, D, H, W] -> tokens [B, D'*H'*W', embed_dim] (d, h, w order)."""
+
+    def __init__(self, in_chans: int, embed_dim: int, patch_size):
+        super().__init__()
+        self.patch_size = _triple(patch_size)
+        self.proj = nn.Conv3d(in_chans, embed_dim, kernel_size=self.patch_size,
+                              stride=self.patch_size)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.proj(x)
+        return y.flatten(2).transpose(1, 2)
+
+
+class Mlp(nn.Module):
+    """layers = Sequential(fc1, GELU, fc2); the reference's wrapper swaps the GELU to the tanh
+    approximation (screamcast/strata_wrappers.py:76-100)."""
+
+    def __init__(self, dim: int, hidden: int):
+        super().__init__()
+        self.layers = nn.Sequential(nn.Linear(dim, hidden), nn.GELU(approximate="none"),
+                                    nn.Linear(hidden, dim))
+
+
+class NeighborhoodAttention3D(nn.Module):
+    def __init__(self, dim: int, num_heads: int, qkv_bias: bool, gated: bool):
+        super().__init__()
+        self.num_heads = num_heads
+        self.qkv = nn.Linear(dim, 3 * dim, bias=qkv_bias)
+        self.proj = nn.Linear(dim, dim)
+        if gated:
+            self.gate_proj = nn.Linear(dim, dim)
+
+
+class StrataTransformer3DBlock(nn.Module):
+    """Pre-norm block without norm parameters: x += proj(gate * NA3D(rope(qkv(LN(x)))));
+    x += fc2(gelu(fc1(LN(x))))."""
+
+    def __init__(self, dim: int, num_heads: int, mlp_ratio: float, qkv_bias: bool, qk_norm: bool,
+                 gated: bool, kernel):
+        super().__init__()
+        self.dim, self.num_heads = dim, num_heads
+        self.qk_norm = qk_norm
+        self.kernel = _triple(kernel)
+        self.attn = NeighborhoodAttention3D(dim, num_heads, qkv_bias, gated)
+        self.mlp = Mlp(dim, int(dim * mlp_ratio))
+        self._bf16_cache = None
+        self._bf16_key = None
+
+    def _gelu_is_tanh(self) -> bool:
+        act = self.mlp.layers[1]
+        return isinstance(act, nn.GELU) and act.approximate == "tanh"
+
+    def device_weights(self) -> dict:
+        """bf16 weights / fp32 biases for the C ABI, re-cast whenever a parameter changes."""
+        params = [self.attn.qkv.weight, self.attn.proj.weight, self.mlp.layers[0].weight,
+                  self.mlp.layers[2].weight]
+        key = tuple((p.data_ptr(), p._version, p.device) for p in self.parameters())
+        if self._bf16_cache is not None and key == self._bf16_key:
+            return self._bf16_cache
+
+        def w(lin):
+            return lin.weight.detach().to(torch.bfloat16).contiguous()
+
+        def b(lin):
+            return None if lin.bias is None else lin.bias.detach().float().contiguous()
+
+        cache = {"w_qkv": w(self.attn.qkv), "b_qkv": b(self.attn.qkv),
+                 "w_proj": w(self.attn.proj), "b_proj": b(self.attn.proj),
+                 "w_fc1": w(self.mlp.layers[0]), "b_fc1": b(self.mlp.layers[0]),
+                 "w_fc2": w(self.mlp.layers[2]), "b_fc2": b(self.mlp.layers[2])}
+        if hasattr(self.attn, "gate_proj"):
+            cache["w_gate"], cache["b_gate"] = w(self.attn.gate_proj), b(self.attn.gate_proj)
+        self._bf16_cache, self._bf16_key = cache, key
+        del params
+        return cache
+
+    def forward(self, x: torch.Tensor, grid, rope_cos, rope_sin, workspace=None) -> torch.Tensor:
+        """x: [n_tiles, D*H*W, C] bf16 contiguous; returns the same shape."""
+        if not self._gelu_is_tanh():
+            raise RuntimeError(
+                "the fused MLP kernel implements the tanh GELU the Strata checkpoints were "
+                "trained with; this block's Mlp still holds an exact GELU (the wrapper's "
+                "tanh swap did not run)")
+        return ops.block_forward(x, self.device_weights(), grid=grid, num_heads=self.num_heads,
+                                 kernel=self.kernel, rope_cos=rope_cos, rope_sin=rope_sin,
+                                 qk_norm=self.qk_norm, workspace=workspace)
+
+
+class FinalLayer(nn.Module):
+    """Non-affine LayerNorm + Linear to patch pixels."""
+
+    def __init__(self, dim: int, out_features: int):
+        super().__init__()
+        self.linear = nn.Linear(dim, out_features)
+
+
+class StrataTransformer3D(nn.Module):
+    """Backbone: patch embed -> N blocks -> final projection -> unpatchify.
+
+    forward(x[B, C_in, D, H, W], pos[B, 2, H, W] lat/lon radians) -> [B, C_out, D, H, W].
+    """
+
+    def __init__(self, *, in_channels: int, out_channels: int, input_shape, patch_size=(1, 1, 1),
+                 embed_dim: int = 768, num_heads: int = 16, num_layers: int = 12,
+                 mlp_ratio: float = 4.0, qkv_bias: bool = True, qk_norm: bool = False,
+                 qk_norm_affine: bool = False, attn_kernel=3, na_dilation: int = 3,
+                 do_interleaved_dilation: bool = False, do_alt_depthwise_attn: bool = False,
+                 gated_attention: bool = False, na3d_backend: str | None = None,
+                 rope_mode: str = "none", rope_base: float = 100.0, rope_length_scale: float = 1.0,
+                 activation_checkpointing: bool | float = False, bf16_mixed: bool = False):
+        super().__init__()
+        if rope_mode not in ("none", "axial", "stereographic"):
+            raise ValueError(f"unknown rope_mode {rope_mode!r}")
+        if qk_norm_affine:
+            raise ValueError("qk_norm_affine=True is not supported (production configs use "
+                             "non-affine qk norm)")
+        if do_interleaved_dilation:
+            raise ValueError("dilated neighbourhood attention is not supported "
+                             "(production configs use dilation 1)")
+        if embed_dim % num_heads or embed_dim // num_heads != 64:
+            raise ValueError("head_dim must be 64 for the sm_100a attention kernel")
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.depth, self.height, self.width = (int(v) for v in input_shape)
+        self.patch_size = _triple(patch_size)
+        self.embed_dim, self.num_heads = embed_dim, num_heads
+        self.head_dim = embed_dim // num_heads
+        self.rope_mode, self.rope_base = rope_mode, float(rope_base)
+        self.rope_length_scale = float(rope_length_scale)
+        self.na3d_backend = na3d_backend  # accepted for config compatibility; one backend here
+        self.bf16_mixed = bf16_mixed
+        self._activation_checkpointing_ratio = float(activation_checkpointing)
+        kernel = _triple(attn_kernel)
+        self.attn_kernel = kernel
+        self.patch_embed = PatchEmbed3D(in_channels, embed_dim, self.patch_size)
+        blocks = []
+        for i in range(num_layers):
+            k = kernel
+            if do_alt_depthwise_attn and i % 2 == 1:
+                # every other block attends along depth only (kd x 1 x 1 window)
+                k = (kernel[0], 1, 1)
+            blocks.append(StrataTransformer3DBlock(embed_dim, num_heads, mlp_ratio, qkv_bias,
+                                                   qk_norm, gated_attention, k))
+        self.blocks = nn.ModuleList(blocks)
+        pv, ph, pw = self.patch_size
+        self.final_layer = FinalLayer(embed_dim, pv * ph * pw * out_channels)
+        self._workspace = None
+
+    # ---------------------------------------------------------------- geometry
+    def set_tile_size(self, height: int, width: int) -> None:
+        self.height, self.width = int(height), int(width)
+
+    def token_grid(self, D: int, H: int, W: int):
+        pv, ph, pw = self.patch_size
+        return D // pv, H // ph, W // pw
+
+    def rope_tables(self, pos: torch.Tensor | None, n_tiles: int, grid):
+        _, h, w = grid
+        if self.rope_mode == "none":
+            return None, None
+        if self.rope_mode == "axial":
+            cos, sin = rope.axial_rope_tables(h, w, self.head_dim, self.rope_base,
+                                              device=self.final_layer.linear.weight.device)
+            return cos.expand(n_tiles, -1, -1).contiguous(), sin.expand(n_tiles, -1, -1).contiguous()
+        if pos is None:
+            raise ValueError("stereographic RoPE needs pos=[B, 2, H, W] (lat, lon)")
+        return rope.stereographic_rope_tables(pos, self.head_dim, self.patch_size[1],
+                                              self.rope_length_scale, self.rope_base)
+
+    def _get_workspace(self, M: int, device) -> torch.Tensor:
+        hidden = self.blocks[0].mlp.layers[0].out_features
+        need = ops.block_workspace_bytes(M, self.embed_dim, hidden)
+        ws = self._workspace
+        if ws is None or ws.numel() < need or ws.device != device:
+            ws = torch.empty(need, dtype=torch.uint8, device=device)
+            self._workspace = ws
+        return ws
+
+    # ---------------------------------------------------------------- forward
+    def forward_tokens(self, tokens: torch.Tensor, grid, rope_cos, rope_sin) -> torch.Tensor:
+        """Runs the block stack on bf16 tokens [n_tiles, D*H*W, C]."""
+        ws = self._get_workspace(tokens.shape[0] * tokens.shape[1], tokens.device)
+        x = tokens
+        for blk in self.blocks:
+            x = blk(x, grid, rope_cos, rope_sin, workspace=ws)
+        return x
+
+    def forward(self, x: torch.Tensor, pos: torch.Tensor | None = None) -> torch.Tensor:
+        B, _, D, H, W = x.shape
+        grid = self.token_grid(D, H, W)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=x.is_cuda):
+            tokens = self.patch_embed(x)
+        tokens = tokens.to(torch.bfloat16).contiguous()
+        cos, sin = self.rope_tables(pos, B, grid)
+        tokens = self.forward_tokens(tokens, grid, cos, sin)
+        y = torch.nn.functional.layer_norm(tokens.float(), (self.embed_dim,), eps=1e-6)
+        y = self.final_layer.linear(y)
+        return self.unpatchify(y, grid)
+
+    def unpatchify(self, y: torch.Tensor, grid) -> torch.Tensor:
+        B = y.shape[0]
+        d, h, w = grid
+        pv, ph, pw = self.patch_size
+        c = self.out_channels
+        y = y.reshape(B, d, h, w, pv, ph, pw, c)
+        y = y.permute(0, 7, 1, 4, 2, 5, 3, 6)
+        return y.reshape(B, c, d * pv, h * ph, w * pw)

@@ -1,0 +1,286 @@
+"""Drop-in counterparts of the reference's model wrappers (screamcast/strata_wrappers.py):
+same class names, constructor arguments, methods, properties, error behaviour and
+state-dict keys (`strata.*`), with `self.strata` built from this package's sm_100a backbone
+instead of physicsnemo + NATTEN.
+
+    network = StrataBackboneModel(depth=..., height=..., width=..., embed_dim=..., ...)
+    y = network(x, index)      # x [B, C, D, H, W]; index: column ids or {"lat","lon"} radians
+"""
+from __future__ import annotations
+
+import math
+from typing import Mapping, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import rope
+from .strata import Mlp, StrataTransformer3D
+
+
+# --------------------------------------------------------------------------- helpers
+def _replace_channels(x: torch.Tensor, replacements: dict) -> torch.Tensor:
+    """Channel-dim rebuild by slice + cat (reference: strata_wrappers.py:61-73)."""
+    pieces = [replacements[c].unsqueeze(1) if c in replacements else x[:, c:c + 1]
+              for c in range(x.shape[1])]
+    return torch.cat(pieces, dim=1)
+
+
+def _use_tanh_gelu(model: nn.Module) -> None:
+    """Swap every Mlp's exact GELU for the tanh approximation (strata_wrappers.py:76-100)."""
+    n = 0
+    for module in model.modules():
+        if isinstance(module, Mlp):
+            for i, layer in enumerate(module.layers):
+                if isinstance(layer, nn.GELU) and layer.approximate == "none":
+                    module.layers[i] = nn.GELU(approximate="tanh")
+                    n += 1
+    if n == 0:
+        raise RuntimeError("_use_tanh_gelu found no exact-GELU Mlp layers to swap")
+
+
+def _resolve_rope_base(rope_length_scale: Optional[float]) -> float:
+    """None / 0 -> the historical default; negative raises (strata_wrappers.py:134-150)."""
+    if rope_length_scale is not None and rope_length_scale < 0:
+        raise ValueError("rope_length_scale must be positive (or 0/None for the default); "
+                         f"got {rope_length_scale}")
+    return rope_length_scale or TileGeometry.default_rope_length_scale(1)
+
+
+def _rope_mode(do_rope_2d: bool, do_rope_2d_stereographic: bool) -> str:
+    if do_rope_2d and do_rope_2d_stereographic:
+        raise ValueError("Cannot use both row/column RoPE and stereographic RoPE simultaneously")
+    if do_rope_2d_stereographic:
+        return "stereographic"
+    return "axial" if do_rope_2d else "none"
+
+
+def mean_longitude(lon: torch.Tensor, reduce_dims=(-2, -1), return_0_2pi: bool = True):
+    """Circular mean of longitude (reference: screamcast/tile_geometry.py:33-61)."""
+    s = lon.sin().mean(dim=reduce_dims, keepdim=True)
+    c = lon.cos().mean(dim=reduce_dims, keepdim=True)
+    m = torch.atan2(s, c)
+    return m % (2 * torch.pi) if return_0_2pi else m
+
+
+class TileGeometry(nn.Module):
+    """index -> per-pixel lat/lon (radians). Explicit {"lat","lon"} indices pass through;
+    integer column ids need lookup tables, which the reference reads from earth2grid or a
+    grid file (screamcast/tile_geometry.py:64-112) and which are supplied here with
+    set_lookup_tables() because neither source is part of this package."""
+
+    def __init__(self, grid_type: str = "healpix", nside: int = 1024,
+                 cubesphere_latlon_path: str | None = None, index_is_latlon: bool = False):
+        super().__init__()
+        self.grid_type = (grid_type or "healpix").lower()
+        if self.grid_type not in {"healpix", "cubesphere"}:
+            raise ValueError(f"Unsupported grid_type='{grid_type}'. Expected 'healpix' or "
+                             "'cubesphere'.")
+        self.nside = nside
+        self.index_is_latlon = index_is_latlon
+        self.register_buffer("_lat_radians", torch.zeros(0), persistent=False)
+        self.register_buffer("_lon_radians", torch.zeros(0), persistent=False)
+
+    def set_lookup_tables(self, lat_radians: torch.Tensor, lon_radians: torch.Tensor) -> None:
+        self.register_buffer("_lat_radians", lat_radians.float(), persistent=False)
+        self.register_buffer("_lon_radians", lon_radians.float(), persistent=False)
+
+    def lat_lon_from_index(self, index):
+        if self.index_is_latlon:
+            try:
+                lat, lon = index["lat"], index["lon"]
+            except Exception as exc:
+                raise ValueError("index must provide 'lat' and 'lon' tensors when "
+                                 "index_is_latlon is True") from exc
+            if lat.ndim == 2:
+                lat = lat.unsqueeze(0)
+            if lon.ndim == 2:
+                lon = lon.unsqueeze(0)
+            if lat.ndim != 3 or lon.ndim != 3:
+                raise ValueError("lat/lon tensors must be 2D or 3D with shape [B, H, W]")
+            if lat.shape != lon.shape:
+                raise ValueError("lat/lon tensors must have matching shapes")
+            return lat, lon
+        if self._lat_radians.numel() == 0:
+            raise ValueError("integer tile indices need lat/lon lookup tables: call "
+                             "geometry.set_lookup_tables(lat, lon) or use index_is_latlon=True")
+        return self._lat_radians[index.long()], self._lon_radians[index.long()]
+
+    @staticmethod
+    def tile_center(lat: torch.Tensor, lon: torch.Tensor):
+        """Arithmetic-mean latitude, circular-mean longitude, each [B, 1, 1]."""
+        return lat.mean(dim=(1, 2), keepdim=True), mean_longitude(lon)
+
+    @staticmethod
+    def default_rope_length_scale(patch_size_horiz: int) -> float:
+        return rope.default_rope_length_scale(patch_size_horiz)
+
+
+# --------------------------------------------------------------------------- wind rotation
+def local_basis_ENR(lat, lon):
+    """East, north, radial unit vectors (reference: screamcast/wind_rotation.py:26-46)."""
+    cl, sl, co, so = torch.cos(lat), torch.sin(lat), torch.cos(lon), torch.sin(lon)
+    return (-so, co, torch.zeros_like(lat)), (-sl * co, -sl * so, cl), (cl * co, cl * so, sl)
+
+
+def forward_uv_to_tile(U, V, lat, lon, lat0, lon0):
+    """(U,V) east/north at each pixel -> components in the tile centre's tangent basis
+    (reference: screamcast/wind_rotation.py:49-92)."""
+    lat, lon, lat0, lon0 = lat.unsqueeze(1), lon.unsqueeze(1), lat0.unsqueeze(1), lon0.unsqueeze(1)
+    E, N, _ = local_basis_ENR(lat, lon)
+    v = [U * E[i] + V * N[i] for i in range(3)]
+    E0, N0, R0 = local_basis_ENR(lat0, lon0)
+    d = v[0] * R0[0] + v[1] * R0[1] + v[2] * R0[2]
+    vt = [v[i] - d * R0[i] for i in range(3)]
+    return (vt[0] * E0[0] + vt[1] * E0[1] + vt[2] * E0[2],
+            vt[0] * N0[0] + vt[1] * N0[1] + vt[2] * N0[2])
+
+
+def inverse_tile_to_uv(U_loc, V_loc, lat, lon, lat0, lon0):
+    """Inverse of forward_uv_to_tile (reference: screamcast/wind_rotation.py:95-144)."""
+    lat, lon, lat0, lon0 = lat.unsqueeze(1), lon.unsqueeze(1), lat0.unsqueeze(1), lon0.unsqueeze(1)
+    E0, N0, R0 = local_basis_ENR(lat0, lon0)
+    vt = [U_loc * E0[i] + V_loc * N0[i] for i in range(3)]
+    E, N, R = local_basis_ENR(lat, lon)
+    beta = -(vt[0] * R[0] + vt[1] * R[1] + vt[2] * R[2]) / (R0[0] * R[0] + R0[1] * R[1] + R0[2] * R[2])
+    v = [vt[i] + beta * R0[i] for i in range(3)]
+    return (v[0] * E[0] + v[1] * E[1] + v[2] * E[2], v[0] * N[0] + v[1] * N[1] + v[2] * N[2])
+
+
+# --------------------------------------------------------------------------- wrappers
+class _StrataModelBase(nn.Module):
+    """Geometry / wind / latitude-concat plumbing (reference: strata_wrappers.py:165-249)."""
+
+    def __init__(self, *, do_concat_latitude: bool, do_rotate_wind: bool,
+                 wind_channel_indices: Optional[Tuple[int, int]], grid_type: str, nside: int,
+                 cubesphere_latlon_path: str, index_is_latlon: bool):
+        super().__init__()
+        if do_rotate_wind and wind_channel_indices is None:
+            raise ValueError("Must specify wind_channel_indices when do_rotate_wind is True")
+        self._do_concat_latitude = do_concat_latitude
+        self._do_rotate_wind = do_rotate_wind
+        self._wind_channel_indices = wind_channel_indices
+        self.geometry = TileGeometry(grid_type=grid_type, nside=nside,
+                                     cubesphere_latlon_path=cubesphere_latlon_path,
+                                     index_is_latlon=index_is_latlon)
+
+    @property
+    def _index_is_latlon(self) -> bool:
+        return self.geometry.index_is_latlon
+
+    def _preprocess(self, x, index):
+        B, _, dd, _, _ = x.shape
+        lat, lon = self.geometry.lat_lon_from_index(index)
+        if lat.shape[0] != B:
+            lat = lat.expand(B, -1, -1)
+            lon = lon.expand(B, -1, -1)
+        lat_lon_data = None
+        if self._do_rotate_wind:
+            lat0, lon0 = TileGeometry.tile_center(lat, lon)
+            lat_lon_data = (lat, lon, lat0, lon0)
+            u_idx, v_idx = self._wind_channel_indices
+            u_rot, v_rot = forward_uv_to_tile(x[:, u_idx], x[:, v_idx], lat, lon, lat0, lon0)
+            x = _replace_channels(x, {u_idx: u_rot, v_idx: v_rot})
+        if self._do_concat_latitude:
+            lat_e = lat.unsqueeze(1).unsqueeze(2).expand(-1, 1, dd, -1, -1)
+            x = torch.cat([x, torch.cos(lat_e), torch.sin(lat_e)], dim=1)
+        pos = torch.cat([lat.unsqueeze(1), lon.unsqueeze(1)], dim=1)
+        return x, pos, lat_lon_data
+
+    def _postprocess(self, x, lat_lon_data):
+        if self._do_rotate_wind and lat_lon_data is not None:
+            lat, lon, lat0, lon0 = lat_lon_data
+            u_idx, v_idx = self._wind_channel_indices
+            u_geo, v_geo = inverse_tile_to_uv(x[:, u_idx], x[:, v_idx], lat, lon, lat0, lon0)
+            x = _replace_channels(x, {u_idx: u_geo, v_idx: v_geo})
+        return x
+
+
+class StrataBackboneModel(_StrataModelBase):
+    """Single-stage model (reference: strata_wrappers.py:252-415). Constructor argument
+    names and defaults are the reference's."""
+
+    def __init__(self, *, depth: int = 256, height: int = 256, width: int = 256,
+                 n_layers: int = 12, nside: int = 1024, patch_size: int = 1,
+                 patch_size_vert: int | None = None, patch_size_horiz: int | None = None,
+                 in_chans: int = 3, base_out_chans: int = 3, embed_dim: int = 768,
+                 num_heads: int = 16, mlp_ratio: float = 4.0, qkv_bias: bool = True,
+                 qk_norm: bool = False, qk_norm_elementwise_affine: bool = False,
+                 attn_kernel: int | tuple[int, int, int] = 3, do_alt_depthwise_attn: bool = False,
+                 do_interleaved_dilation: bool = False, na_dilations: int = 3,
+                 do_rope_2d: bool = False, do_rope_2d_stereographic: bool = False,
+                 do_concat_latitude: bool = True, do_rotate_wind: bool = False,
+                 wind_channel_indices: Optional[Tuple[int, int]] = None,
+                 do_bf16_mixed: bool = False, do_activation_checkpointing: bool | float = False,
+                 gated_attention: bool = False, na3d_backend: Optional[str] = None,
+                 grid_type: str = "healpix", cubesphere_latlon_path: str = "data/latlon_ne1024pg2.nc",
+                 rope_length_scale: Optional[float] = None, index_is_latlon: bool = False,
+                 use_dealiased_patch_embed: bool = False,
+                 dealias_resample_filter: tuple = (1, 4, 6, 4, 1)):
+        super().__init__(do_concat_latitude=do_concat_latitude, do_rotate_wind=do_rotate_wind,
+                         wind_channel_indices=wind_channel_indices, grid_type=grid_type,
+                         nside=nside, cubesphere_latlon_path=cubesphere_latlon_path,
+                         index_is_latlon=index_is_latlon)
+        if use_dealiased_patch_embed:
+            raise ValueError("use_dealiased_patch_embed is not supported by this package yet")
+        pv = patch_size_vert if patch_size_vert is not None else patch_size
+        ph = patch_size_horiz if patch_size_horiz is not None else patch_size
+        rope_mode = _rope_mode(do_rope_2d, do_rope_2d_stereographic)
+        self._rope_length_scale_base = _resolve_rope_base(rope_length_scale)
+        self.strata = StrataTransformer3D(
+            in_channels=in_chans + (2 if do_concat_latitude else 0),
+            out_channels=base_out_chans, input_shape=(depth, height, width),
+            patch_size=(pv, ph, ph), embed_dim=embed_dim, num_heads=num_heads,
+            num_layers=n_layers, mlp_ratio=mlp_ratio, qkv_bias=qkv_bias, qk_norm=qk_norm,
+            qk_norm_affine=qk_norm_elementwise_affine, attn_kernel=attn_kernel,
+            na_dilation=na_dilations, do_interleaved_dilation=do_interleaved_dilation,
+            do_alt_depthwise_attn=do_alt_depthwise_attn, gated_attention=gated_attention,
+            na3d_backend=na3d_backend, rope_mode=rope_mode, rope_base=100.0,
+            rope_length_scale=(self._rope_length_scale_base * ph
+                               if rope_mode == "stereographic" else 1.0),
+            activation_checkpointing=do_activation_checkpointing, bf16_mixed=do_bf16_mixed)
+        _use_tanh_gelu(self.strata)
+
+    @property
+    def _out_chans(self) -> int:
+        return self.strata.out_channels
+
+    @property
+    def _depth(self) -> int:
+        return self.strata.depth
+
+    @property
+    def _height(self) -> int:
+        return self.strata.height
+
+    @property
+    def _width(self) -> int:
+        return self.strata.width
+
+    @property
+    def _activation_checkpointing_ratio(self) -> float:
+        return self.strata._activation_checkpointing_ratio
+
+    @_activation_checkpointing_ratio.setter
+    def _activation_checkpointing_ratio(self, value: float) -> None:
+        _ = self.strata._activation_checkpointing_ratio
+        self.strata._activation_checkpointing_ratio = value
+
+    def disable_activation_checkpointing(self) -> None:
+        self._activation_checkpointing_ratio = 0.0
+
+    def set_tile_size(self, height: int, width: int) -> None:
+        self.strata.set_tile_size(height, width)
+
+    def set_rope_length_scale(self, base: float) -> None:
+        if base <= 0:
+            raise ValueError(f"rope length scale base must be positive, got {base}")
+        if self.strata.rope_mode != "stereographic":
+            raise ValueError("set_rope_length_scale is only meaningful for stereographic RoPE")
+        self._rope_length_scale_base = base
+        self.strata.rope_length_scale = base * self.strata.patch_size[1]
+
+    def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+        x, pos, lat_lon_data = self._preprocess(x, index)
+        x = self.strata(x, pos=pos)
+        return self._postprocess(x, lat_lon_data)

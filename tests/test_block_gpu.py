@@ -1,0 +1,194 @@
+"""GPU parity of the kernels and of the whole block against the CPU oracle, through the C ABI.
+
+Tolerances (stated by the task): bf16 outputs within 2e-2 max-abs relative error of the fp32
+oracle; against the oracle that rounds to bf16 at the same points as the GPU path
+(fp32 accumulation on both sides) the relative RMS difference stays below 1e-3.
+"""
+import pytest
+import torch
+
+from oracle import block_oracle as bo
+from tests.util import device_block_weights, rel_max_err, rel_rms_err, tile_latlon
+
+pytestmark = pytest.mark.gpu
+TOL_BF16 = 2e-2
+TOL_FP32_ACC = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from strata_b200 import ops as _ops
+    assert torch.cuda.is_available()
+    return _ops
+
+
+def _status():
+    from strata_b200 import _lib
+    return _lib.device_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1000, 384, 512), (300, 200, 72), (4096, 1536, 512),
+                                   (19072, 512, 2048), (1, 64, 64)])
+def test_linear_bias(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    b = torch.randn(N, generator=g)
+    y = ops.linear(x.cuda(), w.cuda(), b.cuda())
+    assert _status() == 0
+    ref = x.float() @ w.float().T + b
+    assert rel_max_err(y, ref) < TOL_BF16
+    assert rel_rms_err(y, ref.bfloat16()) < TOL_FP32_ACC
+
+
+@pytest.mark.parametrize("epi", ["gelu", "residual", "gate"])
+@pytest.mark.parametrize("M,N,K", [(2048, 512, 512), (777, 320, 256)])
+def test_linear_epilogues(ops, epi, M, N, K):
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    b = torch.randn(N, generator=g)
+    aux = torch.randn(M, N, generator=g).bfloat16()
+    acc = x.float() @ w.float().T + b
+    if epi == "gelu":
+        y = ops.linear(x.cuda(), w.cuda(), b.cuda(), ops.EPI_GELU)
+        ref = torch.nn.functional.gelu(acc, approximate="tanh")
+    elif epi == "residual":
+        y = ops.linear(x.cuda(), w.cuda(), b.cuda(), ops.EPI_RESIDUAL, aux.cuda())
+        ref = acc + aux.float()
+    else:
+        y = ops.linear(x.cuda(), w.cuda(), b.cuda(), ops.EPI_GATE, aux.cuda())
+        ref = aux.float() * torch.sigmoid(acc)
+    assert _status() == 0
+    assert rel_max_err(y, ref) < TOL_BF16
+
+
+def test_linear_rejects_bad_arguments(ops):
+    x = torch.zeros(8, 60, dtype=torch.bfloat16, device="cuda")   # K not a multiple of 8
+    w = torch.zeros(16, 60, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.linear(x, w)
+    with pytest.raises(ValueError):
+        ops.linear(torch.zeros(8, 64, dtype=torch.bfloat16, device="cuda"),
+                   torch.zeros(16, 32, dtype=torch.bfloat16, device="cuda"))
+    # empty input: nothing to do, no error
+    y = ops.linear(torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda"),
+                   torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda"))
+    assert y.shape == (0, 16)
+
+
+def test_layernorm(ops):
+    g = torch.Generator().manual_seed(1)
+    for M, C in [(5000, 512), (33, 128), (700, 1024), (10, 768)]:
+        x = (torch.randn(M, C, generator=g) * 2 + 0.5).bfloat16()
+        y = ops.layernorm(x.cuda())
+        ref = torch.nn.functional.layer_norm(x.float(), (C,), eps=1e-6)
+        assert rel_max_err(y, ref) < TOL_BF16
+        assert rel_rms_err(y, ref.bfloat16()) < TOL_FP32_ACC
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+@pytest.mark.parametrize("hd", [64, 32])
+def test_qkv_rope(ops, qk_norm, hd):
+    n_tiles, D, H, W, C = 2, 3, 8, 8, 128
+    heads = C // hd
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(n_tiles * D * H * W, C, generator=g).bfloat16()
+    w = (torch.randn(3 * C, C, generator=g) * 0.08).bfloat16()
+    b = torch.randn(3 * C, generator=g) * 0.1
+    lat, lon = tile_latlon(n_tiles, H, W)
+    cos, sin = bo.stereographic_rope_tables(lat, lon, hd, 1, bo.default_rope_length_scale(1))
+    y = ops.qkv_rope(x.cuda(), w.cuda(), b.cuda(), hd, cos.cuda(), sin.cuda(), D * H * W, H * W,
+                     qk_norm=qk_norm)
+    assert _status() == 0
+    qkv = (x.float() @ w.float().T + b).reshape(n_tiles, D, H * W, 3, heads, hd)
+    q, k, v = qkv[:, :, :, 0], qkv[:, :, :, 1], qkv[:, :, :, 2]
+    if qk_norm:
+        q, k = bo.rms_norm(q), bo.rms_norm(k)
+    q, k = bo.apply_rope(q, cos, sin), bo.apply_rope(k, cos, sin)
+    ref = torch.stack([q, k, v], dim=3).reshape(-1, 3 * C)
+    assert rel_max_err(y, ref) < TOL_BF16
+
+
+NA_CASES = [
+    (1, 4, 16, 16, 2, (3, 9, 9)), (1, 2, 8, 8, 1, (1, 3, 3)), (2, 5, 19, 21, 1, (3, 7, 7)),
+    (1, 6, 24, 24, 2, (5, 13, 13)), (1, 1, 32, 32, 2, (1, 9, 9)), (1, 3, 16, 16, 1, (3, 15, 15)),
+    (1, 8, 9, 9, 1, (3, 9, 9)),       # window == whole axis: every query sees every key
+    (1, 7, 12, 30, 1, (5, 11, 5)), (1, 5, 8, 8, 1, (5, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("B,D,H,W,nh,kernel", NA_CASES)
+def test_na3d_matches_oracle(ops, B, D, H, W, nh, kernel):
+    g = torch.Generator().manual_seed(B * 1000 + D * 100 + H)
+    q, k, v = (torch.randn(B, D, H, W, nh, 64, generator=g).bfloat16() for _ in range(3))
+    o = ops.na3d(q.cuda(), k.cuda(), v.cuda(), kernel)
+    assert _status() == 0
+    ref = bo.na3d(q.float(), k.float(), v.float(), kernel)
+    assert rel_max_err(o, ref) < TOL_BF16
+
+
+def test_na3d_packed_qkv_views_and_unwritten_cells(ops):
+    B, D, H, W, nh = 2, 4, 16, 16, 2
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, D, H, W, 3, nh, 64, generator=g).bfloat16()
+    dq = qkv.cuda()
+    out = torch.full((B, D, H, W, nh, 64), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.na3d(dq[..., 0, :, :], dq[..., 1, :, :], dq[..., 2, :, :], (3, 9, 9), out=out)
+    assert _status() == 0
+    assert not torch.isnan(out).any()          # NaN-poisoned output: every cell must be written
+    ref = bo.na3d(qkv[..., 0, :, :].float(), qkv[..., 1, :, :].float(), qkv[..., 2, :, :].float(),
+                  (3, 9, 9))
+    assert rel_max_err(out, ref) < TOL_BF16
+
+
+def test_na3d_rejects_oversized_kernel(ops):
+    q = torch.zeros(1, 2, 8, 8, 1, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.na3d(q, q, q, (3, 3, 3))       # kd > D
+    with pytest.raises(Exception):
+        ops.na3d(q, q, q, (1, 3, 4))       # even kernel: no kernel for it
+
+
+@pytest.mark.parametrize("gated,qk_norm,kernel,grid", [
+    (False, False, (3, 7, 7), (4, 16, 16)),
+    (True, True, (3, 9, 9), (4, 16, 16)),
+    (False, False, (1, 5, 5), (2, 8, 24)),
+])
+def test_block_forward_matches_oracle(ops, gated, qk_norm, kernel, grid):
+    C, heads, n_tiles = 256, 4, 2
+    D, H, W = grid
+    p = bo.init_block_params(C, gated=gated, seed=3)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(n_tiles, D * H * W, C, generator=g)
+    lat, lon = tile_latlon(n_tiles, H, W)
+    cos, sin = bo.stereographic_rope_tables(lat, lon, C // heads, 1, bo.default_rope_length_scale(1))
+    y = ops.block_forward(x.bfloat16().cuda().contiguous(), device_block_weights(p, "cuda"),
+                          grid=grid, num_heads=heads, kernel=kernel, rope_cos=cos.cuda(),
+                          rope_sin=sin.cuda(), qk_norm=qk_norm)
+    assert _status() == 0
+    kw = dict(grid=grid, num_heads=heads, kernel=kernel, rope_cos=cos, rope_sin=sin,
+              qk_norm=qk_norm, gated=gated)
+    ref = bo.block_forward(x.bfloat16().float(), p, **kw)
+    ref_bf16 = bo.block_forward(x.bfloat16().float(), p, emulate_bf16=True, **kw)
+    assert rel_max_err(y, ref) < TOL_BF16
+    assert rel_rms_err(y, ref_bf16) < TOL_FP32_ACC
+
+
+def test_block_forward_in_place_and_workspace_check(ops):
+    C, heads, grid = 128, 2, (2, 8, 8)
+    p = bo.init_block_params(C, seed=9)
+    w = device_block_weights(p, "cuda")
+    x = torch.randn(1, 128, C, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    y = ops.block_forward(x, w, grid=grid, num_heads=heads, kernel=(1, 3, 3), rope_cos=None,
+                          rope_sin=None)
+    y2 = ops.block_forward(x.clone(), w, grid=grid, num_heads=heads, kernel=(1, 3, 3),
+                           rope_cos=None, rope_sin=None, out=None)
+    assert torch.equal(y, y2)                  # deterministic
+    xin = x.clone()
+    ops.block_forward(xin, w, grid=grid, num_heads=heads, kernel=(1, 3, 3), rope_cos=None,
+                      rope_sin=None, out=xin)
+    assert torch.equal(xin, y)                 # y may alias x
+    with pytest.raises(ValueError):
+        ops.block_forward(x, w, grid=grid, num_heads=heads, kernel=(1, 3, 3), rope_cos=None,
+                          rope_sin=None, workspace=torch.empty(1024, dtype=torch.uint8, device="cuda"))
