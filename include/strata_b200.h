@@ -28,6 +28,7 @@ extern "C" {
 #define STRATA_ERR_ARG (-1)         /* invalid shape / pointer / alignment */
 #define STRATA_ERR_UNSUPPORTED (-2) /* configuration this build has no kernel for */
 #define STRATA_ERR_NO_DEVICE (-3)   /* no sm_100 device current */
+#define STRATA_ERR_SCRATCH_LIMIT (-4) /* problem needs more than the built-in scratch array holds */
 #define STRATA_ERR_TENSORMAP (-20)  /* cuTensorMapEncodeTiled refused the operand layout */
 /* <= -1000: -(cudaError_t) - 1000 from a launch or runtime call */
 
@@ -120,6 +121,43 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
                               const strata_block_weights* h_weights, const float* rope_cos,
                               const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Size in bytes of the scratch array built into the library for
+ * strata_block_forward_static_scratch_bf16. */
+#define STRATA_STATIC_SCRATCH_BYTES (64ll * 1024 * 1024)
+
+/* Same computation and same arguments as strata_block_forward_bf16, except that the caller
+ * passes no workspace: the scratch lives in a 64 MiB array that is part of the library image.
+ * (This entry point has no counterpart in the reference; it is an addition of this library.)
+ *
+ * Who it is for: code that must run the block but is not in a position to obtain device
+ * memory of its own - a plugin called from inside someone else's inference loop with a fixed
+ * memory budget, a host whose allocator must not be touched while a latency-critical section
+ * or another library's memory pool is active, or an embedder that is handed input and output
+ * buffers and nothing else. Such callers cannot call cudaMalloc (or have torch do it), so the
+ * ordinary entry point, which wants a caller-allocated workspace, is closed to them.
+ *
+ * Contract
+ *   - Allocates nothing: no cudaMalloc/cudaFree, no allocating library call. Inputs, outputs,
+ *     weights and RoPE tables are still the caller's buffers.
+ *   - Limit: strata_block_workspace_bytes(M, C, hidden) must not exceed
+ *     STRATA_STATIC_SCRATCH_BYTES (e.g. 26 214 tokens at C=128, hidden=512); larger problems
+ *     are refused with STRATA_ERR_SCRATCH_LIMIT before anything is launched.
+ *   - Cost: every GPU on which the library is loaded keeps the 64 MiB array until the
+ *     process exits, whether or not this entry point is ever called.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current). Make that first call outside any stream capture.
+ *   - All calls on a device share the one array. It keeps whatever the previous call left in
+ *     it; nothing in it has to start at zero because every scratch buffer is fully written
+ *     before it is read. Two calls whose kernels can overlap on the GPU (different streams
+ *     without an ordering between them, or different host threads) race on the array and
+ *     corrupt each other: serialise them. */
+int strata_block_forward_static_scratch_bf16(const void* x, void* y, int n_tiles, int D, int H,
+                                             int W, int C, int heads, int hidden, int kd, int kh,
+                                             int kw, const strata_block_weights* h_weights,
+                                             const float* rope_cos, const float* rope_sin,
+                                             int qk_norm, float ln_eps, float qk_eps,
+                                             void* stream);
 
 #ifdef __cplusplus
 }

@@ -43,6 +43,9 @@ _SIGNATURES = {
                                           c_int, c_int, c_int, c_int, c_int, POINTER(BlockWeights),
                                           c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
                                           c_int64, c_void_p]),
+    "strata_block_forward_static_scratch_bf16": (c_int, [
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+        POINTER(BlockWeights), c_void_p, c_void_p, c_int, c_float, c_float, c_void_p]),
 }
 
 

@@ -43,6 +43,9 @@ const char* strata_error_string(int code) {
     case STRATA_ERR_ARG: return "invalid argument (shape, pointer or alignment)";
     case STRATA_ERR_UNSUPPORTED: return "unsupported configuration";
     case STRATA_ERR_NO_DEVICE: return "no sm_100 CUDA device is current";
+    case STRATA_ERR_SCRATCH_LIMIT:
+      return "problem too large for the library's built-in 64 MiB scratch array; use the entry "
+             "point that takes a caller-provided workspace";
     case STRATA_ERR_TENSORMAP:
     case -21: return "TMA tensor map could not be encoded for this operand layout";
     default: break;
@@ -234,3 +237,40 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of the block forward: its scratch is this file-scope device array.
+// In host code the name below is only a handle for the runtime (not a device address); the
+// address kernels can use is obtained once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[STRATA_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" int strata_block_forward_static_scratch_bf16(
+    const void* x, void* y, int n_tiles, int D, int H, int W, int C, int heads, int hidden, int kd,
+    int kh, int kw, const strata_block_weights* wts, const float* rope_cos, const float* rope_sin,
+    int qk_norm, float ln_eps, float qk_eps, void* stream) {
+  if (n_tiles < 0 || D <= 0 || H <= 0 || W <= 0 || C <= 0 || hidden <= 0) return STRATA_ERR_ARG;
+  const int64_t M = static_cast<int64_t>(n_tiles) * D * H * W;
+  const int64_t need = strata_block_workspace_bytes(M, C, hidden);
+  if (need < 0) return STRATA_ERR_ARG;
+  if (need > STRATA_STATIC_SCRATCH_BYTES) return STRATA_ERR_SCRATCH_LIMIT;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+  if (dev < 0 || dev >= kMaxDevices) return STRATA_ERR_NO_DEVICE;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // One-time set-up for this device (which is current): resolve the array's device address.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    if (p == nullptr) return STRATA_ERR_NO_DEVICE;
+    g_static_scratch_addr[dev] = p;
+  }
+  return strata_block_forward_bf16(x, y, n_tiles, D, H, W, C, heads, hidden, kd, kh, kw, wts,
+                                   rope_cos, rope_sin, qk_norm, ln_eps, qk_eps,
+                                   g_static_scratch_addr[dev], STRATA_STATIC_SCRATCH_BYTES, stream);
+}
