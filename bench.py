@@ -222,6 +222,15 @@ def run_gpu_arm(args):
             ms = float(t.item())
         return ms
 
+    if args.only:
+        # profiling aid: run one kernel of the block alone on the bench workload
+        res = kernel_breakdown(torch, ops, x, weights, cos, sin, (D, H, W), heads, kernel, hidden,
+                               iters=args.steps, only=args.only)
+        if rank == 0:
+            print(json.dumps({"only": args.only, "result": [
+                {k: v for k, v in r.items() if k in ("name", "ms", "frac", "bound")} for r in res]}))
+        return
+
     warm = max(args.warmup, 3)
     for _ in range(warm):
         step(x, y)
@@ -282,7 +291,8 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidden, iters=5):
+def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidden, iters=5,
+                     only=None):
     """Times each kernel of the block alone (CUDA events on the launching stream) and attaches
     its algorithmic flops / bytes and roofline fraction."""
     tf_peak, hbm_peak, _ = measured_peaks()
@@ -315,6 +325,8 @@ def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidd
     ]
     out = []
     for name, fn, bound, flop, nbytes in items:
+        if only is not None and name != only:
+            continue
         fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -337,6 +349,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="strata_b200", choices=["strata_b200", "reference"])
+    ap.add_argument("--only", default=None,
+                    help="run a single kernel of the block (name as in the 'kernels' list) "
+                         "--steps times and print its time; used for ncu captures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
