@@ -1,0 +1,262 @@
+"""Cubed-sphere tile decomposition and halo index maps (host side, numpy / torch).
+
+`TileTopology` keeps the reference's interface (screamcast/distributed_halo.py:57-205):
+tiles enumerate product(face, ti, tj) and rank r owns the contiguous slice
+[r * tiles_per_rank, (r + 1) * tiles_per_rank).
+
+The halo of a tile is built by COPY from the neighbouring tile or face — the index logic of the
+reference's face padding (screamcast/cubesphere_transforms.py:149-445): edge strips of the
+neighbouring face re-oriented into this face's frame, and corner blocks filled by the diagonal
+rule. Here that logic is compiled once into gather maps (`halo_source_maps`): for every cell of
+every padded local tile, the id of the interior cell it copies (and, on a corner diagonal, the
+second cell it averages with). The GPU gather kernel then applies face-edge rotation and
+corner rule by following the map, reading the source cell from local or peer memory.
+
+Conventions (as in the reference): arrays are [row i, col j]; "bottom" = first rows, "top" =
+last rows, "left" = first columns, "right" = last columns; face layout
+    | 5 |
+    | 0 | 1 | 2 | 3 |
+    | 4 |
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+Tile = tuple  # (face, tile_i, tile_j)
+
+# FACE_LINKS[face][side] = (neighbour face, neighbour's edge that touches this side)
+FACE_LINKS = (
+    {"top": (5, "bottom"), "right": (1, "left"), "bottom": (4, "top"), "left": (3, "right")},
+    {"top": (5, "right"), "right": (2, "left"), "bottom": (4, "right"), "left": (0, "right")},
+    {"top": (5, "top"), "right": (3, "left"), "bottom": (4, "bottom"), "left": (1, "right")},
+    {"top": (5, "left"), "right": (0, "left"), "bottom": (4, "left"), "left": (2, "right")},
+    {"top": (0, "bottom"), "right": (1, "bottom"), "bottom": (2, "bottom"), "left": (3, "bottom")},
+    {"top": (2, "top"), "right": (1, "top"), "bottom": (0, "top"), "left": (3, "top")},
+)
+
+
+@dataclass(frozen=True)
+class TileTopology:
+    """Distributed cubed-sphere tile decomposition (same fields and methods as the reference)."""
+
+    world_size: int
+    rank: int
+    face_size: int
+    tile_size: int
+    halo_width: int
+    n_faces: int = 6
+
+    def __post_init__(self) -> None:
+        if self.face_size % self.tile_size != 0:
+            raise ValueError(
+                f"face_size={self.face_size} must be divisible by tile_size={self.tile_size}")
+        if self.total_tiles % self.world_size != 0:
+            raise ValueError(f"Number of tiles ({self.total_tiles}) must be divisible by "
+                             f"world_size ({self.world_size})")
+
+    @property
+    def tiles_per_dim(self) -> int:
+        return self.face_size // self.tile_size
+
+    @property
+    def total_tiles(self) -> int:
+        return self.n_faces * self.tiles_per_dim * self.tiles_per_dim
+
+    @property
+    def tiles_per_rank(self) -> int:
+        return self.total_tiles // self.world_size
+
+    @property
+    def padded_tile_size(self) -> int:
+        return self.tile_size + 2 * self.halo_width
+
+    @property
+    def global_tiles(self) -> list:
+        return list(itertools.product(range(self.n_faces), range(self.tiles_per_dim),
+                                      range(self.tiles_per_dim)))
+
+    @property
+    def local_tiles(self) -> list:
+        start = self.rank * self.tiles_per_rank
+        return self.global_tiles[start:start + self.tiles_per_rank]
+
+    def interior_origin(self, tile: Tile) -> tuple:
+        _, ti, tj = tile
+        return ti * self.tile_size, tj * self.tile_size
+
+    def _tile_coords(self, coords: dict, size: int) -> dict:
+        out = dict(coords)
+        out["face"] = np.arange(len(self.local_tiles))
+        out["x"] = np.arange(size)
+        out["y"] = np.arange(size)
+        return out
+
+    def interior_coords(self, base_coords: dict, *, time=None) -> dict:
+        coords = dict(base_coords)
+        if time is not None:
+            coords["time"] = time
+        return self._tile_coords(coords, self.tile_size)
+
+    def pad_coords(self, coords: dict) -> dict:
+        return self._tile_coords(coords, self.padded_tile_size)
+
+    def crop_coords(self, coords: dict) -> dict:
+        return self._tile_coords(coords, self.tile_size)
+
+    def crop(self, x):
+        h = self.halo_width
+        return x if h == 0 else x[..., h:-h, h:-h]
+
+    def faces_to_local_tiles(self, x: torch.Tensor) -> torch.Tensor:
+        """(..., n_faces, N, N) -> (..., tiles_per_rank, T, T); no communication."""
+        ts = self.tile_size
+        return torch.stack([x[..., f, ti * ts:(ti + 1) * ts, tj * ts:(tj + 1) * ts]
+                            for f, ti, tj in self.local_tiles], dim=-3)
+
+    def gather_tiles_to_faces(self, x: torch.Tensor) -> torch.Tensor:
+        """All-gather local interior tiles (..., tiles_per_rank, T, T) into (..., 6, N, N)."""
+        *lead, tpr, nx, ny = x.shape
+        if tpr != self.tiles_per_rank:
+            raise ValueError(f"Expected {self.tiles_per_rank} local tiles, got {tpr}")
+        if nx != self.tile_size or ny != self.tile_size:
+            raise ValueError(f"Expected interior tile shape ({self.tile_size}, {self.tile_size}), "
+                             f"got ({nx}, {ny})")
+        if self.world_size == 1:
+            gathered = x
+        else:
+            parts = [torch.zeros_like(x) for _ in range(self.world_size)]
+            torch.distributed.all_gather(parts, x.contiguous())
+            gathered = torch.cat(parts, dim=-3)
+        out = gathered.new_zeros(*lead, self.n_faces, self.face_size, self.face_size)
+        ts = self.tile_size
+        for g, (f, ti, tj) in enumerate(self.global_tiles):
+            out[..., f, ti * ts:(ti + 1) * ts, tj * ts:(tj + 1) * ts] = gathered[..., g, :, :]
+        return out
+
+
+# --------------------------------------------------------------------------- halo maps
+def _edge_source(face: int, side: str, depth: np.ndarray, along: np.ndarray, N: int):
+    """Source cell (face', i', j') of the halo cells beyond `side` of `face`.
+
+    depth: distance outwards from the edge (0 = the halo line touching the face);
+    along: position along the edge in this face's own row/column direction.
+    The copied cell sits at the same depth INSIDE the neighbouring face; its position along
+    the neighbour's edge runs the same or the opposite way depending on the two sides.
+    """
+    nb, nb_edge = FACE_LINKS[face][side]
+    # position along the strip once it is laid out the canonical way
+    canon = along if side in ("top", "left") else N - 1 - along
+    u = canon if nb_edge in ("bottom", "right") else N - 1 - canon
+    if nb_edge == "bottom":
+        i, j = depth, u
+    elif nb_edge == "top":
+        i, j = N - 1 - depth, u
+    elif nb_edge == "left":
+        i, j = u, depth
+    else:  # right
+        i, j = u, N - 1 - depth
+    return np.full_like(i, nb), i, j
+
+
+def face_halo_sources(N: int, p: int):
+    """Sources of every cell of the 6 padded faces.
+
+    Returns (src_a, src_b), int64 arrays [6, N+2p, N+2p] of flat ids f*N*N + i*N + j into the
+    unpadded faces. src_b is -1 except on corner diagonals, where the cell is the mean of the
+    two sources.
+    """
+    S = N + 2 * p
+    I, J = np.meshgrid(np.arange(S), np.arange(S), indexing="ij")
+    src_a = np.full((6, S, S), -1, dtype=np.int64)
+    src_b = np.full((6, S, S), -1, dtype=np.int64)
+    inside_i = (I >= p) & (I < p + N)
+    inside_j = (J >= p) & (J < p + N)
+
+    def flat(f, i, j):
+        return f * N * N + i * N + j
+
+    for face in range(6):
+        a = src_a[face]
+        m = inside_i & inside_j
+        a[m] = flat(face, I[m] - p, J[m] - p)
+        regions = {
+            "bottom": ((I < p) & inside_j, lambda: (p - 1 - I, J - p)),
+            "top": ((I >= p + N) & inside_j, lambda: (I - (p + N), J - p)),
+            "left": (inside_i & (J < p), lambda: (p - 1 - J, I - p)),
+            "right": (inside_i & (J >= p + N), lambda: (J - (p + N), I - p)),
+        }
+        for side, (mask, da) in regions.items():
+            depth, along = da()
+            f2, i2, j2 = _edge_source(face, side, depth[mask], along[mask], N)
+            a[mask] = flat(f2, i2, j2)
+    if p == 0:
+        return src_a, src_b
+    # Corner blocks: each cell looks sideways to the vertical-strip neighbour in its own row
+    # (column `vcol` of the bottom/top halo) and up/down to the horizontal-strip neighbour in its
+    # own column (row `hrow` of the left/right halo); which of the two it copies is decided by
+    # the side of the block's diagonal it lies on, the diagonal itself takes their mean.
+    lo, hi = p, p + N - 1
+    li = np.arange(p)[:, None]
+    lj = np.arange(p)[None, :]
+    main_upper, main_lower = li < lj, li > lj
+    anti_upper, anti_lower = (li + lj) < (p - 1), (li + lj) > (p - 1)
+    corner_specs = (
+        (0, 0, lo, lo, main_upper, main_lower),            # bottom-left
+        (0, p + N, hi, lo, anti_upper, anti_lower),        # bottom-right
+        (p + N, 0, lo, hi, anti_lower, anti_upper),        # top-left
+        (p + N, p + N, hi, hi, main_lower, main_upper),    # top-right
+    )
+    for face in range(6):
+        edges = src_a[face].copy()
+        for r0, c0, vcol, hrow, take_v, take_h in corner_specs:
+            v = np.broadcast_to(edges[r0:r0 + p, vcol:vcol + 1], (p, p))
+            h = np.broadcast_to(edges[hrow:hrow + 1, c0:c0 + p], (p, p))
+            diag = ~(take_v | take_h)
+            src_a[face, r0:r0 + p, c0:c0 + p] = np.where(take_h, h, v)
+            src_b[face, r0:r0 + p, c0:c0 + p] = np.where(diag, h, -1)
+    return src_a, src_b
+
+
+def halo_source_maps(topo: TileTopology):
+    """Gather maps for this rank's padded tiles.
+
+    Returns (src_a, src_b): int32 arrays [tiles_per_rank, P, P] (P = padded tile size) of
+    GLOBAL cell ids  g * T*T + i*T + j  where g indexes `global_tiles` (so the owning rank is
+    id // (tiles_per_rank*T*T) and the offset inside that rank's buffer is the remainder).
+    src_b = -1 except where the cell is the mean of two sources.
+    """
+    N, T, h = topo.face_size, topo.tile_size, topo.halo_width
+    tpd = topo.tiles_per_dim
+    fa, fb = face_halo_sources(N, h)
+
+    def to_tile_ids(ids):
+        f, rem = np.divmod(ids, N * N)
+        i, j = np.divmod(rem, N)
+        g = f * tpd * tpd + (i // T) * tpd + (j // T)
+        out = g * T * T + (i % T) * T + (j % T)
+        return np.where(ids < 0, -1, out)
+
+    P = T + 2 * h
+    a = np.empty((topo.tiles_per_rank, P, P), dtype=np.int64)
+    b = np.empty_like(a)
+    for n, (f, ti, tj) in enumerate(topo.local_tiles):
+        sl = (f, slice(ti * T, ti * T + P), slice(tj * T, tj * T + P))
+        a[n] = to_tile_ids(fa[sl])
+        b[n] = to_tile_ids(fb[sl])
+    if topo.total_tiles * T * T >= 2 ** 31:
+        raise ValueError("grid too large for 32-bit cell ids")
+    return a.astype(np.int32), b.astype(np.int32)
+
+
+def apply_maps_numpy(all_tiles: np.ndarray, src_a: np.ndarray, src_b: np.ndarray) -> np.ndarray:
+    """Host evaluation of the maps (used by tests and set-up code, e.g. to pad lat/lon grids):
+    all_tiles (..., total_tiles, T, T) in global order -> (..., tiles_per_rank, P, P)."""
+    lead = all_tiles.shape[:-3]
+    flat = all_tiles.reshape(*lead, -1)
+    va = flat[..., src_a]
+    vb = flat[..., np.where(src_b < 0, 0, src_b)]
+    return np.where(src_b < 0, va, (va + vb) / 2).astype(all_tiles.dtype)

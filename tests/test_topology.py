@@ -1,0 +1,93 @@
+"""Host-side tile topology and halo gather maps of the product, against the pinned oracle and
+the golden fixtures produced by the reference. Bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import halo_oracle as ho
+from strata_b200 import topology as tp
+from tests.golden.make_golden import payload
+
+
+def test_known_answer_partition():
+    t = tp.TileTopology(world_size=4, rank=1, face_size=8, tile_size=4, halo_width=2)
+    assert (t.tiles_per_dim, t.total_tiles, t.tiles_per_rank, t.padded_tile_size) == (2, 24, 6, 8)
+    assert t.local_tiles == [(1, 1, 0), (1, 1, 1), (2, 0, 0), (2, 0, 1), (2, 1, 0), (2, 1, 1)]
+    assert t.interior_origin((2, 1, 0)) == (4, 0)
+
+
+def test_invalid_sizes_raise():
+    with pytest.raises(ValueError, match="divisible by tile_size"):
+        tp.TileTopology(1, 0, 10, 4, 1)
+    with pytest.raises(ValueError, match="divisible by"):
+        tp.TileTopology(5, 0, 8, 4, 1)
+
+
+def test_coord_helpers():
+    t = tp.TileTopology(world_size=1, rank=0, face_size=4, tile_size=2, halo_width=1)
+    base = {"variable": np.array(["A", "B"]), "lead_time": np.array([0])}
+    c = t.interior_coords(base, time=np.array([np.datetime64("2020-01-01")]))
+    assert list(c) == ["variable", "lead_time", "time", "face", "x", "y"]
+    assert len(c["face"]) == 24 and len(c["x"]) == 2
+    assert len(t.pad_coords(c)["x"]) == 4 and len(t.crop_coords(t.pad_coords(c))["y"]) == 2
+
+
+def test_fixtures_from_reference(golden_dir):
+    g = np.load(golden_dir / "tile_topology.npz")
+    for ci, (ws, rk, fs, ts, hw) in enumerate(g["cases"].tolist()):
+        t = tp.TileTopology(ws, rk, fs, ts, hw)
+        assert np.array_equal(np.array(t.local_tiles), g[f"c{ci}_local_tiles"])
+        x = payload(2, fs, 10 + ci)
+        lt = t.faces_to_local_tiles(torch.from_numpy(x)).numpy()
+        assert np.array_equal(lt, g[f"c{ci}_local_from_faces"])
+        full = tp.TileTopology(1, 0, fs, ts, hw)
+        all_tiles = full.faces_to_local_tiles(torch.from_numpy(x)).numpy()
+        a, b = tp.halo_source_maps(t)
+        got = tp.apply_maps_numpy(all_tiles, a, b)
+        assert np.array_equal(got, g[f"c{ci}_padded_local_tiles"])     # reference output
+        assert np.array_equal(t.crop(got), g[f"c{ci}_cropped"])
+
+
+@pytest.mark.parametrize("N,p", [(4, 2), (8, 3), (6, 1), (8, 8), (5, 0)])
+def test_face_maps_match_reference_padding(golden_dir, N, p):
+    a, b = tp.face_halo_sources(N, p)
+    x = payload(3, N, 99)
+    flat = x.reshape(3, -1)
+    got = np.where(b < 0, flat[:, a], (flat[:, a] + flat[:, np.where(b < 0, 0, b)]) / 2)
+    want = ho.create_padded_faces(x, p)
+    assert np.array_equal(got.astype(np.float32), want)
+    # coverage: every padded cell has a source; interior maps to itself
+    assert (a >= 0).all()
+    if p:
+        assert (b >= 0).sum() == 6 * 4 * p          # one diagonal of length p per corner
+
+
+@pytest.mark.parametrize("world,fs,ts,hw", [(1, 8, 4, 2), (2, 8, 4, 4), (8, 16, 4, 3), (24, 8, 4, 1),
+                                            (6, 12, 4, 6)])
+def test_tile_maps_all_ranks(world, fs, ts, hw):
+    x = payload(2, fs, 5)
+    full_o = ho.TileTopology(1, 0, fs, ts, hw)
+    all_tiles = full_o.faces_to_local_tiles(x)
+    seen_ranks = set()
+    for rank in range(world):
+        t = tp.TileTopology(world, rank, fs, ts, hw)
+        a, b = tp.halo_source_maps(t)
+        got = tp.apply_maps_numpy(all_tiles, a, b)
+        want = ho.padded_local_tiles(all_tiles, ho.TileTopology(world, rank, fs, ts, hw))
+        assert np.array_equal(got, want)
+        seen_ranks |= set((a // (t.tiles_per_rank * ts * ts)).ravel().tolist())
+    assert seen_ranks <= set(range(world))
+
+
+def test_interior_tile_halo_equals_neighbour_data():
+    # invariant held by the reference's tests (tests/test_distributed_tile_halo.py:249-293):
+    # for a tile strictly inside a face the halo is the neighbouring tiles' data, exactly
+    fs, ts, hw = 16, 4, 2
+    x = payload(1, fs, 3)[0]                     # (6, 16, 16), integer identity payload
+    full = tp.TileTopology(1, 0, fs, ts, hw)
+    all_tiles = full.faces_to_local_tiles(torch.from_numpy(x)).numpy()
+    a, b = tp.halo_source_maps(full)
+    padded = tp.apply_maps_numpy(all_tiles, a, b)
+    g = full.global_tiles.index((2, 1, 2))
+    want = x[2, 1 * ts - hw:2 * ts + hw, 2 * ts - hw:3 * ts + hw]
+    assert np.array_equal(padded[g], want)
