@@ -122,6 +122,47 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
                               const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
                               void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- cubed-sphere tile halo exchange ------------------------------------------------------
+ * Gather maps: int32 arrays over the cells of this rank's padded tiles
+ * [tiles_per_rank, P, P] (P = tile + 2*halo). src_a[c] is the global id of the interior cell
+ * that padded cell c copies; src_b[c] >= 0 marks a corner-diagonal cell that is the mean of
+ * cells src_a[c] and src_b[c]. Cell id = g*T*T + i*T + j, g = index of the tile in the global
+ * tile order product(face, ti, tj); owner rank = id / cells_per_rank with
+ * cells_per_rank = tiles_per_rank*T*T. h_peer_src[r] is the DEVICE pointer through which this
+ * GPU reads rank r's tile buffer (its own buffer for r = me, a peer-mapped pointer otherwise);
+ * the array itself is in HOST memory, world <= 16.
+ * Together they replace the halo padding of screamcast/distributed_halo.py:305-327 (all-gather +
+ * regrid) by the copy / rot90 / diagonal-corner index logic of
+ * screamcast/cubesphere_transforms.py:357-445 applied per tile
+ * (screamcast/distributed_halo.py:451-473), reading only the neighbours' cells. */
+
+/* Token-space halo: buffers [tiles_per_rank, D, T*T, C] bf16 -> out [tiles_per_rank, D, P*P, C].
+ * only_halo != 0 leaves the interior cells of `out` untouched. */
+int strata_halo_gather_tokens_bf16(void* out, const void* const* h_peer_src, int world,
+                                   const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
+                                   int D, int T, int halo, int C, int only_halo, void* stream);
+
+/* Field-space halo (the reference module's interface): buffers [L, tiles_per_rank, T, T] fp32
+ * -> out [L, tiles_per_rank, P, P]; L = product of the leading dims. */
+int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int world,
+                                  const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
+                                  int T, int halo, int64_t L, void* stream);
+
+/* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
+ * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
+ * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work
+ * enqueued before it is visible to the peers' kernels enqueued after their barrier. A timeout
+ * sets device status 105. Every rank must run on its own GPU. */
+int strata_halo_barrier(int* const* h_flags, int me, int world, int epoch, int timeout_ms,
+                        void* stream);
+
+/* Peer-shareable device memory (CUDA IPC). These four calls DO allocate / map memory; use
+ * them at set-up. handle: 64 bytes, exchanged between the processes of one node by any means. */
+int strata_ipc_alloc(int64_t bytes, void** dptr, void* h_handle64);
+int strata_ipc_open(const void* h_handle64, void** dptr);
+int strata_ipc_close(void* dptr);
+int strata_ipc_free(void* dptr);
+
 /* Size in bytes of the scratch array built into the library for
  * strata_block_forward_static_scratch_bf16. */
 #define STRATA_STATIC_SCRATCH_BYTES (64ll * 1024 * 1024)

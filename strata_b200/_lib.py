@@ -43,6 +43,16 @@ _SIGNATURES = {
                                           c_int, c_int, c_int, c_int, c_int, POINTER(BlockWeights),
                                           c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
                                           c_int64, c_void_p]),
+    "strata_halo_gather_tokens_bf16": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                               c_void_p]),
+    "strata_halo_gather_fields_f32": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p,
+                                              c_int, c_int, c_int, c_int64, c_void_p]),
+    "strata_halo_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p]),
+    "strata_ipc_alloc": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
+    "strata_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "strata_ipc_close": (c_int, [c_void_p]),
+    "strata_ipc_free": (c_int, [c_void_p]),
     "strata_block_forward_static_scratch_bf16": (c_int, [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
         POINTER(BlockWeights), c_void_p, c_void_p, c_int, c_float, c_float, c_void_p]),

@@ -2,10 +2,13 @@
 // Single translation unit: the kernels live in the .cuh files included below.
 #include "../../include/strata_b200.h"
 
+#include <string.h>
+
 #include "common.cuh"
 #include "gemm_tcgen05.cuh"
 #include "layernorm.cuh"
 #include "na3d.cuh"
+#include "halo.cuh"
 
 using namespace strata;
 
@@ -234,6 +237,123 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
     return r;
   return strata_linear_bf16(hbuf, hidden, wts->w_fc2, hidden, wts->b_fc2, y, C, M, C, hidden,
                             STRATA_EPI_RESIDUAL, x1, C, stream);
+}
+
+int strata_halo_gather_tokens_bf16(void* out, const void* const* h_peer_src, int world,
+                                   const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
+                                   int D, int T, int halo, int C, int only_halo, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!out || !h_peer_src || !src_a || !src_b) return STRATA_ERR_ARG;
+  if (world < 1 || world > HALO_MAX_RANKS) return STRATA_ERR_UNSUPPORTED;
+  if (tiles_per_rank <= 0 || D <= 0 || T <= 0 || halo < 0 || C <= 0 || C % 8 != 0)
+    return STRATA_ERR_ARG;
+  if (!aligned16(out)) return STRATA_ERR_ARG;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_src[r] || !aligned16(h_peer_src[r])) return STRATA_ERR_ARG;
+    pp.p[r] = h_peer_src[r];
+  }
+  const int P = T + 2 * halo;
+  const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
+  if (cells * world > 0x7fffffffLL) return STRATA_ERR_ARG;
+  const long long work = static_cast<long long>(P) * P * (C / 8);
+  long long bx = (work + 255) / 256;
+  const long long cap = static_cast<long long>(sms) * 8;
+  if (bx > cap) bx = cap;
+  dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(tiles_per_rank * D));
+  if (static_cast<long long>(tiles_per_rank) * D > 65535) return STRATA_ERR_UNSUPPORTED;
+  halo_gather_tokens_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      static_cast<__nv_bfloat16*>(out), pp, src_a, src_b, P * P, T * T, D, C,
+      static_cast<int>(cells), only_halo, halo, halo + T, P);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int world,
+                                  const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
+                                  int T, int halo, int64_t L, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!out || !h_peer_src || !src_a || !src_b) return STRATA_ERR_ARG;
+  if (world < 1 || world > HALO_MAX_RANKS) return STRATA_ERR_UNSUPPORTED;
+  if (tiles_per_rank <= 0 || T <= 0 || halo < 0 || L < 0) return STRATA_ERR_ARG;
+  if (L == 0) return STRATA_OK;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_src[r]) return STRATA_ERR_ARG;
+    pp.p[r] = h_peer_src[r];
+  }
+  const int P = T + 2 * halo;
+  const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
+  const long long ocells = static_cast<long long>(tiles_per_rank) * P * P;
+  if (cells * world > 0x7fffffffLL || ocells > 0x7fffffffLL || L > 0x7fffffffLL)
+    return STRATA_ERR_ARG;
+  long long bx = (ocells + 255) / 256;
+  if (bx > 4096) bx = 4096;
+  long long by = L;
+  const long long want = static_cast<long long>(sms) * 16;  // enough CTAs for two waves
+  if (bx * by > want) by = (want + bx - 1) / bx;
+  if (by < 1) by = 1;
+  if (by > 65535) by = 65535;
+  dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(by));
+  halo_gather_fields_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      out, pp, src_a, src_b, static_cast<int>(ocells), static_cast<int>(cells),
+      static_cast<int>(L));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_halo_barrier(int* const* h_flags, int me, int world, int epoch, int timeout_ms,
+                        void* stream) {
+  if (!h_flags || world < 1 || world > HALO_MAX_RANKS || me < 0 || me >= world)
+    return STRATA_ERR_ARG;
+  FlagPtrs fp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_flags[r]) return STRATA_ERR_ARG;
+    fp.p[r] = h_flags[r];
+  }
+  if (timeout_ms <= 0) timeout_ms = 2000;
+  const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;  // ~2 GHz
+  halo_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(fp, me, world, epoch, limit);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_ipc_alloc(int64_t bytes, void** dptr, void* h_handle64) {
+  if (bytes <= 0 || !dptr || !h_handle64) return STRATA_ERR_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+  e = cudaMemset(p, 0, static_cast<size_t>(bytes));
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(h_handle64), p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return -static_cast<int>(e) - 1000;
+  }
+  *dptr = p;
+  return STRATA_OK;
+}
+
+int strata_ipc_open(const void* h_handle64, void** dptr) {
+  if (!h_handle64 || !dptr) return STRATA_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, h_handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_ipc_close(void* dptr) {
+  if (!dptr) return STRATA_ERR_ARG;
+  cudaError_t e = cudaIpcCloseMemHandle(dptr);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_ipc_free(void* dptr) {
+  if (!dptr) return STRATA_ERR_ARG;
+  cudaError_t e = cudaFree(dptr);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
 }  // extern "C"

@@ -1,0 +1,129 @@
+// Cubed-sphere tile halo exchange: gather kernels and the cross-GPU flag barrier.
+//
+// A padded tile is assembled by GATHER: for every cell of every padded local tile a
+// precomputed map names the interior cell it copies (src_a) and, on a corner diagonal, a
+// second cell it is averaged with (src_b >= 0). A cell id is  g*T*T + i*T + j  with g the
+// tile's position in the global tile order; id / cells_per_rank is the owning rank and the
+// remainder the cell's offset inside that rank's tile buffer, so the source may sit in this
+// GPU's memory or in a peer's (plain loads over NVLink through a peer-mapped pointer; no TMA,
+// no multicast). Face-edge rotation and the corner rule are entirely in the map, so the
+// kernel's result is bit-identical to applying the same index logic on the host.
+//
+// Mean of two cells: (a + b) / 2 evaluated in the storage type's own arithmetic (fp32: one
+// add, one halving; bf16: the sum is rounded to bf16, then halved - what a bf16 tensor
+// expression produces).
+//
+// HBM-bound (remote part: NVLink-bound): payload bytes read once and written once.
+#pragma once
+#include "common.cuh"
+
+namespace strata {
+
+constexpr int HALO_MAX_RANKS = 16;
+struct PeerPtrs {
+  const void* p[HALO_MAX_RANKS];
+};
+struct FlagPtrs {
+  int* p[HALO_MAX_RANKS];
+};
+
+// Token layout: source buffers [tiles_per_rank, D, T*T, C] bf16, output [tiles_per_rank, D, P*P, C].
+// grid: x over (padded cell, 16-byte vector) pairs, y over (tile, depth).
+__global__ void __launch_bounds__(256)
+halo_gather_tokens_kernel(__nv_bfloat16* __restrict__ out, const PeerPtrs src,
+                          const int* __restrict__ src_a, const int* __restrict__ src_b, int PP,
+                          int TT, int D, int C, int cells_per_rank, int only_halo,
+                          int halo_lo, int halo_hi, int P) {
+  const int vpc = C >> 3;  // 16-byte vectors per cell
+  const int tile = blockIdx.y / D;
+  const int d = blockIdx.y - tile * D;
+  const long long total = static_cast<long long>(PP) * vpc;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pc = static_cast<int>(idx / vpc);
+    const int v = static_cast<int>(idx - static_cast<long long>(pc) * vpc);
+    if (only_halo) {
+      const int pi = pc / P, pj = pc - pi * P;
+      if (pi >= halo_lo && pi < halo_hi && pj >= halo_lo && pj < halo_hi) continue;
+    }
+    const int a = __ldg(src_a + tile * PP + pc);
+    const int b = __ldg(src_b + tile * PP + pc);
+    auto load = [&](int id) {
+      const int rank = id / cells_per_rank;
+      const int local = id - rank * cells_per_rank;
+      const int st = local / TT;
+      const int sc = local - st * TT;
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(src.p[rank]);
+      const long long off = ((static_cast<long long>(st) * D + d) * TT + sc) * C + (v << 3);
+      return *reinterpret_cast<const uint4*>(base + off);
+    };
+    uint4 r = load(a);
+    if (b >= 0) {
+      const uint4 s = load(b);
+      uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+      const uint32_t* sw = reinterpret_cast<const uint32_t*>(&s);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        // sum rounded to bf16 first, then halved (exact)
+        const float lo = __bfloat162float(__float2bfloat16(bf16_lo(rw[t]) + bf16_lo(sw[t]))) * 0.5f;
+        const float hi = __bfloat162float(__float2bfloat16(bf16_hi(rw[t]) + bf16_hi(sw[t]))) * 0.5f;
+        rw[t] = pack_bf16(lo, hi);
+      }
+    }
+    const long long ooff = ((static_cast<long long>(tile) * D + d) * PP + pc) * C + (v << 3);
+    *reinterpret_cast<uint4*>(out + ooff) = r;
+  }
+}
+
+// Field layout: source buffers [L, tiles_per_rank*T*T] fp32 (L = product of leading dims),
+// output [L, tiles_per_rank*P*P]. grid: x over padded cells, y over leading index.
+__global__ void __launch_bounds__(256)
+halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
+                          const int* __restrict__ src_a, const int* __restrict__ src_b,
+                          int n_out_cells, int cells_per_rank, int L) {
+  for (int oc = blockIdx.x * blockDim.x + threadIdx.x; oc < n_out_cells;
+       oc += gridDim.x * blockDim.x) {
+    const int a = __ldg(src_a + oc);
+    const int b = __ldg(src_b + oc);
+    const int ra = a / cells_per_rank, la = a - ra * cells_per_rank;
+    const float* pa = static_cast<const float*>(src.p[ra]) + la;
+    const float* pb = nullptr;
+    if (b >= 0) {
+      const int rb = b / cells_per_rank, lb = b - rb * cells_per_rank;
+      pb = static_cast<const float*>(src.p[rb]) + lb;
+    }
+    for (int l = blockIdx.y; l < L; l += gridDim.y) {
+      const long long so = static_cast<long long>(l) * cells_per_rank;
+      float v = pa[so];
+      if (pb) v = (v + pb[so]) / 2.0f;
+      out[static_cast<long long>(l) * n_out_cells + oc] = v;
+    }
+  }
+}
+
+// Cross-GPU barrier on flag words: rank `me` publishes `epoch` into slot [me] of every
+// rank's flag array (release, system scope), then waits until every slot of its own array has
+// reached `epoch` (acquire). One thread per peer. The wait is bounded; on expiry the status
+// word records ST_TIMEOUT_PEER_FLAG and the kernel returns.
+__global__ void halo_barrier_kernel(const FlagPtrs flags, int me, int world, int epoch,
+                                    long long limit_cycles) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  int* remote = flags.p[r] + me;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const int* mine = flags.p[me] + r;
+  const long long t0 = clock64();
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v >= epoch) break;
+    if (clock64() - t0 > limit_cycles) {
+      atomicCAS(&g_status, 0, ST_TIMEOUT_PEER_FLAG);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+}  // namespace strata

@@ -1,0 +1,244 @@
+"""Tile halo exchange over peer memory (one process per GPU).
+
+`DistributedTileCopyHaloPadding` has the interface of the reference's halo module
+(screamcast/distributed_halo.py:208-327): `forward(x[..., tiles_per_rank, T, T]) ->
+[..., tiles_per_rank, T+2h, T+2h]`, attributes `.topology`, `.lat_deg`, `.lon_deg`, the
+classmethod `from_padded_face_grid(...)`, wrappable per channel chunk, and `topology.crop`
+inverts it. What differs is the mechanism: instead of all-gathering the whole globe to every
+rank and regridding, each rank publishes its tiles in a peer-mapped buffer and every GPU's
+gather kernel reads just the cells its halos need, directly from the owning GPU over NVLink,
+following precomputed copy / rot90 / corner maps (strata_b200/topology.py). Halo values are
+COPIES of neighbour cells (exact inside a face, and the reference's own face-padding rule
+across face edges), not k-nearest-neighbour interpolants.
+
+`pad_tokens` is the same exchange for bf16 token tensors [tiles_per_rank, D, T*T, C] (per
+block, token space).
+
+Synchronisation: a device-side flag barrier on the current stream before the gather (all
+ranks have published) — buffers alternate between two slots, so a rank may publish step n+1
+while a slower peer still reads step n. Waits are bounded; a peer that never arrives shows up
+as device status 105 (`check_status`).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .topology import TileTopology, halo_source_maps
+
+
+class _DevPtrTensorView:
+    """Exposes raw device memory to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerSharedBuffer:
+    """`nbytes` of device memory on every rank, each rank's block mapped into all others.
+
+    ptrs[r] is the pointer through which THIS process reaches rank r's block. Set-up only
+    (allocates, exchanges CUDA IPC handles through torch.distributed).
+    """
+
+    def __init__(self, nbytes: int, group=None):
+        lib = _lib.load()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.nbytes = int(nbytes)
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.strata_ipc_alloc(self.nbytes, ctypes.byref(ptr), handle), "strata_ipc_alloc")
+        self._own = ptr.value
+        self.ptrs = [None] * self.world
+        self.ptrs[self.rank] = self._own
+        self._opened = []
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(lib.strata_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)),
+                           "strata_ipc_open")
+                self.ptrs[r] = p.value
+                self._opened.append(p.value)
+        self.local = torch.as_tensor(_DevPtrTensorView(self._own, self.nbytes),
+                                     device=torch.device("cuda", torch.cuda.current_device()))
+
+    def ptr_array(self, byte_offset: int = 0):
+        arr = (ctypes.c_void_p * self.world)()
+        for r in range(self.world):
+            arr[r] = self.ptrs[r] + byte_offset
+        return arr
+
+    def close(self):
+        lib = _lib.load()
+        if self.world > 1 and dist.is_initialized():
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        for p in self._opened:
+            lib.strata_ipc_close(p)
+        self._opened = []
+        if self._own:
+            self.local = None
+            lib.strata_ipc_free(self._own)
+            self._own = None
+
+
+class DistributedTileCopyHaloPadding(torch.nn.Module):
+    """Materialise halo-padded local tiles from distributed interior tiles by peer copies."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, *, topology: TileTopology, lat_deg: torch.Tensor | None = None,
+                 lon_deg: torch.Tensor | None = None, device=None, group=None,
+                 max_bytes_per_call: int = 0, timeout_ms: int = 2000):
+        super().__init__()
+        self.topology = topology
+        self.group = group
+        self.timeout_ms = int(timeout_ms)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        a, b = halo_source_maps(topology)
+        self.register_buffer("src_a", torch.from_numpy(a).to(dev), persistent=False)
+        self.register_buffer("src_b", torch.from_numpy(b).to(dev), persistent=False)
+        if lat_deg is not None:
+            self.register_buffer("lat_deg", lat_deg, persistent=False)
+            self.register_buffer("lon_deg", lon_deg, persistent=False)
+        self._shared = None
+        self._slot_bytes = 0
+        self._epoch = 0
+        self._max_bytes = int(max_bytes_per_call)
+        if topology.world_size > 1:
+            if not dist.is_initialized():
+                raise RuntimeError("world_size > 1 needs an initialised torch.distributed group")
+            if dist.get_world_size(group) != topology.world_size or dist.get_rank(group) != topology.rank:
+                raise ValueError("topology world_size / rank do not match the process group")
+            if self._max_bytes > 0:
+                self._ensure_shared(self._max_bytes)
+
+    @classmethod
+    def from_padded_face_grid(cls, *, topology: TileTopology, lon: torch.Tensor, lat: torch.Tensor,
+                              pad_width_data: int, device, **kw):
+        """Same arguments as the reference's constructor; lon/lat are padded face grids
+        [6, N + 2*pad, N + 2*pad] (degrees) from which each local tile's padded window is cut."""
+        T, h = topology.tile_size, topology.halo_width
+
+        def cut(g):
+            return torch.stack([g[..., f, pad_width_data + ti * T - h:pad_width_data + (ti + 1) * T + h,
+                                  pad_width_data + tj * T - h:pad_width_data + (tj + 1) * T + h]
+                                for f, ti, tj in topology.local_tiles])
+        return cls(topology=topology, lat_deg=cut(lat).to(device), lon_deg=cut(lon).to(device),
+                   device=device, **kw)
+
+    # ---------------------------------------------------------------- shared buffers
+    def _ensure_shared(self, payload_bytes: int):
+        """(Re)allocate the peer-shared buffer: [flags | slot 0 | slot 1]. Collective."""
+        slot = (payload_bytes + 255) // 256 * 256
+        if self._shared is not None and slot <= self._slot_bytes:
+            return
+        if self._shared is not None:
+            self._shared.close()
+        self._slot_bytes = slot
+        self._shared = PeerSharedBuffer(self.FLAG_BYTES + 2 * slot, group=self.group)
+        self._epoch = 0
+
+    def _publish_and_sync(self, x_flat_bytes: torch.Tensor):
+        """Copy this rank's tiles into the current slot, run the flag barrier; returns the
+        per-rank source pointer array for the gather."""
+        topo = self.topology
+        if topo.world_size == 1:
+            arr = (ctypes.c_void_p * 1)()
+            arr[0] = x_flat_bytes.data_ptr()
+            return arr
+        nbytes = x_flat_bytes.numel()
+        if self._shared is None or nbytes > self._slot_bytes:
+            self._ensure_shared(nbytes)
+        self._epoch += 1
+        off = self.FLAG_BYTES + (self._epoch & 1) * self._slot_bytes
+        self._shared.local[off:off + nbytes].copy_(x_flat_bytes, non_blocking=True)
+        flags = self._shared.ptr_array(0)
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.load().strata_halo_barrier(flags, topo.rank, topo.world_size, self._epoch,
+                                                   self.timeout_ms, stream), "strata_halo_barrier")
+        return self._shared.ptr_array(off)
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a peer never reached a barrier (or any kernel timed out)."""
+        st = _lib.device_status()
+        if st != 0:
+            raise RuntimeError(f"halo exchange failed on the device (status {st}: "
+                               f"{'peer flag wait timed out' if st == 105 else 'kernel wait timed out'})")
+
+    # ---------------------------------------------------------------- field space (reference API)
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        topo = self.topology
+        *shape, tpr, nx, ny = x.shape
+        if tpr != topo.tiles_per_rank:
+            raise ValueError(f"Expected {topo.tiles_per_rank} local tiles, got {tpr}")
+        if nx != topo.tile_size or ny != topo.tile_size:
+            raise ValueError(f"Expected interior tile shape ({topo.tile_size}, {topo.tile_size}), "
+                             f"got ({nx}, {ny})")
+        if not x.is_cuda:
+            raise _lib.StrataLibraryError("halo exchange needs CUDA tensors (no CPU path)")
+        if x.dtype != torch.float32:
+            raise TypeError(f"field-space halo exchange is float32, got {x.dtype}")
+        P = topo.padded_tile_size
+        L = int(np.prod(shape)) if shape else 1
+        xc = x.contiguous()
+        out = torch.empty(*shape, tpr, P, P, dtype=x.dtype, device=x.device)
+        if L == 0:
+            return out
+        with torch.cuda.device(x.device):
+            src = self._publish_and_sync(xc.view(-1).view(torch.uint8))
+            _lib.check(_lib.load().strata_halo_gather_fields_f32(
+                out.data_ptr(), src, topo.world_size, self.src_a.data_ptr(), self.src_b.data_ptr(),
+                tpr, topo.tile_size, topo.halo_width, L,
+                torch.cuda.current_stream().cuda_stream), "strata_halo_gather_fields_f32")
+        return out
+
+    # ---------------------------------------------------------------- token space
+    def pad_tokens(self, tokens: torch.Tensor, depth: int, out: torch.Tensor | None = None,
+                   only_halo: bool = False) -> torch.Tensor:
+        """tokens [tiles_per_rank, depth, T*T, C] bf16 -> [tiles_per_rank, depth, P*P, C]."""
+        topo = self.topology
+        T, P = topo.tile_size, topo.padded_tile_size
+        if tokens.dtype != torch.bfloat16 or not tokens.is_cuda:
+            raise TypeError("pad_tokens expects a CUDA bfloat16 tensor")
+        if tuple(tokens.shape[:3]) != (topo.tiles_per_rank, depth, T * T):
+            raise ValueError(f"expected [{topo.tiles_per_rank}, {depth}, {T * T}, C], "
+                             f"got {tuple(tokens.shape)}")
+        C = tokens.shape[-1]
+        tc = tokens.contiguous()
+        if out is None:
+            if only_halo:
+                raise ValueError("only_halo needs a preallocated `out` holding the interiors")
+            out = torch.empty(topo.tiles_per_rank, depth, P * P, C, dtype=torch.bfloat16,
+                              device=tokens.device)
+        with torch.cuda.device(tokens.device):
+            src = self._publish_and_sync(tc.view(-1).view(torch.uint8))
+            _lib.check(_lib.load().strata_halo_gather_tokens_bf16(
+                out.data_ptr(), src, topo.world_size, self.src_a.data_ptr(), self.src_b.data_ptr(),
+                topo.tiles_per_rank, depth, T, topo.halo_width, C, 1 if only_halo else 0,
+                torch.cuda.current_stream().cuda_stream), "strata_halo_gather_tokens_bf16")
+        return out
+
+    def close(self):
+        if self._shared is not None:
+            self._shared.close()
+            self._shared = None
+
+
+def channel_chunked(fn, chunk: int = 32):
+    """Apply a halo module over channel chunks (the reference's rollout driver wraps its halo
+    exchange the same way: scripts/ace/run_screamcast_nudged.py:119-134)."""
+    def wrapped(x: torch.Tensor) -> torch.Tensor:
+        return torch.cat([fn(x[:, c:c + chunk]) for c in range(0, x.shape[1], chunk)], dim=1)
+    return wrapped

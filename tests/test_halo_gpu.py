@@ -1,0 +1,114 @@
+"""GPU halo gather (world_size 1: every source is local) against the pinned oracle. Bit-exact:
+halo exchange is index logic plus the corner mean in the storage type's arithmetic."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import halo_oracle as ho
+from tests.golden.make_golden import payload
+
+pytestmark = pytest.mark.gpu
+
+
+def _topos(fs, ts, hw):
+    from strata_b200.topology import TileTopology
+    return TileTopology(1, 0, fs, ts, hw), ho.TileTopology(1, 0, fs, ts, hw)
+
+
+@pytest.mark.parametrize("fs,ts,hw,lead", [(8, 4, 2, (3,)), (16, 4, 3, (2, 5)), (8, 8, 8, (1,)),
+                                           (12, 4, 1, ()), (8, 4, 0, (2,))])
+def test_field_halo_bit_exact(fs, ts, hw, lead):
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    t, to = _topos(fs, ts, hw)
+    n_lead = int(np.prod(lead)) if lead else 1
+    x = payload(max(n_lead, 2), fs, 7)[:n_lead]                       # (L, 6, N, N)
+    tiles = to.faces_to_local_tiles(x).reshape(*lead, t.tiles_per_rank, ts, ts)
+    mod = DistributedTileCopyHaloPadding(topology=t)
+    out = mod(torch.from_numpy(np.ascontiguousarray(tiles)).cuda())
+    mod.check_status()
+    want = ho.padded_local_tiles(tiles, to)
+    assert out.shape == want.shape
+    assert np.array_equal(out.cpu().numpy(), want)
+    assert np.array_equal(t.crop(out).cpu().numpy(), tiles)           # crop(pad(x)) == x
+
+
+def test_field_halo_golden_from_reference(golden_dir):
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    from strata_b200.topology import TileTopology
+    g = np.load(golden_dir / "tile_topology.npz")
+    for ci, (ws, rk, fs, ts, hw) in enumerate(g["cases"].tolist()):
+        if ws != 1:
+            continue
+        t = TileTopology(ws, rk, fs, ts, hw)
+        x = payload(2, fs, 10 + ci)
+        tiles = t.faces_to_local_tiles(torch.from_numpy(x)).cuda()
+        out = DistributedTileCopyHaloPadding(topology=t)(tiles)
+        assert np.array_equal(out.cpu().numpy(), g[f"c{ci}_padded_local_tiles"])
+
+
+def test_token_halo_bit_exact_bf16():
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    fs, ts, hw, D, C = 8, 4, 2, 3, 64
+    t, to = _topos(fs, ts, hw)
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randn(t.tiles_per_rank, D, ts * ts, C, generator=g).bfloat16()
+    mod = DistributedTileCopyHaloPadding(topology=t)
+    out = mod.pad_tokens(tok.cuda(), D)
+    mod.check_status()
+    # oracle in bf16 arithmetic: channels/depth become leading dims of the (tile, i, j) layout
+    lead = tok.permute(1, 3, 0, 2).reshape(D, C, t.tiles_per_rank, ts, ts)
+    want = torch.from_numpy(ho.padded_local_tiles(lead.float().numpy(), to))
+    # the corner mean must round like bf16 arithmetic: (a + b) rounded, then halved
+    a, b = mod.src_a.cpu().numpy(), mod.src_b.cpu().numpy()
+    flat = lead.reshape(D, C, -1)
+    va = flat[..., torch.from_numpy(a.astype(np.int64))]
+    vb = flat[..., torch.from_numpy(np.where(b < 0, 0, b).astype(np.int64))]
+    want_bf16 = torch.where(torch.from_numpy(b < 0), va, (va + vb) / 2)        # bf16 tensor math
+    P = t.padded_tile_size
+    got = out.cpu().reshape(t.tiles_per_rank, D, P, P, C).permute(1, 4, 0, 2, 3)
+    assert torch.equal(got, want_bf16)
+    assert (got.float() - want).abs().max() <= 2 ** -7 * want.abs().max()     # and close to fp32
+
+
+def test_token_halo_only_halo_keeps_interior():
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    fs, ts, hw, D, C = 8, 4, 2, 2, 32
+    t, _ = _topos(fs, ts, hw)
+    P = t.padded_tile_size
+    tok = torch.randn(t.tiles_per_rank, D, ts * ts, C, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    mod = DistributedTileCopyHaloPadding(topology=t)
+    full = mod.pad_tokens(tok, D)
+    out = torch.full_like(full, 7.0)
+    mod.pad_tokens(tok, D, out=out, only_halo=True)
+    o5 = out.view(t.tiles_per_rank, D, P, P, C)
+    f5 = full.view(t.tiles_per_rank, D, P, P, C)
+    assert (o5[:, :, hw:-hw, hw:-hw] == 7.0).all()
+    o5[:, :, hw:-hw, hw:-hw] = f5[:, :, hw:-hw, hw:-hw]
+    assert torch.equal(o5, f5)
+
+
+def test_shape_validation():
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    t, _ = _topos(8, 4, 2)
+    mod = DistributedTileCopyHaloPadding(topology=t)
+    with pytest.raises(ValueError, match="local tiles"):
+        mod(torch.zeros(1, 5, 4, 4, device="cuda"))
+    with pytest.raises(ValueError, match="interior tile shape"):
+        mod(torch.zeros(1, 24, 5, 4, device="cuda"))
+
+
+def _two_gpus():
+    return torch.cuda.is_available() and torch.cuda.device_count() >= 2
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs on one node")
+def test_two_rank_peer_halo():
+    import subprocess, sys
+    from pathlib import Path
+    worker = Path(__file__).resolve().parent / "halo_worker.py"
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                        "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
+                        "29531", str(worker)], capture_output=True, text=True, timeout=600,
+                       env={**__import__("os").environ, "NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "HALO WORKER OK" in r.stdout
