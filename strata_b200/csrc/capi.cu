@@ -50,7 +50,9 @@ const char* strata_error_string(int code) {
       return "problem too large for the library's built-in 64 MiB scratch array; use the entry "
              "point that takes a caller-provided workspace";
     case STRATA_ERR_TENSORMAP:
-    case -21: return "TMA tensor map could not be encoded for this operand layout";
+    case -21:
+    case -22:
+    case -23: return "TMA tensor map could not be encoded for this operand layout";
     default: break;
   }
   if (code <= -1000) return cudaGetErrorString(static_cast<cudaError_t>(-(code + 1000)));
@@ -89,7 +91,8 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (M == 0 && N > 0 && K > 0) return STRATA_OK;
   if (!x || !w || !y || M < 0 || N <= 0 || K <= 0) return STRATA_ERR_ARG;
-  if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldx < K || ldw < K || ldy < N)
+  if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldx < K || ldw < K || ldy < N ||
+      ldy % 8 != 0 || (aux && ldaux % 8 != 0))
     return STRATA_ERR_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (bias && !aligned16(bias)))
     return STRATA_ERR_ARG;

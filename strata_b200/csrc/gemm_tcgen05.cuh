@@ -60,98 +60,77 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGING_BYTES = 32 * 64 * 2;             // one 32-row x 64-col bf16 box
+  static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;      // per epilogue warp
+  static constexpr int BAR_OFF = STAGING_OFF + GEMM_EPI_WARPS * STAGING_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TOTAL = BAR_OFF + BAR_BYTES + 1024;      // + alignment slack
 };
 
+// TMA store of a shared-memory box to global memory (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(tm), "r"(src), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// Epilogue math on 32 consecutive columns [n0, n0+32) of output row m, in place. Lane l of
+// the warp holds the bias of column n0+l; `aux` holds the residual / gated operand of the same
+// columns (bf16 pairs) for the epilogues that use one; `qk_scale` is the RMS-norm factor of the
+// head these columns belong to (1 when qk norm is off).
 template <int EPI>
-__device__ __forceinline__ void gemm_epilogue_64(float (&v)[64], int m, int n0, bool row_ok,
-                                                 const GemmParams& p) {
-  // v holds acc for columns [n0, n0+64) of row m. Apply bias + epilogue in place.
+__device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], int m, int n0, bool row_ok,
+                                                 float b_lane, const uint32_t (&aux)[16],
+                                                 float qk_scale, const GemmParams& p) {
   if (p.bias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-      if (n0 + j + 3 < p.N) {
-        float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + n0 + j));
-        v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
-      } else {
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          if (n0 + j + t < p.N) v[j + t] += __ldg(p.bias + n0 + j + t);
-      }
-    }
+    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, j);
   }
   if constexpr (EPI == EPI_GELU) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) v[j] = gelu_tanh(v[j]);
-  } else if constexpr (EPI == EPI_RESIDUAL || EPI == EPI_GATE) {
-    if (row_ok) {
-      const __nv_bfloat16* rp = p.aux + static_cast<long long>(m) * p.ldaux + n0;
-      if (n0 + 64 <= p.N && (p.ldaux % 8) == 0) {
+    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+  } else if constexpr (EPI == EPI_RESIDUAL) {
 #pragma unroll
-        for (int j = 0; j < 64; j += 8) {
-          uint4 r = __ldg(reinterpret_cast<const uint4*>(rp + j));
-          const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    for (int j = 0; j < 16; ++j) {
+      v[2 * j] += bf16_lo(aux[j]);
+      v[2 * j + 1] += bf16_hi(aux[j]);
+    }
+  } else if constexpr (EPI == EPI_GATE) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            float lo = bf16_lo(w[t]), hi = bf16_hi(w[t]);
-            if constexpr (EPI == EPI_RESIDUAL) {
-              v[j + 2 * t] += lo;
-              v[j + 2 * t + 1] += hi;
-            } else {
-              v[j + 2 * t] = lo / (1.0f + __expf(-v[j + 2 * t]));
-              v[j + 2 * t + 1] = hi / (1.0f + __expf(-v[j + 2 * t + 1]));
-            }
-          }
-        }
-      } else {
-        for (int j = 0; j < 64; ++j) {
-          if (n0 + j < p.N) {
-            float r = __bfloat162float(rp[j]);
-            if constexpr (EPI == EPI_RESIDUAL) v[j] += r;
-            else v[j] = r / (1.0f + __expf(-v[j]));
-          }
-        }
-      }
+    for (int j = 0; j < 16; ++j) {
+      v[2 * j] = bf16_lo(aux[j]) / (1.0f + __expf(-v[2 * j]));
+      v[2 * j + 1] = bf16_hi(aux[j]) / (1.0f + __expf(-v[2 * j + 1]));
     }
   } else if constexpr (EPI == EPI_QKV_ROPE) {
     if (n0 < p.rope_cols && row_ok) {
-      const int hd = p.head_dim;  // 32 or 64; 64-column chunks never straddle a head
-      if (p.qk_norm) {
-        if (hd == 64) {
-          float ss = 0.f;
-#pragma unroll
-          for (int j = 0; j < 64; ++j) ss += v[j] * v[j];
-          const float r = rsqrtf(ss * (1.0f / 64.0f) + p.qk_eps);
-#pragma unroll
-          for (int j = 0; j < 64; ++j) v[j] *= r;
-        } else {
-          float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { s0 += v[j] * v[j]; s1 += v[32 + j] * v[32 + j]; }
-          const float r0 = rsqrtf(s0 * (1.0f / 32.0f) + p.qk_eps);
-          const float r1 = rsqrtf(s1 * (1.0f / 32.0f) + p.qk_eps);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { v[j] *= r0; v[32 + j] *= r1; }
-        }
-      }
+      const int hd = p.head_dim;  // 32 or 64
       const int half = hd >> 1;
       const long long trow =
           static_cast<long long>(m / p.tokens_per_tile) * p.hw + (m % p.hw);
-      const float* cp = p.rope_cos + trow * half;
-      const float* sp = p.rope_sin + trow * half;
+      const int pj0 = (n0 % hd) >> 1;  // first pair index of these columns within the head
+      const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + trow * half + pj0);
+      const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + trow * half + pj0);
 #pragma unroll
-      for (int j = 0; j < 64; j += 8) {
-        const int pj = ((n0 + j) % hd) >> 1;  // pair index within the head
-        float4 c = __ldg(reinterpret_cast<const float4*>(cp + pj));
-        float4 s = __ldg(reinterpret_cast<const float4*>(sp + pj));
+      for (int q = 0; q < 4; ++q) {
+        const float4 c = __ldg(cp + q);
+        const float4 s = __ldg(sp + q);
         const float cc[4] = {c.x, c.y, c.z, c.w};
         const float sn[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          float a = v[j + 2 * t], b = v[j + 2 * t + 1];
-          v[j + 2 * t] = a * cc[t] - b * sn[t];
-          v[j + 2 * t + 1] = a * sn[t] + b * cc[t];
+          const float a = v[8 * q + 2 * t] * qk_scale, b = v[8 * q + 2 * t + 1] * qk_scale;
+          v[8 * q + 2 * t] = a * cc[t] - b * sn[t];
+          v[8 * q + 2 * t + 1] = a * sn[t] + b * cc[t];
         }
       }
     }
@@ -161,19 +140,22 @@ __device__ __forceinline__ void gemm_epilogue_64(float (&v)[64], int m, int n0, 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmOut,
+                    const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using S = GemmSmem<BN>;
+  constexpr bool HAS_AUX = (EPI == EPI_RESIDUAL || EPI == EPI_GATE);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-  const uint32_t bar_base = smem_base + S::STAGES * S::STAGE_BYTES;
-  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  const uint32_t bar_base = smem_base + S::BAR_OFF;
+  // barriers (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], aux[8]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S::STAGES + s); };
   auto accf_bar = [&](int b) { return bar_base + 8u * (2 * S::STAGES + b); };
   auto acce_bar = [&](int b) { return bar_base + 8u * (2 * S::STAGES + 2 + b); };
-  uint8_t* tail = smem_gen + S::STAGES * S::STAGE_BYTES + 8 * (2 * S::STAGES + 4);
+  auto aux_bar = [&](int w) { return bar_base + 8u * (2 * S::STAGES + 4 + w); };
+  uint8_t* tail = smem_gen + S::BAR_OFF + 8 * (2 * S::STAGES + 4 + GEMM_EPI_WARPS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
 
@@ -194,6 +176,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(accf_bar(b), 1);
       mbar_init(acce_bar(b), GEMM_EPI_WARPS);
     }
+    for (int w = 0; w < GEMM_EPI_WARPS; ++w) mbar_init(aux_bar(w), 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -272,59 +255,149 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
+    // Each warp owns 32 output rows (its TMEM lane quarter) x BN/2 columns of the tile and
+    // walks them in 64-column chunks: TMEM -> registers -> math -> 128-byte-swizzled staging
+    // box in shared memory -> TMA store (clipped at the matrix edge by the tensor map). The
+    // residual / gated operand of a chunk is TMA-loaded into the same staging box beforehand.
     const int e = warp - 2;
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
     const int col_half = e >> 2;             // which half of the BN columns
     constexpr int HALF_COLS = BN / 2;
+    constexpr int NCHUNK = HALF_COLS / 64;
+    const uint32_t stage_s = smem_base + S::STAGING_OFF + e * S::STAGING_BYTES;
+    const uint32_t my_row_s = stage_s + lane * 128;
+    const uint32_t sw = static_cast<uint32_t>(lane & 7);
+    uint32_t aux_phase = 0;
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       const int m0 = (t / tiles_n) * GEMM_BM;
       const int n_tile0 = (t % tiles_n) * BN;
-      if (!mbar_wait(accf_bar(buf), acc_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after();
-      const int m = m0 + quarter * 32 + lane;
+      const int m_warp = m0 + quarter * 32;
+      const int m = m_warp + lane;
       const bool row_ok = m < p.M;
+      const int n_warp0 = n_tile0 + col_half * HALF_COLS;
+      bool acc_ready = false;
 #pragma unroll 1
-      for (int c = 0; c < HALF_COLS; c += 64) {
-        const int n0 = n_tile0 + col_half * HALF_COLS + c;
-        if (n0 >= p.N) break;  // warp-uniform
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                               static_cast<uint32_t>(buf * BN + col_half * HALF_COLS + c);
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(taddr, r0);
-        tmem_ld_32x32(taddr + 32, r1);
-        tmem_ld_wait();
-        float v[64];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = __uint_as_float(r0[j]);
-          v[32 + j] = __uint_as_float(r1[j]);
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int n0 = n_warp0 + c * 64;
+        const bool chunk_live = (n0 < p.N) && (m_warp < p.M);   // warp-uniform
+        float b_lane[2] = {0.f, 0.f};
+        if (p.bias != nullptr) {
+          if (n0 + lane < p.N) b_lane[0] = __ldg(p.bias + n0 + lane);
+          if (n0 + 32 + lane < p.N) b_lane[1] = __ldg(p.bias + n0 + 32 + lane);
         }
-        gemm_epilogue_64<EPI>(v, m, n0, row_ok, p);
-        if (row_ok) {
-          __nv_bfloat16* op = p.out + static_cast<long long>(m) * p.ldo + n0;
-          if (n0 + 64 <= p.N && (p.ldo % 8) == 0) {
-#pragma unroll
-            for (int j = 0; j < 64; j += 8) {
-              uint4 o;
-              o.x = pack_bf16(v[j], v[j + 1]);
-              o.y = pack_bf16(v[j + 2], v[j + 3]);
-              o.z = pack_bf16(v[j + 4], v[j + 5]);
-              o.w = pack_bf16(v[j + 6], v[j + 7]);
-              *reinterpret_cast<uint4*>(op + j) = o;
+        if (chunk_live) {
+          // staging box free again? (previous TMA store has finished reading it)
+          if (lane == 0) tma_store_wait_read0();
+          __syncwarp();
+          if constexpr (HAS_AUX) {
+            if (lane == 0) {
+              mbar_expect_tx(aux_bar(e), S::STAGING_BYTES);
+              tma_load_2d(stage_s, &tmAux, n0, m_warp, aux_bar(e));
             }
-          } else {
-            for (int j = 0; j < 64; ++j)
-              if (n0 + j < p.N) op[j] = __float2bfloat16(v[j]);
           }
         }
+        if (!acc_ready) {
+          if (!mbar_wait(accf_bar(buf), acc_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          acc_ready = true;
+        }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               static_cast<uint32_t>(buf * BN + col_half * HALF_COLS + c * 64);
+        float qk_scale[2] = {1.f, 1.f};
+        if constexpr (EPI == EPI_QKV_ROPE) {
+          // per-head RMS factor needs the whole head: one extra pass over the accumulator
+          if (chunk_live && p.qk_norm && n0 < p.rope_cols) {
+            float ss[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + 32 * hh, r);
+              tmem_ld_wait();
+              float acc = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float x = __uint_as_float(r[j]) +
+                                (p.bias != nullptr ? __shfl_sync(0xffffffffu, b_lane[hh], j) : 0.f);
+                acc += x * x;
+              }
+              ss[hh] = acc;
+            }
+            if (p.head_dim == 64) {
+              qk_scale[0] = qk_scale[1] = rsqrtf((ss[0] + ss[1]) * (1.0f / 64.0f) + p.qk_eps);
+            } else {
+              qk_scale[0] = rsqrtf(ss[0] * (1.0f / 32.0f) + p.qk_eps);
+              qk_scale[1] = rsqrtf(ss[1] * (1.0f / 32.0f) + p.qk_eps);
+            }
+          }
+        }
+        if constexpr (HAS_AUX) {
+          if (chunk_live) {
+            if (!mbar_wait(aux_bar(e), aux_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
+              ok = false;
+              break;
+            }
+            aux_phase ^= 1u;
+          }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          if (chunk_live) {
+            tmem_ld_32x32(taddr + 32 * hh, r);
+            tmem_ld_wait();
+          }
+          if (hh == 1 && c == NCHUNK - 1) {
+            // the accumulator is in registers (or not needed): hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(buf));
+          }
+          if (chunk_live) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            uint32_t aux[16];
+            if constexpr (HAS_AUX) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(aux[4 * q]), "=r"(aux[4 * q + 1]), "=r"(aux[4 * q + 2]),
+                               "=r"(aux[4 * q + 3])
+                             : "r"(addr)
+                             : "memory");
+              }
+            }
+            gemm_epilogue_32<EPI>(v, m, n0 + 32 * hh, row_ok, b_lane[hh], aux, qk_scale[hh], p);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16(v[8 * q], v[8 * q + 1])),
+                           "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])),
+                           "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
+                           "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7]))
+                           : "memory");
+            }
+          }
+        }
+        if (!chunk_live) continue;
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmOut, stage_s, n0, m_warp);
+          tma_store_commit();
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(buf));
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -354,6 +427,18 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
     uint32_t box[2] = {GEMM_BK, static_cast<uint32_t>(BN)};
     if (make_tmap_bf16(&tmB, W, 2, dims, str, box) != 0) return -21;
   }
+  CUtensorMap tmOut, tmAux;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M)};
+    uint64_t str[1] = {static_cast<uint64_t>(p.ldo) * 2};
+    uint32_t box[2] = {64, 32};
+    if (make_tmap_bf16(&tmOut, p.out, 2, dims, str, box) != 0) return -22;
+    tmAux = tmOut;
+    if (EPI == EPI_RESIDUAL || EPI == EPI_GATE) {
+      uint64_t astr[1] = {static_cast<uint64_t>(p.ldaux) * 2};
+      if (make_tmap_bf16(&tmAux, p.aux, 2, dims, astr, box) != 0) return -23;
+    }
+  }
   using S = GemmSmem<BN>;
   auto kern = gemm_tcgen05_kernel<BN, EPI>;
   {
@@ -364,7 +449,7 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
   }
   const int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmOut, tmAux, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
