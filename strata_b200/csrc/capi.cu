@@ -179,7 +179,7 @@ int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
   int r = launch_na3d(static_cast<const __nv_bfloat16*>(q), ldq,
                       static_cast<const __nv_bfloat16*>(k), ldk,
                       static_cast<const __nv_bfloat16*>(v), ldv, static_cast<__nv_bfloat16*>(out),
-                      ldo, B, D, H, W, heads, kd, kh, kw, sc, as_stream(stream));
+                      ldo, B, D, H, W, heads, kd, kh, kw, sc, sms, as_stream(stream));
   if (r == -1) return STRATA_ERR_ARG;
   if (r == -2) return STRATA_ERR_UNSUPPORTED;
   return r;

@@ -3,29 +3,35 @@
 // window, times v. Windows keep their full size at the borders: along an axis of length L
 // the window of query i starts at clamp(i - k/2, 0, L - k).
 //
-// Work decomposition
-//   CTA            one tile of 128 queries (QD x QH x 8 tokens) of one head of one tile batch
-//                  entry; two CTAs are co-resident per SM so one CTA's softmax overlaps the
-//                  other's tensor work.
-//   key blocks     the union of the tile's windows is a box of ED x EH x EW keys
+// Work decomposition (persistent kernel, one CTA per SM, 10 warps)
+//   work item      one tile of 128 queries (QD x QH x 8 tokens) of one head of one batch entry;
+//                  CTA c handles items c, c + gridDim.x, ... (neighbouring items are
+//                  neighbouring tiles of the same head, so their key halos meet in L2).
+//   key blocks     the union of a tile's windows is a box of ED x EH x EW keys
 //                  (E* = Q* + k* - 1) starting at the window start of the tile's first query.
-//                  It is streamed as blocks of one depth plane x 8 rows x EW columns
-//                  (NKEYS = 8*EW keys); TMA zero-fills whatever lies outside the tensor.
-//   warp 0         TMA producer: Q tile once, then K and V blocks into a 2-stage ring
-//                  (5-D tensor maps over [B, D, H, W, channels]; 128-byte swizzle, a key's 64
-//                  channels are one 128-byte row).
-//   warp 1         MMA issuer: S = Q K^T (M=128, N=NKEYS, K=64) into TMEM, then
-//                  O_blk = P V (M=128, N=64, K=NKEYS) with P read from shared memory.
-//   warps 2-5      softmax: each thread owns one query row. Pass 1 reads its S row from
-//                  TMEM and takes the masked maximum, pass 2 re-reads it, exponentiates,
-//                  writes bf16 P into the swizzled A-operand layout and keeps the running
-//                  sum; the per-block P V result is read back from TMEM and accumulated
-//                  in registers with the usual online-softmax rescaling. Key rows that no
-//                  query of the warp can see are skipped (zeros written) without touching
-//                  the exponential unit.
-//   mask           per (query, key): the key's box coordinates must fall in the query's
-//                  window on all three axes; evaluated from a per-thread column bit mask,
-//                  a row bit mask and a plane test, so border clamping is exact per row.
+//                  It is streamed as blocks of one depth plane x 8 rows x EWP columns
+//                  (EWP = EW rounded up to a multiple of 4, NKEYS = 8*EWP); TMA zero-fills
+//                  whatever lies outside the tensor.
+//   warp 0         TMA producer: Q tile (double-buffered across items) and the K / V blocks into
+//                  a 2-3 stage ring (5-D tensor maps over [B, D, H, W, channels]; 128-byte
+//                  swizzle, a key's 64 channels are one 128-byte row). Runs ahead across items.
+//   warp 1         MMA issuer: S = Q K^T (M=128, N=NKEYS, K=64) into one of two TMEM buffers -
+//                  block i+1 is issued before the softmax of block i has finished - then
+//                  O_g = P_g V_g (M=128, N=64) for each of the two key halves g.
+//   warps 2-9      softmax, two warpgroups. A query row is shared by one thread of each group;
+//                  group g owns key rows [4g, 4g+4) of every block, keeps its own running
+//                  max / sum / 64-wide output accumulator for them (no exchange per block), and
+//                  the two partial results are merged once per item through shared memory.
+//                  Per block: pass 1 reads the thread's S row segment from TMEM and takes the
+//                  masked maximum, pass 2 re-reads it, exponentiates, writes bf16 P into the
+//                  swizzled A-operand layout and keeps the running sum; the previous block's
+//                  P V result is read back from TMEM and accumulated in registers with the
+//                  online-softmax rescaling. Key rows no query of the warp can see are skipped
+//                  (zeros written) without touching the exponential unit.
+//   mask           per (query, key): the key's box coordinates must fall in the query's window
+//                  on all three axes. Columns: an additive per-thread bias vector (0 / -1e30);
+//                  rows: a per-thread bit mask; planes: one comparison per block. Border
+//                  clamping is therefore exact per query row.
 #pragma once
 #include "common.cuh"
 #include "tensormap.cuh"
@@ -37,28 +43,35 @@ struct Na3dParams {
   int kd, kh;            // kernel extents along depth and rows (columns: template KW)
   int QD, QH;            // query tile extents (QW = 8); QD*QH = 16
   int tiles_d, tiles_h, tiles_w;
+  int n_items;           // tiles_d*tiles_h*tiles_w*heads*B
   __nv_bfloat16* out;    // [B, D, H, W, ldo] with head h at channel offset h*64
   long long ldo;
   float scale_log2e;
 };
 
-constexpr int NA_THREADS = 192;
+constexpr int NA_THREADS = 320;
 constexpr int NA_QW = 8;
-constexpr int NA_TMEM_COLS = 256;
-constexpr int NA_O_COL = 192;
+constexpr int NA_TMEM_COLS = 512;
+constexpr int NA_S1_COL = 192;
+constexpr int NA_O_COL = 384;   // O of key half 0; half 1 at +64
+constexpr int NA_MERGE_FLOATS = 66;
 
 template <int KW>
 struct Na3dCfg {
   static constexpr int EW = NA_QW + KW - 1;
-  static constexpr int NKEYS = 8 * EW;
+  static constexpr int EWP = (EW + 3) / 4 * 4;
+  static constexpr int NKEYS = 8 * EWP;
   static constexpr int KV_BYTES = NKEYS * 128;
   static constexpr int P_ATOMS = (NKEYS + 63) / 64;
   static constexpr int Q_BYTES = 128 * 128;
-  static constexpr int STAGES = 2;
-  static constexpr int P_OFF = Q_BYTES + STAGES * 2 * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_ATOMS * 16384;
-  static constexpr int TOTAL = BAR_OFF + 128;
-  static_assert(NKEYS % 16 == 0 && NKEYS <= NA_O_COL, "key block must fit the S columns");
+  static constexpr int STAGES = NKEYS <= 128 ? 3 : 2;
+  static constexpr int KV_OFF = 2 * Q_BYTES;
+  static constexpr int P_OFF = KV_OFF + STAGES * 2 * KV_BYTES;
+  static constexpr int MERGE_OFF = P_OFF + P_ATOMS * 16384;
+  static constexpr int BAR_OFF = MERGE_OFF + 128 * NA_MERGE_FLOATS * 4;
+  static constexpr int TOTAL = BAR_OFF + 256;
+  static_assert(NKEYS % 32 == 0 && NKEYS <= NA_S1_COL, "key block must fit an S buffer");
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
 __device__ __forceinline__ int na_window_start(int i, int L, int k) {
@@ -67,6 +80,12 @@ __device__ __forceinline__ int na_window_start(int i, int L, int k) {
   return s > L - k ? L - k : s;
 }
 
+__device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
@@ -84,69 +103,101 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
-// Loads at least EW consecutive S columns of this thread's row (extra columns are ignored).
-template <int EW>
-__device__ __forceinline__ void tmem_ld_keyrow(uint32_t taddr, uint32_t (&a)[32]) {
-  if constexpr (EW <= 16) {
+// Loads EWP (8, 12, 16, 20 or 24) consecutive S columns of this thread's row.
+template <int EWP>
+__device__ __forceinline__ void tmem_ld_keyrow(uint32_t taddr, uint32_t (&a)[24]) {
+  if constexpr (EWP == 8) {
+    tmem_ld_x8(taddr, a);
+  } else if constexpr (EWP == 12) {
+    tmem_ld_x8(taddr, a);
+    tmem_ld_x4(taddr + 8, a + 8);
+  } else if constexpr (EWP == 16) {
     tmem_ld_x16(taddr, a);
-  } else if constexpr (EW <= 24) {
+  } else if constexpr (EWP == 20) {
+    tmem_ld_x16(taddr, a);
+    tmem_ld_x4(taddr + 16, a + 16);
+  } else {
     tmem_ld_x16(taddr, a);
     tmem_ld_x8(taddr + 16, a + 16);
-  } else {
-    tmem_ld_32x32(taddr, a);
   }
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+struct NaItem {
+  int b, head, d0, h0, w0, bd0, bh0, bw0;
+};
+template <int KW>
+__device__ __forceinline__ NaItem na_decode_item(int item, const Na3dParams& p) {
+  NaItem it;
+  int t = item;
+  const int tw = t % p.tiles_w; t /= p.tiles_w;
+  const int th = t % p.tiles_h; t /= p.tiles_h;
+  const int td = t % p.tiles_d; t /= p.tiles_d;
+  it.head = t % p.heads;
+  it.b = t / p.heads;
+  it.d0 = td * p.QD; it.h0 = th * p.QH; it.w0 = tw * NA_QW;
+  // key box origin = window start of the tile's first query on each axis
+  it.bd0 = na_window_start(it.d0, p.D, p.kd);
+  it.bh0 = na_window_start(it.h0, p.H, p.kh);
+  it.bw0 = na_window_start(it.w0, p.W, KW);
+  return it;
 }
 
 template <int KW>
-__global__ void __launch_bounds__(NA_THREADS, 2)
+__global__ void __launch_bounds__(NA_THREADS, 1)
 na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const Na3dParams p) {
   using Cfg = Na3dCfg<KW>;
   constexpr int EW = Cfg::EW;
+  constexpr int EWP = Cfg::EWP;
   constexpr int NKEYS = Cfg::NKEYS;
+  constexpr int STAGES = Cfg::STAGES;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   if ((sbase & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(&g_status, 0, ST_BAD_TMEM);
     return;
   }
-  const uint32_t q_smem = sbase;
-  auto k_smem = [&](int st) { return sbase + Cfg::Q_BYTES + st * 2 * Cfg::KV_BYTES; };
+  auto q_smem = [&](int qb) { return sbase + qb * Cfg::Q_BYTES; };
+  auto k_smem = [&](int st) { return sbase + Cfg::KV_OFF + st * 2 * Cfg::KV_BYTES; };
   auto v_smem = [&](int st) { return k_smem(st) + Cfg::KV_BYTES; };
   const uint32_t p_smem = sbase + Cfg::P_OFF;
+  float* merge = reinterpret_cast<float*>(smem + Cfg::MERGE_OFF);
   const uint32_t bar = sbase + Cfg::BAR_OFF;
-  const uint32_t q_full = bar, s_full = bar + 8, p_ready = bar + 16, o_full = bar + 24;
-  auto kv_full = [&](int st) { return bar + 32 + 8 * st; };
-  auto kv_empty = [&](int st) { return bar + 48 + 8 * st; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 64);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 72);
+  // barriers, 8 bytes each
+  auto q_full = [&](int qb) { return bar + 8u * qb; };           // 0,1
+  auto q_empty = [&](int qb) { return bar + 16u + 8u * qb; };    // 2,3
+  auto s_full = [&](int sb) { return bar + 32u + 8u * sb; };     // 4,5
+  const uint32_t p_ready = bar + 48u, o_full = bar + 56u;        // 6,7
+  const uint32_t merge_full = bar + 64u, merge_free = bar + 72u; // 8,9
+  auto kv_full = [&](int st) { return bar + 80u + 8u * st; };    // 10..12
+  auto kv_empty = [&](int st) { return bar + 104u + 8u * st; };  // 13..15
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 168);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // tile coordinates
-  int t = blockIdx.x;
-  const int tw = t % p.tiles_w; t /= p.tiles_w;
-  const int th = t % p.tiles_h; t /= p.tiles_h;
-  const int td = t;
-  const int head = blockIdx.y;
-  const int b = blockIdx.z;
-  const int d0 = td * p.QD, h0 = th * p.QH, w0 = tw * NA_QW;
-  // key box origin = window start of the tile's first query on each axis
-  const int bd0 = na_window_start(d0, p.D, p.kd);
-  const int bh0 = na_window_start(h0, p.H, p.kh);
-  const int bw0 = na_window_start(w0, p.W, KW);
   const int ED = p.QD + p.kd - 1;
   const int EH = p.QH + p.kh - 1;
   const int n_hb = (EH + 7) >> 3;
   const int nblk = ED * n_hb;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full(i), 1);
+      mbar_init(q_empty(i), 1);
+      mbar_init(s_full(i), 1);
+    }
+    mbar_init(p_ready, 256);
     mbar_init(o_full, 1);
-    for (int s = 0; s < Cfg::STAGES; ++s) {
+    mbar_init(merge_full, 128);
+    mbar_init(merge_free, 128);
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
@@ -163,55 +214,114 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
-      tma_load_5d(q_smem, &tmQ, head * 64, w0, h0, d0, b, q_full);
       bool ok = true;
-      for (int i = 0; i < nblk; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1u;
-        if (!mbar_wait(kv_empty(st), ph ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
-          ok = false;
-          break;
+      int n = 0;
+      long long gb = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
+        const NaItem it = na_decode_item<KW>(item, p);
+        const int qb = n & 1;
+        if (!mbar_wait(q_empty(qb), ((n >> 1) & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) break;
+        mbar_expect_tx(q_full(qb), Cfg::Q_BYTES);
+        tma_load_5d(q_smem(qb), &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full(qb));
+        for (int i = 0; i < nblk; ++i, ++gb) {
+          const int st = static_cast<int>(gb % STAGES);
+          const uint32_t ph = static_cast<uint32_t>((gb / STAGES) & 1);
+          if (!mbar_wait(kv_empty(st), ph ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const int ip = i / n_hb, hb = i - ip * n_hb;
+          mbar_expect_tx(kv_full(st), 2 * Cfg::KV_BYTES);
+          tma_load_5d(k_smem(st), &tmK, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
+                      kv_full(st));
+          tma_load_5d(v_smem(st), &tmV, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
+                      kv_full(st));
         }
-        const int ip = i / n_hb, hb = i - ip * n_hb;
-        mbar_expect_tx(kv_full(st), 2 * Cfg::KV_BYTES);
-        tma_load_5d(k_smem(st), &tmK, head * 64, bw0, bh0 + 8 * hb, bd0 + ip, b, kv_full(st));
-        tma_load_5d(v_smem(st), &tmV, head * 64, bw0, bh0 + 8 * hb, bd0 + ip, b, kv_full(st));
       }
       if (!ok)
         for (int i = 0; i < 2000; ++i) __nanosleep(100);
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NKEYS, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, false, true);
-      const uint32_t s_tmem = tmem_base;
-      const uint32_t o_tmem = tmem_base + NA_O_COL;
-      if (mbar_wait(q_full, 0, abort_flag, ST_TIMEOUT_MMA)) {
-        const uint64_t qdesc = umma_smem_desc_sw128(q_smem);
-        for (int i = 0; i < nblk; ++i) {
-          const int st = i & 1;
-          const uint32_t ph = (i >> 1) & 1u;
-          if (!mbar_wait(kv_full(st), ph, abort_flag, ST_TIMEOUT_MMA)) break;
-          tc_fence_after();
-          const uint64_t kdesc = umma_smem_desc_sw128(k_smem(st));
+      constexpr int HALF_STEPS = EWP / 4;  // 16-key MMA steps per key half
+      auto issue_qk = [&](uint32_t qaddr, long long g) {
+        const int st = static_cast<int>(g % STAGES);
+        const uint64_t qdesc = umma_smem_desc_sw128(qaddr);
+        const uint64_t kdesc = umma_smem_desc_sw128(k_smem(st));
+        const uint32_t s_tmem = tmem_base + ((g & 1) ? NA_S1_COL : 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ss(s_tmem, qdesc + 2u * k, kdesc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
-          umma_commit(s_full);
-          if (!mbar_wait(p_ready, i & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
+        for (int k = 0; k < 4; ++k)
+          umma_ss(s_tmem, qdesc + 2u * k, kdesc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
+        umma_commit(s_full(static_cast<int>(g & 1)));
+      };
+      auto wait_kv = [&](long long g) {
+        const int st = static_cast<int>(g % STAGES);
+        return mbar_wait(kv_full(st), static_cast<uint32_t>((g / STAGES) & 1), abort_flag,
+                         ST_TIMEOUT_MMA);
+      };
+      bool ok = true;
+      int n = 0;
+      long long gb = 0;
+      // Invariant at the top of an item: S for its block 0 has NOT been issued yet unless
+      // `pre_issued` (it is issued at the end of the previous item to keep the pipe full).
+      bool pre_issued = false;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
+        const int qb = n & 1;
+        if (!pre_issued) {
+          if (!mbar_wait(q_full(qb), (n >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
+          if (!wait_kv(gb)) break;
           tc_fence_after();
+          issue_qk(q_smem(qb), gb);
+        }
+        pre_issued = false;
+        for (int i = 0; i < nblk; ++i, ++gb) {
+          // run ahead: S of the next block (of this item, or block 0 of the next item)
+          if (i + 1 < nblk) {
+            if (!wait_kv(gb + 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_qk(q_smem(qb), gb + 1);
+            if (i + 2 == nblk) umma_commit(q_empty(qb));   // last Q K^T of this item issued
+          } else {
+            if (nblk == 1) umma_commit(q_empty(qb));
+            const int next = item + gridDim.x;
+            if (next < p.n_items) {
+              const int nq = (n + 1) & 1;
+              if (!mbar_wait(q_full(nq), ((n + 1) >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) {
+                ok = false;
+                break;
+              }
+              if (!wait_kv(gb + 1)) { ok = false; break; }
+              tc_fence_after();
+              issue_qk(q_smem(nq), gb + 1);
+              pre_issued = true;
+            }
+          }
+          if (!mbar_wait(p_ready, static_cast<uint32_t>(gb & 1), abort_flag, ST_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int st = static_cast<int>(gb % STAGES);
           const uint64_t vdesc = umma_smem_desc_sw128(v_smem(st));
 #pragma unroll
-          for (int s = 0; s < NKEYS / 16; ++s) {
-            const uint64_t pdesc =
-                umma_smem_desc_sw128(p_smem + (s >> 2) * 16384 + (s & 3) * 32);
-            // V advances 16 keys = 16 rows of 128 bytes per step (2048 bytes, 128 units)
-            umma_ss(o_tmem, pdesc, vdesc + 128u * s, idesc_pv, s != 0 ? 1u : 0u);
+          for (int g = 0; g < 2; ++g) {
+#pragma unroll
+            for (int s0 = 0; s0 < HALF_STEPS; ++s0) {
+              const int s = g * HALF_STEPS + s0;
+              const uint64_t pdesc =
+                  umma_smem_desc_sw128(p_smem + (s >> 2) * 16384 + (s & 3) * 32);
+              // V advances 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
+              umma_ss(tmem_base + NA_O_COL + 64 * g, pdesc, vdesc + 128u * s, idesc_pv,
+                      s0 != 0 ? 1u : 0u);
+            }
           }
           umma_commit(kv_empty(st));
           umma_commit(o_full);
@@ -221,133 +331,198 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else {
     // ------------------------------------------------------------ softmax warps
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
+    const int grp = (warp - 2) >> 2;          // key half this thread owns
+    const int r = quarter * 32 + lane;        // query row
     const int zw = r & 7;
     const int zh = (r >> 3) % p.QH;
     const int zd = (r >> 3) / p.QH;
-    const bool q_ok = (d0 + zd < p.D) && (h0 + zh < p.H) && (w0 + zw < p.W);
-    const int id = min(d0 + zd, p.D - 1), ih = min(h0 + zh, p.H - 1), iw = min(w0 + zw, p.W - 1);
-    const int wd = na_window_start(id, p.D, p.kd) - bd0;
-    const int wh = na_window_start(ih, p.H, p.kh) - bh0;
-    const int ww = na_window_start(iw, p.W, KW) - bw0;
-    const uint32_t colmask = ((1u << KW) - 1u) << ww;
-    const uint32_t hmask_all = ((1u << p.kh) - 1u) << wh;   // bit = key row of the box
     const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t o_taddr = lane_taddr + NA_O_COL + 64 * grp;
     const uint32_t p_row = p_smem + r * 128;
     const uint32_t sw = static_cast<uint32_t>(r & 7);
     const float c = p.scale_log2e;
-
-    float m_run = -1e30f, l_run = 0.f, alpha_prev = 1.f;
-    float o[64];
-#pragma unroll
-    for (int j = 0; j < 64; ++j) o[j] = 0.f;
+    constexpr int GKEYS = 4 * EWP;            // keys per block owned by one group
 
     bool ok = true;
-    for (int i = 0; i < nblk && ok; ++i) {
-      const int ip = i / n_hb, hb = i - ip * n_hb;
-      if (!mbar_wait(s_full, i & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) { ok = false; break; }
-      tc_fence_after();
-      const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
-      const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb)) & 0xffu) : 0u;
-      const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
+    int n = 0;
+    long long gb = 0;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
+      const NaItem it = na_decode_item<KW>(item, p);
+      const bool q_ok = (it.d0 + zd < p.D) && (it.h0 + zh < p.H) && (it.w0 + zw < p.W);
+      const int id = min(it.d0 + zd, p.D - 1), ih = min(it.h0 + zh, p.H - 1),
+                iw = min(it.w0 + zw, p.W - 1);
+      const int wd = na_window_start(id, p.D, p.kd) - it.bd0;
+      const int wh = na_window_start(ih, p.H, p.kh) - it.bh0;
+      const int ww = na_window_start(iw, p.W, KW) - it.bw0;
+      float cb[EWP];   // additive column mask: 0 inside the window, -1e30 outside
+#pragma unroll
+      for (int cc = 0; cc < EWP; ++cc)
+        cb[cc] = (static_cast<unsigned>(cc - ww) < static_cast<unsigned>(KW)) ? 0.f : -1e30f;
+      const uint32_t hmask_all = ((1u << p.kh) - 1u) << wh;   // bit = key row of the box
 
-      // pass 1: masked row maximum
-      float bm = -1e30f;
+      float m_run = -1e30f, l_run = 0.f, alpha_prev = 1.f;
+      float o[64];
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
-        if ((warp_rows >> rr) & 1u) {
-          uint32_t a[32];
-          tmem_ld_keyrow<EW>(lane_taddr + rr * EW, a);
-          tmem_ld_wait();
-          const uint32_t mk = ((rowmask >> rr) & 1u) ? colmask : 0u;
-#pragma unroll
-          for (int cc = 0; cc < EW; ++cc)
-            if ((mk >> cc) & 1u) bm = fmaxf(bm, __uint_as_float(a[cc]));
+      for (int j = 0; j < 64; ++j) o[j] = 0.f;
+
+      for (int i = 0; i < nblk; ++i, ++gb) {
+        const int ip = i / n_hb, hb = i - ip * n_hb;
+        const int sb = static_cast<int>(gb & 1);
+        if (!mbar_wait(s_full(sb), static_cast<uint32_t>((gb >> 1) & 1), abort_flag,
+                       ST_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
         }
-      }
-      const float m_new = fmaxf(m_run, bm);
-      const float alpha = fast_exp2((m_run - m_new) * c);
-      const float mc = m_new * c;
-
-      // fold in the previous block's P V result
-      if (i > 0) {
-        if (!mbar_wait(o_full, (i - 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t s_taddr = lane_taddr + (sb ? NA_S1_COL : 0) + grp * GKEYS;
+        const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
+        const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + 4 * grp)) & 0xfu) : 0u;
+        const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
+
+        // pass 1: masked row maximum over this thread's key rows
+        float bm = -1e30f;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          if ((warp_rows >> rr) & 1u) {
+            uint32_t a[24];
+            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+            tmem_ld_wait();
+            float rm = -1e30f;
+#pragma unroll
+            for (int cc = 0; cc < EW; cc += 2)
+              rm = fmax3(rm, __uint_as_float(a[cc]) + cb[cc],
+                         (cc + 1 < EW) ? __uint_as_float(a[cc + 1]) + cb[cc + 1] : -1e30f);
+            bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? rm : -1e30f);
+          }
+        }
+        const float m_new = fmaxf(m_run, bm);
+        const float alpha = fast_exp2((m_run - m_new) * c);
+        const float mc = m_new * c;
+
+        // fold in the previous block's P V result of this key half
+        if (i > 0) {
+          if (!mbar_wait(o_full, static_cast<uint32_t>((gb - 1) & 1), abort_flag,
+                         ST_TIMEOUT_SOFTMAX)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t ob[32];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            tmem_ld_32x32(o_taddr + 32 * hh, ob);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              o[32 * hh + j] = o[32 * hh + j] * alpha_prev + __uint_as_float(ob[j]);
+          }
+        }
+
+        // pass 2: exponentials, row sum, bf16 P into the swizzled A-operand layout
+        float nb[EWP];
+#pragma unroll
+        for (int cc = 0; cc < EWP; ++cc) nb[cc] = cb[cc] - mc;
+        float rs = 0.f;
+        uint32_t pk[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const bool need = (warp_rows >> rr) & 1u;
+          const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
+          uint32_t a[24];
+          float rsr = 0.f;
+          if (need) {
+            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+            tmem_ld_wait();
+          }
+#pragma unroll
+          for (int cc = 0; cc < EWP; cc += 2) {
+            const int jj = rr * EWP + cc;   // even, compile-time
+            uint32_t packed = 0u;
+            if (need && cc < EW) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, nb[cc]));
+              const float p1 =
+                  (cc + 1 < EW) ? fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, nb[cc + 1])) : 0.f;
+              rsr += p0 + p1;
+              packed = pack_bf16(p0, p1) & keep;
+            }
+            pk[(jj >> 1) & 3] = packed;
+            if ((jj & 7) == 6) {
+              const int j = grp * GKEYS + jj;   // key index within the block
+              const uint32_t addr =
+                  p_row + static_cast<uint32_t>(j >> 6) * 16384u +
+                  ((static_cast<uint32_t>((j & 63) >> 3) ^ sw) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]),
+                           "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                           : "memory");
+            }
+          }
+          rs += keep ? rsr : 0.f;
+        }
+        l_run = l_run * alpha + rs;
+        m_run = m_new;
+        alpha_prev = alpha;
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(p_ready);
+      }
+      if (!ok) break;
+
+      // item epilogue: last P V, merge the two key halves, normalise, store
+      if (!mbar_wait(o_full, static_cast<uint32_t>((gb - 1) & 1), abort_flag, ST_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      {
         uint32_t ob[32];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          tmem_ld_32x32(lane_taddr + NA_O_COL + 32 * hh, ob);
+          tmem_ld_32x32(o_taddr + 32 * hh, ob);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             o[32 * hh + j] = o[32 * hh + j] * alpha_prev + __uint_as_float(ob[j]);
         }
       }
-
-      // pass 2: exponentials, row sum, bf16 P into the swizzled A-operand layout
-      float rs = 0.f;
-      uint32_t pk[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
-        const bool need = (warp_rows >> rr) & 1u;
-        uint32_t a[32];
-        uint32_t mk = 0u;
-        if (need) {
-          tmem_ld_keyrow<EW>(lane_taddr + rr * EW, a);
-          tmem_ld_wait();
-          mk = ((rowmask >> rr) & 1u) ? colmask : 0u;
-        }
-#pragma unroll
-        for (int cc = 0; cc < EW; cc += 2) {
-          const int j = rr * EW + cc;  // even
-          float p0 = 0.f, p1 = 0.f;
-          if (need) {
-            if ((mk >> cc) & 1u) p0 = fast_exp2(__uint_as_float(a[cc]) * c - mc);
-            if ((mk >> (cc + 1)) & 1u) p1 = fast_exp2(__uint_as_float(a[cc + 1]) * c - mc);
-            rs += p0 + p1;
-          }
-          pk[(j >> 1) & 3] = pack_bf16(p0, p1);
-          if ((j & 7) == 6) {
-            const uint32_t chunk = static_cast<uint32_t>((j & 63) >> 3);
-            const uint32_t addr = p_row + (j >> 6) * 16384 + ((chunk ^ sw) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]),
-                         "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                         : "memory");
-          }
-        }
-      }
-      l_run = l_run * alpha + rs;
-      m_run = m_new;
-      alpha_prev = alpha;
-      fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_ready);
-    }
-
-    if (ok && mbar_wait(o_full, (nblk - 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
-      tc_fence_after();
-      uint32_t ob[32];
-      const float inv = 1.0f / l_run;
+      if (grp == 1) {
+        if (!mbar_wait(merge_free, ((n & 1u) ^ 1u), abort_flag, ST_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
+        }
+        merge[0 * 128 + r] = m_run;
+        merge[1 * 128 + r] = l_run;
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        tmem_ld_32x32(lane_taddr + NA_O_COL + 32 * hh, ob);
-        tmem_ld_wait();
+        for (int j = 0; j < 64; ++j) merge[(2 + j) * 128 + r] = o[j];
+        mbar_arrive(merge_full);   // release semantics order the stores before the arrival
+      } else {
+        if (!mbar_wait(merge_full, n & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
+        }
+        const float m1 = merge[0 * 128 + r];
+        const float l1 = merge[1 * 128 + r];
+        const float m = fmaxf(m_run, m1);
+        const float f0 = fast_exp2((m_run - m) * c);
+        const float f1 = fast_exp2((m1 - m) * c);
+        const float inv = 1.0f / (l_run * f0 + l1 * f1);
+        const float g0 = f0 * inv, g1 = f1 * inv;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          o[32 * hh + j] = (o[32 * hh + j] * alpha_prev + __uint_as_float(ob[j])) * inv;
-      }
-      if (q_ok) {
-        const long long tok =
-            ((static_cast<long long>(b) * p.D + (d0 + zd)) * p.H + (h0 + zh)) * p.W + (w0 + zw);
-        __nv_bfloat16* op = p.out + tok * p.ldo + head * 64;
+        for (int j = 0; j < 64; ++j) o[j] = o[j] * g0 + merge[(2 + j) * 128 + r] * g1;
+        mbar_arrive(merge_free);
+        if (q_ok) {
+          const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.H +
+                                 (it.h0 + zh)) * p.W + (it.w0 + zw);
+          __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64;
 #pragma unroll
-        for (int j = 0; j < 64; j += 8) {
-          uint4 v4;
-          v4.x = pack_bf16(o[j], o[j + 1]);
-          v4.y = pack_bf16(o[j + 2], o[j + 3]);
-          v4.z = pack_bf16(o[j + 4], o[j + 5]);
-          v4.w = pack_bf16(o[j + 6], o[j + 7]);
-          *reinterpret_cast<uint4*>(op + j) = v4;
+          for (int j = 0; j < 64; j += 8) {
+            uint4 v4;
+            v4.x = pack_bf16(o[j], o[j + 1]);
+            v4.y = pack_bf16(o[j + 2], o[j + 3]);
+            v4.z = pack_bf16(o[j + 4], o[j + 5]);
+            v4.w = pack_bf16(o[j + 6], o[j + 7]);
+            *reinterpret_cast<uint4*>(op + j) = v4;
+          }
         }
       }
     }
@@ -367,7 +542,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 template <int KW>
 inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* k,
                          long long ldk, const __nv_bfloat16* v, long long ldv, Na3dParams p,
-                         cudaStream_t stream) {
+                         int sm_count, cudaStream_t stream) {
   using Cfg = Na3dCfg<KW>;
   const uint64_t chans = static_cast<uint64_t>(p.heads) * 64;
   auto make = [&](CUtensorMap* tm, const __nv_bfloat16* base, long long ld, uint32_t bw,
@@ -382,13 +557,13 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
   };
   CUtensorMap tmQ, tmK, tmV;
   if (make(&tmQ, q, ldq, NA_QW, p.QH, p.QD) != 0) return -20;
-  if (make(&tmK, k, ldk, Cfg::EW, 8, 1) != 0) return -20;
-  if (make(&tmV, v, ldv, Cfg::EW, 8, 1) != 0) return -20;
+  if (make(&tmK, k, ldk, Cfg::EWP, 8, 1) != 0) return -20;
+  if (make(&tmV, v, ldv, Cfg::EWP, 8, 1) != 0) return -20;
   auto kern = na3d_fwd_kernel<KW>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::TOTAL);
   if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
-  dim3 grid(p.tiles_d * p.tiles_h * p.tiles_w, p.heads, p.B);
+  const int grid = p.n_items < sm_count ? p.n_items : sm_count;
   kern<<<grid, NA_THREADS, Cfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
@@ -397,7 +572,7 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
 inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* k, long long ldk,
                        const __nv_bfloat16* v, long long ldv, __nv_bfloat16* out, long long ldo,
                        int B, int D, int H, int W, int heads, int kd, int kh, int kw, float scale,
-                       cudaStream_t stream) {
+                       int sm_count, cudaStream_t stream) {
   if (kd > D || kh > H || kw > W || kd < 1 || kh < 1 || kw < 1) return -1;
   if (kh > 15 || kd > 15) return -2;
   Na3dParams p{};
@@ -409,19 +584,21 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   p.tiles_d = (D + p.QD - 1) / p.QD;
   p.tiles_h = (H + p.QH - 1) / p.QH;
   p.tiles_w = (W + NA_QW - 1) / NA_QW;
+  const long long items = static_cast<long long>(p.tiles_d) * p.tiles_h * p.tiles_w * heads * B;
+  if (items > 0x7fffffffLL) return -2;
+  p.n_items = static_cast<int>(items);
   p.out = out;
   p.ldo = ldo;
   p.scale_log2e = scale * 1.4426950408889634f;
-  if (heads > 65535 || B > 65535) return -2;
   switch (kw) {
-    case 1: return launch_na3d_t<1>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 3: return launch_na3d_t<3>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 5: return launch_na3d_t<5>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 7: return launch_na3d_t<7>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 9: return launch_na3d_t<9>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 11: return launch_na3d_t<11>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 13: return launch_na3d_t<13>(q, ldq, k, ldk, v, ldv, p, stream);
-    case 15: return launch_na3d_t<15>(q, ldq, k, ldk, v, ldv, p, stream);
+    case 1: return launch_na3d_t<1>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 3: return launch_na3d_t<3>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 5: return launch_na3d_t<5>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 7: return launch_na3d_t<7>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 9: return launch_na3d_t<9>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 11: return launch_na3d_t<11>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 13: return launch_na3d_t<13>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
+    case 15: return launch_na3d_t<15>(q, ldq, k, ldk, v, ldv, p, sm_count, stream);
     default: return -2;
   }
 }
