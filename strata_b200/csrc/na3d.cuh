@@ -24,10 +24,12 @@
 //                  the two partial results are merged once per item through shared memory.
 //                  Per block: pass 1 reads the thread's S row segment from TMEM and takes the
 //                  masked maximum, pass 2 re-reads it, exponentiates, writes bf16 P into the
-//                  swizzled A-operand layout and keeps the running sum; the previous block's
-//                  P V result is read back from TMEM and accumulated in registers with the
-//                  online-softmax rescaling. Key rows no query of the warp can see are skipped
-//                  (zeros written) without touching the exponential unit.
+//                  swizzled A-operand layout and keeps the running sum. P V accumulates in TMEM
+//                  over all blocks of the item against a per-thread reference maximum; the
+//                  reference moves (and the TMEM accumulator is rescaled through tcgen05.ld /
+//                  tcgen05.st) only when a block maximum exceeds it by more than 2^8, which
+//                  after the first block or two is rare. Key rows no query of the warp can see
+//                  are skipped (zeros written) without touching the exponential unit.
 //   mask           per (query, key): the key's box coordinates must fall in the query's window
 //                  on all three axes. Columns: an additive per-thread bias vector (0 / -1e30);
 //                  rows: a per-thread bit mask; planes: one comparison per block. Border
@@ -120,6 +122,21 @@ __device__ __forceinline__ void tmem_ld_keyrow(uint32_t taddr, uint32_t (&a)[24]
     tmem_ld_x16(taddr, a);
     tmem_ld_x8(taddr + 16, a + 16);
   }
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
@@ -319,8 +336,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               const uint64_t pdesc =
                   umma_smem_desc_sw128(p_smem + (s >> 2) * 16384 + (s & 3) * 32);
               // V advances 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
+              // O accumulates in TMEM over all key blocks of the item
               umma_ss(tmem_base + NA_O_COL + 64 * g, pdesc, vdesc + 128u * s, idesc_pv,
-                      s0 != 0 ? 1u : 0u);
+                      (s0 | i) != 0 ? 1u : 0u);
             }
           }
           umma_commit(kv_empty(st));
@@ -360,10 +378,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         cb[cc] = (static_cast<unsigned>(cc - ww) < static_cast<unsigned>(KW)) ? 0.f : -1e30f;
       const uint32_t hmask_all = ((1u << p.kh) - 1u) << wh;   // bit = key row of the box
 
-      float m_run = -1e30f, l_run = 0.f, alpha_prev = 1.f;
-      float o[64];
-#pragma unroll
-      for (int j = 0; j < 64; ++j) o[j] = 0.f;
+      // Running reference m_run and sum l_run of this thread's key half. The output
+      // accumulator lives in TMEM and is touched only when the reference has to move.
+      float m_run = -1e30f, l_run = 0.f;
 
       for (int i = 0; i < nblk; ++i, ++gb) {
         const int ip = i / n_hb, hb = i - ip * n_hb;
@@ -387,36 +404,51 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint32_t a[24];
             tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
             tmem_ld_wait();
-            float rm = -1e30f;
+            float rm0 = -1e30f, rm1 = -1e30f;
 #pragma unroll
-            for (int cc = 0; cc < EW; cc += 2)
-              rm = fmax3(rm, __uint_as_float(a[cc]) + cb[cc],
-                         (cc + 1 < EW) ? __uint_as_float(a[cc + 1]) + cb[cc + 1] : -1e30f);
-            bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? rm : -1e30f);
+            for (int cc = 0; cc < EW; cc += 4) {
+              rm0 = fmax3(rm0, __uint_as_float(a[cc]) + cb[cc],
+                          __uint_as_float(a[cc + 1]) + cb[cc + 1]);
+              if (cc + 2 < EW)
+                rm1 = fmax3(rm1, __uint_as_float(a[cc + 2]) + cb[cc + 2],
+                            __uint_as_float(a[cc + 3]) + cb[cc + 3]);
+            }
+            bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
           }
         }
-        const float m_new = fmaxf(m_run, bm);
-        const float alpha = fast_exp2((m_run - m_new) * c);
-        const float mc = m_new * c;
-
-        // fold in the previous block's P V result of this key half
+        // Move the reference only when the block maximum exceeds it by more than 2^8 (P stays
+        // well inside bf16 / fp32 range otherwise) - or adopt it for free while nothing has
+        // been accumulated yet. Moving it rescales the TMEM accumulator, so it must wait for
+        // the previous block's P V.
+        const bool grow = (bm - m_run) * c > 8.0f;
+        const bool rescale = grow && l_run > 0.f;
+        if (grow && !rescale) m_run = bm;
+        // Every phase of o_full is observed in order (also when nothing is rescaled), so a
+        // parity wait can never be satisfied by an older completion.
         if (i > 0) {
           if (!mbar_wait(o_full, static_cast<uint32_t>((gb - 1) & 1), abort_flag,
                          ST_TIMEOUT_SOFTMAX)) {
             ok = false;
             break;
           }
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
           tc_fence_after();
-          uint32_t ob[32];
+          const float alpha = rescale ? fast_exp2((m_run - bm) * c) : 1.0f;
+          if (rescale) m_run = bm;
+          l_run *= alpha;
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
+            uint32_t ob[32];
             tmem_ld_32x32(o_taddr + 32 * hh, ob);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              o[32 * hh + j] = o[32 * hh + j] * alpha_prev + __uint_as_float(ob[j]);
+            for (int j = 0; j < 32; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+            tmem_st_32x32(o_taddr + 32 * hh, ob);
           }
+          tmem_st_wait();
         }
+        const float mc = m_run * c;
 
         // pass 2: exponentials, row sum, bf16 P into the swizzled A-operand layout
         float nb[EWP];
@@ -429,7 +461,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const bool need = (warp_rows >> rr) & 1u;
           const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
           uint32_t a[24];
-          float rsr = 0.f;
+          float rs0 = 0.f, rs1 = 0.f;
           if (need) {
             tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
             tmem_ld_wait();
@@ -440,9 +472,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint32_t packed = 0u;
             if (need && cc < EW) {
               const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, nb[cc]));
-              const float p1 =
-                  (cc + 1 < EW) ? fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, nb[cc + 1])) : 0.f;
-              rsr += p0 + p1;
+              const float p1 = fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, nb[cc + 1]));
+              if (cc & 2) rs1 += p0 + p1; else rs0 += p0 + p1;
               packed = pack_bf16(p0, p1) & keep;
             }
             pk[(jj >> 1) & 3] = packed;
@@ -456,11 +487,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                            : "memory");
             }
           }
-          rs += keep ? rsr : 0.f;
+          rs += keep ? (rs0 + rs1) : 0.f;
         }
-        l_run = l_run * alpha + rs;
-        m_run = m_new;
-        alpha_prev = alpha;
+        l_run += rs;
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(p_ready);
@@ -473,6 +502,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
+      float o[64];
       {
         uint32_t ob[32];
 #pragma unroll
@@ -480,8 +510,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_ld_32x32(o_taddr + 32 * hh, ob);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            o[32 * hh + j] = o[32 * hh + j] * alpha_prev + __uint_as_float(ob[j]);
+          for (int j = 0; j < 32; ++j) o[32 * hh + j] = __uint_as_float(ob[j]);
         }
       }
       tc_fence_before();
