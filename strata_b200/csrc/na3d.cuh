@@ -69,7 +69,11 @@ struct Na3dCfg {
   static constexpr int STAGES = NKEYS <= 128 ? 3 : 2;
   static constexpr int KV_OFF = 2 * Q_BYTES;
   static constexpr int P_OFF = KV_OFF + STAGES * 2 * KV_BYTES;
-  static constexpr int MERGE_OFF = P_OFF + P_ATOMS * 16384;
+  static constexpr int P_BYTES = P_ATOMS * 16384;
+  // Two P buffers when they fit: the softmax of block i+1 then never waits for P V of block i.
+  static constexpr int P_BUFS =
+      (P_OFF + 2 * P_BYTES + 128 * NA_MERGE_FLOATS * 4 + 256 <= 227 * 1024) ? 2 : 1;
+  static constexpr int MERGE_OFF = P_OFF + P_BUFS * P_BYTES;
   static constexpr int BAR_OFF = MERGE_OFF + 128 * NA_MERGE_FLOATS * 4;
   static constexpr int TOTAL = BAR_OFF + 256;
   static_assert(NKEYS % 32 == 0 && NKEYS <= NA_S1_COL, "key block must fit an S buffer");
@@ -189,12 +193,13 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto q_full = [&](int qb) { return bar + 8u * qb; };           // 0,1
   auto q_empty = [&](int qb) { return bar + 16u + 8u * qb; };    // 2,3
   auto s_full = [&](int sb) { return bar + 32u + 8u * sb; };     // 4,5
-  const uint32_t p_ready = bar + 48u, o_full = bar + 56u;        // 6,7
+  const uint32_t p_ready = bar + 48u;                            // 6
+  auto o_full = [&](uint32_t par) { return bar + 56u + 120u * par; };   // 7 and 22 (by block parity)
   const uint32_t merge_full = bar + 64u, merge_free = bar + 72u; // 8,9
   auto kv_full = [&](int st) { return bar + 80u + 8u * st; };    // 10..12
   auto kv_empty = [&](int st) { return bar + 104u + 8u * st; };  // 13..15
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 160);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 168);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 200);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -211,7 +216,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(s_full(i), 1);
     }
     mbar_init(p_ready, 256);
-    mbar_init(o_full, 1);
+    mbar_init(o_full(0), 1);
+    mbar_init(o_full(1), 1);
     mbar_init(merge_full, 128);
     mbar_init(merge_free, 128);
     for (int s = 0; s < STAGES; ++s) {
@@ -238,26 +244,27 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmV);
       bool ok = true;
       int n = 0;
-      long long gb = 0;
+      int st = 0;
+      uint32_t ph = 0;
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
         const NaItem it = na_decode_item<KW>(item, p);
         const int qb = n & 1;
         if (!mbar_wait(q_empty(qb), ((n >> 1) & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(q_full(qb), Cfg::Q_BYTES);
         tma_load_5d(q_smem(qb), &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full(qb));
-        for (int i = 0; i < nblk; ++i, ++gb) {
-          const int st = static_cast<int>(gb % STAGES);
-          const uint32_t ph = static_cast<uint32_t>((gb / STAGES) & 1);
+        int ip = 0, hb = 0;
+        for (int i = 0; i < nblk; ++i) {
           if (!mbar_wait(kv_empty(st), ph ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
-          const int ip = i / n_hb, hb = i - ip * n_hb;
           mbar_expect_tx(kv_full(st), 2 * Cfg::KV_BYTES);
           tma_load_5d(k_smem(st), &tmK, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
                       kv_full(st));
           tma_load_5d(v_smem(st), &tmV, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
                       kv_full(st));
+          if (++hb == n_hb) { hb = 0; ++ip; }
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
         }
       }
       if (!ok)
@@ -265,84 +272,95 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // One thread issues every MMA, so its instruction stream is kept short: descriptors are
+    // two 32-bit halves (a constant high word, a low word that is a base plus compile-time
+    // offsets), ring positions are carried incrementally.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NKEYS, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, false, true);
       constexpr int HALF_STEPS = EWP / 4;  // 16-key MMA steps per key half
-      auto issue_qk = [&](uint32_t qaddr, long long g) {
-        const int st = static_cast<int>(g % STAGES);
-        const uint64_t qdesc = umma_smem_desc_sw128(qaddr);
-        const uint64_t kdesc = umma_smem_desc_sw128(k_smem(st));
-        const uint32_t s_tmem = tmem_base + ((g & 1) ? NA_S1_COL : 0);
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t STAGE_UNITS = (2 * Cfg::KV_BYTES) >> 4;
+      auto lo_of = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };
+      auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(DESC_HI) << 32) | lo; };
+      const uint32_t q_lo[2] = {lo_of(q_smem(0)), lo_of(q_smem(1))};
+      const uint32_t k_lo0 = lo_of(k_smem(0));
+      const uint32_t v_lo0 = lo_of(v_smem(0));
+      const uint32_t p_lo = lo_of(p_smem);
+      const uint32_t o_tmem = tmem_base + NA_O_COL;
+
+      // position of the next Q K^T to issue (runs one block ahead of the P V position)
+      int qk_st = 0;
+      uint32_t qk_ph = 0, qk_sb = 0;
+      auto issue_qk = [&](uint32_t qlo) -> bool {
+        if (!mbar_wait(kv_full(qk_st), qk_ph, abort_flag, ST_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t klo = k_lo0 + qk_st * STAGE_UNITS;
+        const uint32_t s_tmem = tmem_base + (qk_sb ? NA_S1_COL : 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_ss(s_tmem, qdesc + 2u * k, kdesc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
-        umma_commit(s_full(static_cast<int>(g & 1)));
+          umma_ss(s_tmem, desc(qlo + 2u * k), desc(klo + 2u * k), idesc_qk, k != 0 ? 1u : 0u);
+        umma_commit(s_full(static_cast<int>(qk_sb)));
+        qk_sb ^= 1u;
+        if (++qk_st == STAGES) { qk_st = 0; qk_ph ^= 1u; }
+        return true;
       };
-      auto wait_kv = [&](long long g) {
-        const int st = static_cast<int>(g % STAGES);
-        return mbar_wait(kv_full(st), static_cast<uint32_t>((g / STAGES) & 1), abort_flag,
-                         ST_TIMEOUT_MMA);
-      };
+
       bool ok = true;
       int n = 0;
-      long long gb = 0;
-      // Invariant at the top of an item: S for its block 0 has NOT been issued yet unless
-      // `pre_issued` (it is issued at the end of the previous item to keep the pipe full).
-      bool pre_issued = false;
+      int pv_st = 0;
+      uint32_t pv_par = 0;     // block parity of the next P V (p_ready phase, P buffer, o_full)
+      bool pre_issued = false; // S of this item's block 0 was issued at the end of the previous item
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
         const int qb = n & 1;
         if (!pre_issued) {
           if (!mbar_wait(q_full(qb), (n >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
-          if (!wait_kv(gb)) break;
-          tc_fence_after();
-          issue_qk(q_smem(qb), gb);
+          if (!issue_qk(q_lo[qb])) break;
         }
         pre_issued = false;
-        for (int i = 0; i < nblk; ++i, ++gb) {
+        for (int i = 0; i < nblk; ++i) {
           // run ahead: S of the next block (of this item, or block 0 of the next item)
           if (i + 1 < nblk) {
-            if (!wait_kv(gb + 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_qk(q_smem(qb), gb + 1);
+            if (!issue_qk(q_lo[qb])) { ok = false; break; }
             if (i + 2 == nblk) umma_commit(q_empty(qb));   // last Q K^T of this item issued
           } else {
             if (nblk == 1) umma_commit(q_empty(qb));
-            const int next = item + gridDim.x;
-            if (next < p.n_items) {
+            if (item + static_cast<int>(gridDim.x) < p.n_items) {
               const int nq = (n + 1) & 1;
               if (!mbar_wait(q_full(nq), ((n + 1) >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) {
                 ok = false;
                 break;
               }
-              if (!wait_kv(gb + 1)) { ok = false; break; }
-              tc_fence_after();
-              issue_qk(q_smem(nq), gb + 1);
+              if (!issue_qk(q_lo[nq])) { ok = false; break; }
               pre_issued = true;
             }
           }
-          if (!mbar_wait(p_ready, static_cast<uint32_t>(gb & 1), abort_flag, ST_TIMEOUT_MMA)) {
+          if (!mbar_wait(p_ready, pv_par, abort_flag, ST_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const int st = static_cast<int>(gb % STAGES);
-          const uint64_t vdesc = umma_smem_desc_sw128(v_smem(st));
+          const uint32_t vlo = v_lo0 + pv_st * STAGE_UNITS;
+          const uint32_t plo =
+              p_lo + ((Cfg::P_BUFS == 2 && pv_par) ? static_cast<uint32_t>(Cfg::P_BYTES >> 4) : 0u);
+          const uint32_t acc = i != 0 ? 1u : 0u;   // O accumulates over the blocks of the item
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
 #pragma unroll
             for (int s0 = 0; s0 < HALF_STEPS; ++s0) {
+              constexpr int dummy = 0;
+              (void)dummy;
               const int s = g * HALF_STEPS + s0;
-              const uint64_t pdesc =
-                  umma_smem_desc_sw128(p_smem + (s >> 2) * 16384 + (s & 3) * 32);
-              // V advances 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
-              // O accumulates in TMEM over all key blocks of the item
-              umma_ss(tmem_base + NA_O_COL + 64 * g, pdesc, vdesc + 128u * s, idesc_pv,
-                      (s0 | i) != 0 ? 1u : 0u);
+              // P: 64-key atoms of 16 KB, 32 bytes per 16-key step inside an atom;
+              // V: 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
+              umma_ss(o_tmem + 64 * g, desc(plo + (s >> 2) * 1024u + (s & 3) * 2u),
+                      desc(vlo + 128u * s), idesc_pv, s0 != 0 ? 1u : acc);
             }
           }
-          umma_commit(kv_empty(st));
-          umma_commit(o_full);
+          umma_commit(kv_empty(pv_st));
+          umma_commit(o_full(pv_par));
+          pv_par ^= 1u;
+          if (++pv_st == STAGES) pv_st = 0;
         }
       }
     }
@@ -363,7 +381,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     bool ok = true;
     int n = 0;
-    long long gb = 0;
+    uint32_t gb = 0;
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
       const NaItem it = na_decode_item<KW>(item, p);
       const bool q_ok = (it.d0 + zd < p.D) && (it.h0 + zh < p.H) && (it.w0 + zw < p.W);
@@ -382,16 +400,16 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // accumulator lives in TMEM and is touched only when the reference has to move.
       float m_run = -1e30f, l_run = 0.f;
 
+      int ip = 0, hb = 0;
       for (int i = 0; i < nblk; ++i, ++gb) {
-        const int ip = i / n_hb, hb = i - ip * n_hb;
-        const int sb = static_cast<int>(gb & 1);
-        if (!mbar_wait(s_full(sb), static_cast<uint32_t>((gb >> 1) & 1), abort_flag,
-                       ST_TIMEOUT_SOFTMAX)) {
+        const int sb = static_cast<int>(gb & 1u);
+        if (!mbar_wait(s_full(sb), (gb >> 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t s_taddr = lane_taddr + (sb ? NA_S1_COL : 0) + grp * GKEYS;
+        const uint32_t p_row_b = p_row + ((Cfg::P_BUFS == 2 && sb) ? Cfg::P_BYTES : 0);
         const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
         const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + 4 * grp)) & 0xfu) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
@@ -423,16 +441,26 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool grow = (bm - m_run) * c > 8.0f;
         const bool rescale = grow && l_run > 0.f;
         if (grow && !rescale) m_run = bm;
-        // Every phase of o_full is observed in order (also when nothing is rescaled), so a
-        // parity wait can never be satisfied by an older completion.
-        if (i > 0) {
-          if (!mbar_wait(o_full, static_cast<uint32_t>((gb - 1) & 1), abort_flag,
+        // o_full[par] completes once per block of that parity. With two P buffers the softmax
+        // waits for it only when it must touch the accumulator; with one P buffer it also
+        // guards the buffer against being overwritten while P V of the previous block reads it.
+        bool o_waited = false;
+        if (Cfg::P_BUFS == 1 && i > 0) {
+          if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
                          ST_TIMEOUT_SOFTMAX)) {
             ok = false;
             break;
           }
+          o_waited = true;
         }
         if (__any_sync(0xffffffffu, rescale)) {
+          if (!o_waited) {
+            if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
+                           ST_TIMEOUT_SOFTMAX)) {
+              ok = false;
+              break;
+            }
+          }
           tc_fence_after();
           const float alpha = rescale ? fast_exp2((m_run - bm) * c) : 1.0f;
           if (rescale) m_run = bm;
@@ -480,7 +508,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if ((jj & 7) == 6) {
               const int j = grp * GKEYS + jj;   // key index within the block
               const uint32_t addr =
-                  p_row + static_cast<uint32_t>(j >> 6) * 16384u +
+                  p_row_b + static_cast<uint32_t>(j >> 6) * 16384u +
                   ((static_cast<uint32_t>((j & 63) >> 3) ^ sw) << 4);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]),
                            "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
@@ -493,11 +521,13 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(p_ready);
+        if (++hb == n_hb) { hb = 0; ++ip; }
       }
       if (!ok) break;
 
       // item epilogue: last P V, merge the two key halves, normalise, store
-      if (!mbar_wait(o_full, static_cast<uint32_t>((gb - 1) & 1), abort_flag, ST_TIMEOUT_SOFTMAX)) {
+      if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
+                     ST_TIMEOUT_SOFTMAX)) {
         ok = false;
         break;
       }

@@ -1,0 +1,96 @@
+"""One model step over a tiled cubed sphere: halo exchange -> network on padded tiles -> crop.
+
+This is the body of the reference's distributed rollout loop
+(scripts/ace/run_screamcast_nudged.py:452-477: `x_with_halo = pad(x)`, `model(x_with_halo)`,
+`unpad(out)`) with this package's pieces: the peer-memory copy halo
+(strata_b200/halo.py) in place of the all-gather + regrid, the sm_100a backbone in place of
+physicsnemo + NATTEN, and `TileTopology.crop` as the un-pad. Tiles are the batch dimension of the
+network, exactly as the reference feeds faces/tiles as batch entries.
+
+Also here: a synthetic equiangular cubed-sphere lat/lon generator, standing in for the grid
+files (`ne1024pg2_scrip.nc`, ...) that are not distributed with the reference.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from .halo import DistributedTileCopyHaloPadding
+from .topology import TileTopology, apply_maps_numpy, halo_source_maps
+
+
+def equiangular_cubed_sphere_latlon(n: int):
+    """(lat, lon) in degrees, each [6, n, n], of cell centres of an equiangular gnomonic cubed
+    sphere. Faces 0-3 run around the equator (centre longitudes 0, 90, 180, 270), face 4 is the
+    south cap, face 5 the north cap; rows grow northwards on the equatorial faces."""
+    ang = (np.arange(n) + 0.5) / n * (math.pi / 2) - math.pi / 4
+    a, b = np.meshgrid(np.tan(ang), np.tan(ang), indexing="xy")   # a: column (east), b: row (north)
+    lat = np.empty((6, n, n))
+    lon = np.empty((6, n, n))
+    for f in range(4):
+        x, y, z = np.ones_like(a), a, b
+        lon[f] = np.degrees(np.arctan2(y, x)) + 90.0 * f
+        lat[f] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    # caps: local axes chosen so that the bottom edge of the north cap meets face 0's top edge
+    x, y, z = -b, a, np.ones_like(a)
+    lon[5] = np.degrees(np.arctan2(y, x))
+    lat[5] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    x, y, z = b, a, -np.ones_like(a)
+    lon[4] = np.degrees(np.arctan2(y, x))
+    lat[4] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    return lat, np.mod(lon, 360.0)
+
+
+def padded_tile_latlon(topology: TileTopology):
+    """lat/lon (degrees) of this rank's padded tiles [tiles_per_rank, P, P]: interior cells
+    from the synthetic grid, halo cells copied from the neighbouring tile / face like any other
+    field (so a halo cell carries the coordinates of the cell whose data it receives)."""
+    lat, lon = equiangular_cubed_sphere_latlon(topology.face_size)
+    full = TileTopology(1, 0, topology.face_size, topology.tile_size, topology.halo_width)
+    T = topology.tile_size
+
+    def tiles(g):
+        return np.stack([g[f, ti * T:(ti + 1) * T, tj * T:(tj + 1) * T]
+                         for f, ti, tj in full.global_tiles])
+    a, b = halo_source_maps(topology)
+    # corner diagonals average two cells; do it on unit vectors to stay clear of the lon seam
+    la, lo = np.radians(tiles(lat)), np.radians(tiles(lon))
+    xyz = np.stack([np.cos(la) * np.cos(lo), np.cos(la) * np.sin(lo), np.sin(la)])
+    pad = apply_maps_numpy(xyz, a, b)
+    plat = np.degrees(np.arctan2(pad[2], np.hypot(pad[0], pad[1])))
+    plon = np.mod(np.degrees(np.arctan2(pad[1], pad[0])), 360.0)
+    return plat, plon
+
+
+class TiledSphereStepper(torch.nn.Module):
+    """halo exchange -> network -> crop for this rank's tiles.
+
+    forward(x[C, D, tiles_per_rank, T, T] fp32) -> [C_out, D, tiles_per_rank, T, T].
+    `network` follows the wrapper contract `network(x[B, C, D, H, W], index)` with
+    `index = {"lat", "lon"}` in radians (index_is_latlon=True) and tile size T + 2*halo.
+    """
+
+    def __init__(self, network: torch.nn.Module, topology: TileTopology, device=None, group=None):
+        super().__init__()
+        self.network = network
+        self.topology = topology
+        plat, plon = padded_tile_latlon(topology)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.halo = DistributedTileCopyHaloPadding(
+            topology=topology, lat_deg=torch.from_numpy(plat).float().to(dev),
+            lon_deg=torch.from_numpy(plon).float().to(dev), device=dev, group=group)
+        self.register_buffer("lat_rad", torch.deg2rad(self.halo.lat_deg), persistent=False)
+        self.register_buffer("lon_rad", torch.deg2rad(self.halo.lon_deg), persistent=False)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        padded = self.halo(x)                                   # [C, D, tpr, P, P]
+        xin = padded.permute(2, 0, 1, 3, 4).contiguous()        # tiles become the batch
+        y = self.network(xin, {"lat": self.lat_rad, "lon": self.lon_rad})
+        y = self.topology.crop(y)                               # [tpr, C_out, D, T, T]
+        return y.permute(1, 2, 0, 3, 4).contiguous()
+
+    def close(self):
+        self.halo.close()
