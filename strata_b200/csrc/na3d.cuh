@@ -38,6 +38,10 @@
 #include "common.cuh"
 #include "tensormap.cuh"
 
+#ifndef NA_HOLD_MAX_EWP
+#define NA_HOLD_MAX_EWP 0
+#endif
+
 namespace strata {
 
 struct Na3dParams {
@@ -111,7 +115,7 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
 }
 // Loads EWP (8, 12, 16, 20 or 24) consecutive S columns of this thread's row.
 template <int EWP>
-__device__ __forceinline__ void tmem_ld_keyrow(uint32_t taddr, uint32_t (&a)[24]) {
+__device__ __forceinline__ void tmem_ld_keyrow(uint32_t taddr, uint32_t* a) {
   if constexpr (EWP == 8) {
     tmem_ld_x8(taddr, a);
   } else if constexpr (EWP == 12) {
@@ -193,7 +197,11 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto q_full = [&](int qb) { return bar + 8u * qb; };           // 0,1
   auto q_empty = [&](int qb) { return bar + 16u + 8u * qb; };    // 2,3
   auto s_full = [&](int sb) { return bar + 32u + 8u * sb; };     // 4,5
-  const uint32_t p_ready = bar + 48u;                            // 6
+  // p_ready alternates by block parity: a fast softmax warp may finish block i+1 before a slow
+  // one has finished block i (it cannot reach block i+2 before every warp has arrived for
+  // block i, because S of block i+2 is only issued after that), so two barriers keep the
+  // arrivals of consecutive blocks apart.
+  auto p_ready = [&](uint32_t par) { return bar + 48u + 136u * par; };   // 6 and 23
   auto o_full = [&](uint32_t par) { return bar + 56u + 120u * par; };   // 7 and 22 (by block parity)
   const uint32_t merge_full = bar + 64u, merge_free = bar + 72u; // 8,9
   auto kv_full = [&](int st) { return bar + 80u + 8u * st; };    // 10..12
@@ -215,7 +223,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(q_empty(i), 1);
       mbar_init(s_full(i), 1);
     }
-    mbar_init(p_ready, 256);
+    mbar_init(p_ready(0), 256);
+    mbar_init(p_ready(1), 256);
     mbar_init(o_full(0), 1);
     mbar_init(o_full(1), 1);
     mbar_init(merge_full, 128);
@@ -309,7 +318,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool ok = true;
       int n = 0;
       int pv_st = 0;
-      uint32_t pv_par = 0;     // block parity of the next P V (p_ready phase, P buffer, o_full)
+      uint32_t pv_par = 0;     // block parity of the next P V (p_ready / o_full barrier, P buffer)
+      uint32_t pv_cnt = 0;     // number of P V blocks issued so far
       bool pre_issued = false; // S of this item's block 0 was issued at the end of the previous item
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
         const int qb = n & 1;
@@ -335,7 +345,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               pre_issued = true;
             }
           }
-          if (!mbar_wait(p_ready, pv_par, abort_flag, ST_TIMEOUT_MMA)) {
+          if (!mbar_wait(p_ready(pv_par), (pv_cnt >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
@@ -360,6 +370,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_commit(kv_empty(pv_st));
           umma_commit(o_full(pv_par));
           pv_par ^= 1u;
+          ++pv_cnt;
           if (++pv_st == STAGES) pv_st = 0;
         }
       }
@@ -414,22 +425,34 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + 4 * grp)) & 0xfu) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
 
-        // pass 1: masked row maximum over this thread's key rows
+        // pass 1: masked row maximum over this thread's key rows. For key rows of at most 16
+        // columns all visible rows are fetched from TMEM at once and stay in registers for
+        // pass 2; wider rows are fetched row by row in both passes.
+        constexpr bool HOLD = (EWP <= NA_HOLD_MAX_EWP);
+        uint32_t a[HOLD ? 4 : 1][EWP];
+        if constexpr (HOLD) {
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr)
+            if ((warp_rows >> rr) & 1u) tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a[rr]);
+          tmem_ld_wait();
+        }
         float bm = -1e30f;
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) {
           if ((warp_rows >> rr) & 1u) {
-            uint32_t a[24];
-            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
-            tmem_ld_wait();
+            uint32_t* ar = a[HOLD ? rr : 0];
+            if constexpr (!HOLD) {
+              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, ar);
+              tmem_ld_wait();
+            }
             float rm0 = -1e30f, rm1 = -1e30f;
 #pragma unroll
             for (int cc = 0; cc < EW; cc += 4) {
-              rm0 = fmax3(rm0, __uint_as_float(a[cc]) + cb[cc],
-                          __uint_as_float(a[cc + 1]) + cb[cc + 1]);
+              rm0 = fmax3(rm0, __uint_as_float(ar[cc]) + cb[cc],
+                          __uint_as_float(ar[cc + 1]) + cb[cc + 1]);
               if (cc + 2 < EW)
-                rm1 = fmax3(rm1, __uint_as_float(a[cc + 2]) + cb[cc + 2],
-                            __uint_as_float(a[cc + 3]) + cb[cc + 3]);
+                rm1 = fmax3(rm1, __uint_as_float(ar[cc + 2]) + cb[cc + 2],
+                            __uint_as_float(ar[cc + 3]) + cb[cc + 3]);
             }
             bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
           }
@@ -488,19 +511,21 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int rr = 0; rr < 4; ++rr) {
           const bool need = (warp_rows >> rr) & 1u;
           const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
-          uint32_t a[24];
+          uint32_t* ar = a[HOLD ? rr : 0];
           float rs0 = 0.f, rs1 = 0.f;
-          if (need) {
-            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
-            tmem_ld_wait();
+          if constexpr (!HOLD) {
+            if (need) {
+              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, ar);
+              tmem_ld_wait();
+            }
           }
 #pragma unroll
           for (int cc = 0; cc < EWP; cc += 2) {
             const int jj = rr * EWP + cc;   // even, compile-time
             uint32_t packed = 0u;
             if (need && cc < EW) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, nb[cc]));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, nb[cc + 1]));
+              const float p0 = fast_exp2(fmaf(__uint_as_float(ar[cc]), c, nb[cc]));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(ar[cc + 1]), c, nb[cc + 1]));
               if (cc & 2) rs1 += p0 + p1; else rs0 += p0 + p1;
               packed = pack_bf16(p0, p1) & keep;
             }
@@ -520,7 +545,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l_run += rs;
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(p_ready);
+        mbar_arrive(p_ready(gb & 1u));
         if (++hb == n_hb) { hb = 0; ++ip; }
       }
       if (!ok) break;
