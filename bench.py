@@ -255,6 +255,12 @@ def run_gpu_arm(args):
     ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
     e2e_value = tokens_job / (ms_e2e * 1e-3)
 
+    # secondary metric: one model step over a whole tiled cubed sphere, tiles sharded over ranks
+    try:
+        sphere = sphere_step_bench(torch, dist, world, rank, dev, timed)
+    except Exception as exc:  # reported, never fatal for the headline line
+        sphere = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     # per-kernel breakdown (same sequence as strata_block_forward_bf16, one event pair each)
     breakdown = kernel_breakdown(torch, ops, x, weights, cos, sin, (D, H, W), heads, kernel, hidden)
 
@@ -284,11 +290,55 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world},
+            "sphere_step": sphere,
             "gpu_launches": 7 * args.steps, "device_status": status, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+SPHERE = dict(faces=6, face_tokens=128, tile_tokens=64, halo_tokens=8, depth=16, dim=512, heads=8,
+              kernel=[3, 9, 9], blocks=2, channels=8)
+
+
+def sphere_step_bench(torch, dist, world, rank, dev, timed, steps=3):
+    """Strong-scaling companion metric: halo exchange (peer memory) + 2-block backbone on the
+    padded tiles + crop, for 24 tiles of 16x64x64 tokens with an 8-token halo."""
+    from strata_b200.rollout import TiledSphereStepper
+    from strata_b200.topology import TileTopology
+    from strata_b200.wrappers import StrataBackboneModel
+    c = SPHERE
+    topo = TileTopology(world, rank, c["face_tokens"], c["tile_tokens"], c["halo_tokens"])
+    P = topo.padded_tile_size
+    torch.manual_seed(7)
+    net = StrataBackboneModel(depth=c["depth"], height=P, width=P, n_layers=c["blocks"], patch_size=1,
+                              in_chans=c["channels"], base_out_chans=c["channels"],
+                              embed_dim=c["dim"], num_heads=c["heads"], attn_kernel=tuple(c["kernel"]),
+                              do_rope_2d_stereographic=True, index_is_latlon=True,
+                              do_bf16_mixed=True).to(dev).eval()
+    stepper = TiledSphereStepper(net, topo, device=dev)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(c["channels"], c["depth"], topo.tiles_per_rank, c["tile_tokens"], c["tile_tokens"],
+                    device=dev, generator=g)
+    state = {"x": x}
+
+    def step():
+        state["x"] = stepper(state["x"]).clamp_(-10, 10)
+    for _ in range(2):
+        step()
+    ms = timed(step, steps) / steps
+    stepper.halo.check_status()
+    # halo exchange alone
+    ms_halo = timed(lambda: stepper.halo(x), 5) / 5
+    halo_bytes = x.numel() // (c["tile_tokens"] ** 2) * (P * P + c["tile_tokens"] ** 2) * 4
+    out = dict(ms_per_step=ms, halo_ms=ms_halo, halo_gbs=halo_bytes / (ms_halo * 1e-3) / 1e9,
+               scaling="strong", config=c, tiles_per_rank=topo.tiles_per_rank,
+               padded_tokens_per_step=topo.total_tiles * c["depth"] * P * P)
+    stepper.close()
+    del stepper, net
+    torch.cuda.empty_cache()
+    return out
 
 
 def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidden, iters=5,

@@ -278,3 +278,69 @@ def block_flops_per_token(C: int, kernel, mlp_ratio: float = 4.0, gated: bool = 
     """Algorithmic flop per token per block: 24 C^2 + 4 K C (+ 2 C^2 if gated) at ratio 4."""
     K = kernel[0] * kernel[1] * kernel[2]
     return 6 * C * C + 4 * K * C + 2 * C * C + 4 * mlp_ratio * C * C + (2 * C * C if gated else 0)
+
+
+# --------------------------------------------------------------------------- whole backbone
+def backbone_forward(x: torch.Tensor, state: dict, *, patch, num_heads: int, kernel, num_layers: int,
+                     lat: torch.Tensor, lon: torch.Tensor, rope_mode: str = "stereographic",
+                     rope_length_scale: float | None = None, rope_base: float = 100.0,
+                     qk_norm: bool = False, gated: bool = False, concat_latitude: bool = True,
+                     wind_channels=None, alt_depthwise: bool = False, emulate_bf16: bool = False):
+    """Single-stage model: the wrapper's pre/post-processing (wind rotation, cos/sin(lat)
+    concat: screamcast/strata_wrappers.py:206-249) around patch embed -> blocks -> final layer.
+
+    x [B, C, D, H, W] fp32; lat/lon [B, H, W] radians; state: a `strata.*` state dict
+    (parameter names of tests/regression_data/sweep1_*.param_order.txt).
+    """
+    from oracle import halo_oracle as ho
+    B, _, D, H, W = x.shape
+    pv, ph, pw = patch
+    x = x.float()
+    lat_lon = None
+    if wind_channels is not None:
+        u, v = wind_channels
+        lat0, lon0 = ho.tile_center(lat.numpy(), lon.numpy())
+        ul, vl = ho.forward_uv_to_tile(x[:, u].numpy(), x[:, v].numpy(), lat.numpy(), lon.numpy(),
+                                       lat0, lon0)
+        x = x.clone()
+        x[:, u], x[:, v] = torch.from_numpy(ul), torch.from_numpy(vl)
+        lat_lon = (lat0, lon0)
+    if concat_latitude:
+        le = lat[:, None, None].expand(B, 1, D, H, W)
+        x = torch.cat([x, torch.cos(le), torch.sin(le)], dim=1)
+    r = lambda t: _round(t, emulate_bf16)
+    w = state["strata.patch_embed.proj.weight"].float()
+    t = F.conv3d(r(x), _weight(w, emulate_bf16), state["strata.patch_embed.proj.bias"].float(),
+                 stride=patch)
+    C = t.shape[1]
+    grid = (D // pv, H // ph, W // pw)
+    t = r(t.flatten(2).transpose(1, 2))
+    hd = C // num_heads
+    if rope_mode == "stereographic":
+        scale = rope_length_scale if rope_length_scale else default_rope_length_scale(1) * ph
+        cos, sin = stereographic_rope_tables(lat, lon, hd, ph, scale, rope_base)
+    elif rope_mode == "axial":
+        cos, sin = axial_rope_tables(grid[1], grid[2], hd, rope_base)
+    else:
+        cos = sin = None
+    kernel = (kernel,) * 3 if isinstance(kernel, int) else tuple(kernel)
+    for i in range(num_layers):
+        p = {k[len(f"strata.blocks.{i}."):]: v for k, v in state.items()
+             if k.startswith(f"strata.blocks.{i}.")}
+        k_i = (kernel[0], 1, 1) if (alt_depthwise and i % 2 == 1) else kernel
+        t = block_forward(t, p, grid=grid, num_heads=num_heads, kernel=k_i, rope_cos=cos,
+                          rope_sin=sin, qk_norm=qk_norm, gated=gated, emulate_bf16=emulate_bf16)
+    y = F.layer_norm(t, (C,), eps=LN_EPS)
+    y = F.linear(y, state["strata.final_layer.linear.weight"].float(),
+                 state["strata.final_layer.linear.bias"].float())
+    c_out = y.shape[-1] // (pv * ph * pw)
+    d, h, wd = grid
+    y = y.reshape(B, d, h, wd, pv, ph, pw, c_out).permute(0, 7, 1, 4, 2, 5, 3, 6)
+    y = y.reshape(B, c_out, D, H, W)
+    if wind_channels is not None:
+        u, v = wind_channels
+        ug, vg = ho.inverse_tile_to_uv(y[:, u].numpy(), y[:, v].numpy(), lat.numpy(), lon.numpy(),
+                                       *lat_lon)
+        y = y.clone()
+        y[:, u], y[:, v] = torch.from_numpy(ug), torch.from_numpy(vg)
+    return y

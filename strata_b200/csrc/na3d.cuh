@@ -3,44 +3,46 @@
 // window, times v. Windows keep their full size at the borders: along an axis of length L
 // the window of query i starts at clamp(i - k/2, 0, L - k).
 //
-// Work decomposition (persistent kernel, one CTA per SM, 10 warps)
+// Work decomposition (persistent kernel, one CTA per SM)
 //   work item      one tile of 128 queries (QD x QH x 8 tokens) of one head of one batch entry;
 //                  CTA c handles items c, c + gridDim.x, ... (neighbouring items are
 //                  neighbouring tiles of the same head, so their key halos meet in L2).
 //   key blocks     the union of a tile's windows is a box of ED x EH x EW keys
 //                  (E* = Q* + k* - 1) starting at the window start of the tile's first query.
 //                  It is streamed as blocks of one depth plane x 8 rows x EWP columns
-//                  (EWP = EW rounded up to a multiple of 4, NKEYS = 8*EWP); TMA zero-fills
-//                  whatever lies outside the tensor.
+//                  (EWP = EW padded, NKEYS = 8*EWP <= 192); TMA zero-fills whatever lies
+//                  outside the tensor.
 //   warp 0         TMA producer: Q tile (double-buffered across items) and the K / V blocks into
 //                  a 2-3 stage ring (5-D tensor maps over [B, D, H, W, channels]; 128-byte
 //                  swizzle, a key's 64 channels are one 128-byte row). Runs ahead across items.
 //   warp 1         MMA issuer: S = Q K^T (M=128, N=NKEYS, K=64) into one of two TMEM buffers -
 //                  block i+1 is issued before the softmax of block i has finished - then
-//                  O_g = P_g V_g (M=128, N=64) for each of the two key halves g.
-//   warps 2-9      softmax, two warpgroups. A query row is shared by one thread of each group;
-//                  group g owns key rows [4g, 4g+4) of every block, keeps its own running
-//                  max / sum / 64-wide output accumulator for them (no exchange per block), and
-//                  the two partial results are merged once per item through shared memory.
-//                  Per block: pass 1 reads the thread's S row segment from TMEM and takes the
-//                  masked maximum, pass 2 re-reads it, exponentiates, writes bf16 P into the
-//                  swizzled A-operand layout and keeps the running sum. P V accumulates in TMEM
-//                  over all blocks of the item against a per-thread reference maximum; the
-//                  reference moves (and the TMEM accumulator is rescaled through tcgen05.ld /
-//                  tcgen05.st) only when a block maximum exceeds it by more than 2^8, which
-//                  after the first block or two is rare. Key rows no query of the warp can see
-//                  are skipped (zeros written) without touching the exponential unit.
+//                  O_g += P_g V_g (M=128, N=64) for each key group g; O_g stays in TMEM for
+//                  the whole item.
+//   softmax warps  NG groups of 4 warps (NG = 4 for key blocks of up to 128 keys, else 2). A
+//                  query row is shared by one thread of each group; group g owns key rows
+//                  [g*8/NG, (g+1)*8/NG) of every block and keeps its own reference maximum and
+//                  running sum for them - no exchange between groups per block. Per block:
+//                  pass 1 reads the thread's S row segments from TMEM and takes the masked
+//                  maximum, pass 2 re-reads them, exponentiates, writes bf16 P into the
+//                  swizzled A-operand layout (double-buffered) and adds to the running sum.
+//                  The reference maximum moves (and the group's TMEM accumulator is rescaled
+//                  through tcgen05.ld / tcgen05.st) only when a block maximum exceeds it by
+//                  more than 2^8, which after the first block or two is rare. Key rows no query
+//                  of the warp can see are skipped (zeros written) without touching the
+//                  exponential unit. At the end of an item the groups publish (max, sum) in
+//                  shared memory, and every thread combines the NG accumulators of its row
+//                  straight from TMEM for its own slice of the 64 output channels.
 //   mask           per (query, key): the key's box coordinates must fall in the query's window
 //                  on all three axes. Columns: an additive per-thread bias vector (0 / -1e30);
 //                  rows: a per-thread bit mask; planes: one comparison per block. Border
 //                  clamping is therefore exact per query row.
+//   barriers       all mbarrier waits are bounded. Barriers that consecutive blocks would
+//                  otherwise share (S full, P ready, O full) alternate by block parity, so an
+//                  arrival for block i+1 can never be counted for block i.
 #pragma once
 #include "common.cuh"
 #include "tensormap.cuh"
-
-#ifndef NA_HOLD_MAX_EWP
-#define NA_HOLD_MAX_EWP 0
-#endif
 
 namespace strata {
 
@@ -55,32 +57,35 @@ struct Na3dParams {
   float scale_log2e;
 };
 
-constexpr int NA_THREADS = 320;
 constexpr int NA_QW = 8;
 constexpr int NA_TMEM_COLS = 512;
-constexpr int NA_S1_COL = 192;
-constexpr int NA_O_COL = 384;   // O of key half 0; half 1 at +64
-constexpr int NA_MERGE_FLOATS = 66;
 
 template <int KW>
 struct Na3dCfg {
   static constexpr int EW = NA_QW + KW - 1;
-  static constexpr int EWP = (EW + 3) / 4 * 4;
+  static constexpr int NG = (EW <= 16) ? 4 : 2;                 // softmax groups
+  static constexpr int EWP = (NG == 4) ? (EW + 7) / 8 * 8 : (EW + 3) / 4 * 4;
   static constexpr int NKEYS = 8 * EWP;
+  static constexpr int RPG = 8 / NG;                            // key rows per group
+  static constexpr int GKEYS = RPG * EWP;                       // keys per group per block
+  static constexpr int THREADS = 64 + 128 * NG;
+  static constexpr int SCOLS = (NG == 4) ? 128 : 192;           // TMEM columns per S buffer
+  static constexpr int O_COL = 2 * SCOLS;                       // O of group g at O_COL + 64 g
   static constexpr int KV_BYTES = NKEYS * 128;
   static constexpr int P_ATOMS = (NKEYS + 63) / 64;
+  static constexpr int P_BYTES = P_ATOMS * 16384;
   static constexpr int Q_BYTES = 128 * 128;
   static constexpr int STAGES = NKEYS <= 128 ? 3 : 2;
   static constexpr int KV_OFF = 2 * Q_BYTES;
   static constexpr int P_OFF = KV_OFF + STAGES * 2 * KV_BYTES;
-  static constexpr int P_BYTES = P_ATOMS * 16384;
   // Two P buffers when they fit: the softmax of block i+1 then never waits for P V of block i.
   static constexpr int P_BUFS =
-      (P_OFF + 2 * P_BYTES + 128 * NA_MERGE_FLOATS * 4 + 256 <= 227 * 1024) ? 2 : 1;
-  static constexpr int MERGE_OFF = P_OFF + P_BUFS * P_BYTES;
-  static constexpr int BAR_OFF = MERGE_OFF + 128 * NA_MERGE_FLOATS * 4;
+      (P_OFF + 2 * P_BYTES + 2 * NG * 128 * 8 + 256 <= 227 * 1024) ? 2 : 1;
+  static constexpr int ML_OFF = P_OFF + P_BUFS * P_BYTES;       // [2][NG][128] (max, sum)
+  static constexpr int BAR_OFF = ML_OFF + 2 * NG * 128 * 8;
   static constexpr int TOTAL = BAR_OFF + 256;
-  static_assert(NKEYS % 32 == 0 && NKEYS <= NA_S1_COL, "key block must fit an S buffer");
+  static_assert(NKEYS <= SCOLS && GKEYS % 16 == 0, "key block layout");
+  static_assert(O_COL + 64 * NG <= NA_TMEM_COLS, "TMEM budget");
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
@@ -143,6 +148,15 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -173,7 +187,7 @@ __device__ __forceinline__ NaItem na_decode_item(int item, const Na3dParams& p) 
 }
 
 template <int KW>
-__global__ void __launch_bounds__(NA_THREADS, 1)
+__global__ void __launch_bounds__(Na3dCfg<KW>::THREADS, 1)
 na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const Na3dParams p) {
   using Cfg = Na3dCfg<KW>;
@@ -181,6 +195,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int EWP = Cfg::EWP;
   constexpr int NKEYS = Cfg::NKEYS;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int NG = Cfg::NG;
+  constexpr int RPG = Cfg::RPG;
+  constexpr int GKEYS = Cfg::GKEYS;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   if ((sbase & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
@@ -191,21 +208,17 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto k_smem = [&](int st) { return sbase + Cfg::KV_OFF + st * 2 * Cfg::KV_BYTES; };
   auto v_smem = [&](int st) { return k_smem(st) + Cfg::KV_BYTES; };
   const uint32_t p_smem = sbase + Cfg::P_OFF;
-  float* merge = reinterpret_cast<float*>(smem + Cfg::MERGE_OFF);
+  float2* ml = reinterpret_cast<float2*>(smem + Cfg::ML_OFF);
   const uint32_t bar = sbase + Cfg::BAR_OFF;
   // barriers, 8 bytes each
-  auto q_full = [&](int qb) { return bar + 8u * qb; };           // 0,1
-  auto q_empty = [&](int qb) { return bar + 16u + 8u * qb; };    // 2,3
-  auto s_full = [&](int sb) { return bar + 32u + 8u * sb; };     // 4,5
-  // p_ready alternates by block parity: a fast softmax warp may finish block i+1 before a slow
-  // one has finished block i (it cannot reach block i+2 before every warp has arrived for
-  // block i, because S of block i+2 is only issued after that), so two barriers keep the
-  // arrivals of consecutive blocks apart.
-  auto p_ready = [&](uint32_t par) { return bar + 48u + 136u * par; };   // 6 and 23
-  auto o_full = [&](uint32_t par) { return bar + 56u + 120u * par; };   // 7 and 22 (by block parity)
-  const uint32_t merge_full = bar + 64u, merge_free = bar + 72u; // 8,9
-  auto kv_full = [&](int st) { return bar + 80u + 8u * st; };    // 10..12
-  auto kv_empty = [&](int st) { return bar + 104u + 8u * st; };  // 13..15
+  auto q_full = [&](uint32_t i) { return bar + 8u * i; };             // 0,1
+  auto q_empty = [&](uint32_t i) { return bar + 16u + 8u * i; };      // 2,3
+  auto s_full = [&](uint32_t i) { return bar + 32u + 8u * i; };       // 4,5
+  auto p_ready = [&](uint32_t i) { return bar + 48u + 8u * i; };      // 6,7   (by block parity)
+  auto o_full = [&](uint32_t i) { return bar + 64u + 8u * i; };       // 8,9   (by block parity)
+  auto ml_ready = [&](uint32_t i) { return bar + 80u + 8u * i; };     // 10,11 (by item parity)
+  auto kv_full = [&](int st) { return bar + 96u + 8u * st; };         // 12..14
+  auto kv_empty = [&](int st) { return bar + 120u + 8u * st; };       // 15..17
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 200);
 
@@ -218,17 +231,14 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int nblk = ED * n_hb;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (uint32_t i = 0; i < 2; ++i) {
       mbar_init(q_full(i), 1);
       mbar_init(q_empty(i), 1);
       mbar_init(s_full(i), 1);
+      mbar_init(p_ready(i), 128 * NG);
+      mbar_init(o_full(i), 1);
+      mbar_init(ml_ready(i), 128 * NG);
     }
-    mbar_init(p_ready(0), 256);
-    mbar_init(p_ready(1), 256);
-    mbar_init(o_full(0), 1);
-    mbar_init(o_full(1), 1);
-    mbar_init(merge_full, 128);
-    mbar_init(merge_free, 128);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
@@ -257,7 +267,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t ph = 0;
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
         const NaItem it = na_decode_item<KW>(item, p);
-        const int qb = n & 1;
+        const uint32_t qb = n & 1;
         if (!mbar_wait(q_empty(qb), ((n >> 1) & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(q_full(qb), Cfg::Q_BYTES);
         tma_load_5d(q_smem(qb), &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full(qb));
@@ -287,7 +297,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NKEYS, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, false, true);
-      constexpr int HALF_STEPS = EWP / 4;  // 16-key MMA steps per key half
+      constexpr int GROUP_STEPS = GKEYS / 16;  // 16-key MMA steps per key group
       constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t STAGE_UNITS = (2 * Cfg::KV_BYTES) >> 4;
       auto lo_of = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };
@@ -296,7 +306,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t k_lo0 = lo_of(k_smem(0));
       const uint32_t v_lo0 = lo_of(v_smem(0));
       const uint32_t p_lo = lo_of(p_smem);
-      const uint32_t o_tmem = tmem_base + NA_O_COL;
+      const uint32_t o_tmem = tmem_base + Cfg::O_COL;
 
       // position of the next Q K^T to issue (runs one block ahead of the P V position)
       int qk_st = 0;
@@ -305,11 +315,11 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(kv_full(qk_st), qk_ph, abort_flag, ST_TIMEOUT_MMA)) return false;
         tc_fence_after();
         const uint32_t klo = k_lo0 + qk_st * STAGE_UNITS;
-        const uint32_t s_tmem = tmem_base + (qk_sb ? NA_S1_COL : 0);
+        const uint32_t s_tmem = tmem_base + (qk_sb ? Cfg::SCOLS : 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_ss(s_tmem, desc(qlo + 2u * k), desc(klo + 2u * k), idesc_qk, k != 0 ? 1u : 0u);
-        umma_commit(s_full(static_cast<int>(qk_sb)));
+        umma_commit(s_full(qk_sb));
         qk_sb ^= 1u;
         if (++qk_st == STAGES) { qk_st = 0; qk_ph ^= 1u; }
         return true;
@@ -322,7 +332,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t pv_cnt = 0;     // number of P V blocks issued so far
       bool pre_issued = false; // S of this item's block 0 was issued at the end of the previous item
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
-        const int qb = n & 1;
+        const uint32_t qb = n & 1;
         if (!pre_issued) {
           if (!mbar_wait(q_full(qb), (n >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
           if (!issue_qk(q_lo[qb])) break;
@@ -336,7 +346,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           } else {
             if (nblk == 1) umma_commit(q_empty(qb));
             if (item + static_cast<int>(gridDim.x) < p.n_items) {
-              const int nq = (n + 1) & 1;
+              const uint32_t nq = (n + 1) & 1;
               if (!mbar_wait(q_full(nq), ((n + 1) >> 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) {
                 ok = false;
                 break;
@@ -355,12 +365,10 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               p_lo + ((Cfg::P_BUFS == 2 && pv_par) ? static_cast<uint32_t>(Cfg::P_BYTES >> 4) : 0u);
           const uint32_t acc = i != 0 ? 1u : 0u;   // O accumulates over the blocks of the item
 #pragma unroll
-          for (int g = 0; g < 2; ++g) {
+          for (int g = 0; g < NG; ++g) {
 #pragma unroll
-            for (int s0 = 0; s0 < HALF_STEPS; ++s0) {
-              constexpr int dummy = 0;
-              (void)dummy;
-              const int s = g * HALF_STEPS + s0;
+            for (int s0 = 0; s0 < GROUP_STEPS; ++s0) {
+              const int s = g * GROUP_STEPS + s0;
               // P: 64-key atoms of 16 KB, 32 bytes per 16-key step inside an atom;
               // V: 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
               umma_ss(o_tmem + 64 * g, desc(plo + (s >> 2) * 1024u + (s & 3) * 2u),
@@ -378,17 +386,17 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else {
     // ------------------------------------------------------------ softmax warps
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;          // key half this thread owns
+    const int grp = (warp - 2) >> 2;          // key group this thread owns
     const int r = quarter * 32 + lane;        // query row
     const int zw = r & 7;
     const int zh = (r >> 3) % p.QH;
     const int zd = (r >> 3) / p.QH;
     const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t o_taddr = lane_taddr + NA_O_COL + 64 * grp;
+    const uint32_t o_taddr = lane_taddr + Cfg::O_COL + 64 * grp;
     const uint32_t p_row = p_smem + r * 128;
     const uint32_t sw = static_cast<uint32_t>(r & 7);
     const float c = p.scale_log2e;
-    constexpr int GKEYS = 4 * EWP;            // keys per block owned by one group
+    constexpr uint32_t ROWBITS = (1u << RPG) - 1u;
 
     bool ok = true;
     int n = 0;
@@ -401,131 +409,107 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int wd = na_window_start(id, p.D, p.kd) - it.bd0;
       const int wh = na_window_start(ih, p.H, p.kh) - it.bh0;
       const int ww = na_window_start(iw, p.W, KW) - it.bw0;
-      float cb[EWP];   // additive column mask: 0 inside the window, -1e30 outside
+      float cb[EW];   // additive column mask: 0 inside the window, -1e30 outside
 #pragma unroll
-      for (int cc = 0; cc < EWP; ++cc)
+      for (int cc = 0; cc < EW; ++cc)
         cb[cc] = (static_cast<unsigned>(cc - ww) < static_cast<unsigned>(KW)) ? 0.f : -1e30f;
       const uint32_t hmask_all = ((1u << p.kh) - 1u) << wh;   // bit = key row of the box
 
-      // Running reference m_run and sum l_run of this thread's key half. The output
+      // Reference maximum m_run and running sum l_run of this thread's key group. The output
       // accumulator lives in TMEM and is touched only when the reference has to move.
       float m_run = -1e30f, l_run = 0.f;
 
       int ip = 0, hb = 0;
       for (int i = 0; i < nblk; ++i, ++gb) {
-        const int sb = static_cast<int>(gb & 1u);
+        const uint32_t sb = gb & 1u;
         if (!mbar_wait(s_full(sb), (gb >> 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t s_taddr = lane_taddr + (sb ? NA_S1_COL : 0) + grp * GKEYS;
+        const uint32_t s_taddr = lane_taddr + (sb ? Cfg::SCOLS : 0) + grp * GKEYS;
         const uint32_t p_row_b = p_row + ((Cfg::P_BUFS == 2 && sb) ? Cfg::P_BYTES : 0);
         const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
-        const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + 4 * grp)) & 0xfu) : 0u;
+        const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + RPG * grp)) & ROWBITS) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
 
-        // pass 1: masked row maximum over this thread's key rows. For key rows of at most 16
-        // columns all visible rows are fetched from TMEM at once and stay in registers for
-        // pass 2; wider rows are fetched row by row in both passes.
-        constexpr bool HOLD = (EWP <= NA_HOLD_MAX_EWP);
-        uint32_t a[HOLD ? 4 : 1][EWP];
-        if constexpr (HOLD) {
-#pragma unroll
-          for (int rr = 0; rr < 4; ++rr)
-            if ((warp_rows >> rr) & 1u) tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a[rr]);
-          tmem_ld_wait();
-        }
+        // pass 1: masked row maximum over this thread's key rows
         float bm = -1e30f;
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
+        for (int rr = 0; rr < RPG; ++rr) {
           if ((warp_rows >> rr) & 1u) {
-            uint32_t* ar = a[HOLD ? rr : 0];
-            if constexpr (!HOLD) {
-              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, ar);
-              tmem_ld_wait();
-            }
+            uint32_t a[EWP];
+            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+            tmem_ld_wait();
             float rm0 = -1e30f, rm1 = -1e30f;
 #pragma unroll
             for (int cc = 0; cc < EW; cc += 4) {
-              rm0 = fmax3(rm0, __uint_as_float(ar[cc]) + cb[cc],
-                          __uint_as_float(ar[cc + 1]) + cb[cc + 1]);
+              rm0 = fmax3(rm0, __uint_as_float(a[cc]) + cb[cc],
+                          __uint_as_float(a[cc + 1]) + cb[cc + 1]);
               if (cc + 2 < EW)
-                rm1 = fmax3(rm1, __uint_as_float(ar[cc + 2]) + cb[cc + 2],
-                            __uint_as_float(ar[cc + 3]) + cb[cc + 3]);
+                rm1 = fmax3(rm1, __uint_as_float(a[cc + 2]) + cb[cc + 2],
+                            __uint_as_float(a[cc + 3]) + cb[cc + 3]);
             }
             bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
           }
         }
         // Move the reference only when the block maximum exceeds it by more than 2^8 (P stays
         // well inside bf16 / fp32 range otherwise) - or adopt it for free while nothing has
-        // been accumulated yet. Moving it rescales the TMEM accumulator, so it must wait for
-        // the previous block's P V.
+        // been accumulated yet. Moving it rescales the TMEM accumulator, which must wait for
+        // the previous block's P V (o_full of that block's parity; S of the current block being
+        // complete implies P V of block gb-2 is, so the parity wait cannot alias).
         const bool grow = (bm - m_run) * c > 8.0f;
         const bool rescale = grow && l_run > 0.f;
         if (grow && !rescale) m_run = bm;
-        // o_full[par] completes once per block of that parity. With two P buffers the softmax
-        // waits for it only when it must touch the accumulator; with one P buffer it also
-        // guards the buffer against being overwritten while P V of the previous block reads it.
-        bool o_waited = false;
-        if (Cfg::P_BUFS == 1 && i > 0) {
+        // With a single P buffer the previous block's P V must also be finished before pass 2
+        // overwrites the buffer it reads.
+        const bool must_wait = (Cfg::P_BUFS == 1 && i > 0);
+        const bool any_rescale = __any_sync(0xffffffffu, rescale);
+        if (must_wait || any_rescale) {
           if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
                          ST_TIMEOUT_SOFTMAX)) {
             ok = false;
             break;
           }
-          o_waited = true;
         }
-        if (__any_sync(0xffffffffu, rescale)) {
-          if (!o_waited) {
-            if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
-                           ST_TIMEOUT_SOFTMAX)) {
-              ok = false;
-              break;
-            }
-          }
+        if (any_rescale) {
           tc_fence_after();
           const float alpha = rescale ? fast_exp2((m_run - bm) * c) : 1.0f;
           if (rescale) m_run = bm;
           l_run *= alpha;
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            uint32_t ob[32];
-            tmem_ld_32x32(o_taddr + 32 * hh, ob);
+#pragma unroll 1
+          for (int hh = 0; hh < 4; ++hh) {
+            uint32_t ob[16];
+            tmem_ld_x16(o_taddr + 16 * hh, ob);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
-            tmem_st_32x32(o_taddr + 32 * hh, ob);
+            for (int j = 0; j < 16; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+            tmem_st_x16(o_taddr + 16 * hh, ob);
           }
           tmem_st_wait();
         }
         const float mc = m_run * c;
 
         // pass 2: exponentials, row sum, bf16 P into the swizzled A-operand layout
-        float nb[EWP];
-#pragma unroll
-        for (int cc = 0; cc < EWP; ++cc) nb[cc] = cb[cc] - mc;
         float rs = 0.f;
         uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
+        for (int rr = 0; rr < RPG; ++rr) {
           const bool need = (warp_rows >> rr) & 1u;
           const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
-          uint32_t* ar = a[HOLD ? rr : 0];
+          uint32_t a[EWP];
           float rs0 = 0.f, rs1 = 0.f;
-          if constexpr (!HOLD) {
-            if (need) {
-              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, ar);
-              tmem_ld_wait();
-            }
+          if (need) {
+            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+            tmem_ld_wait();
           }
 #pragma unroll
           for (int cc = 0; cc < EWP; cc += 2) {
             const int jj = rr * EWP + cc;   // even, compile-time
             uint32_t packed = 0u;
             if (need && cc < EW) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(ar[cc]), c, nb[cc]));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(ar[cc + 1]), c, nb[cc + 1]));
+              const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, cb[cc] - mc));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, cb[cc + 1] - mc));
               if (cc & 2) rs1 += p0 + p1; else rs0 += p0 + p1;
               packed = pack_bf16(p0, p1) & keep;
             }
@@ -545,66 +529,66 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l_run += rs;
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(p_ready(gb & 1u));
+        mbar_arrive(p_ready(sb));
         if (++hb == n_hb) { hb = 0; ++ip; }
       }
       if (!ok) break;
 
-      // item epilogue: last P V, merge the two key halves, normalise, store
+      // item epilogue: publish (max, sum), wait for the last P V, then every thread combines
+      // the NG accumulators of its row for its own 64/NG output channels and stores them.
+      const uint32_t ipar = n & 1u;
+      ml[(ipar * NG + grp) * 128 + r] = make_float2(m_run, l_run);
+      mbar_arrive(ml_ready(ipar));
       if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
-                     ST_TIMEOUT_SOFTMAX)) {
+                     ST_TIMEOUT_SOFTMAX) ||
+          !mbar_wait(ml_ready(ipar), (n >> 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      float o[64];
       {
-        uint32_t ob[32];
+        float mj[NG], lj[NG];
+        float m = -1e30f;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          tmem_ld_32x32(o_taddr + 32 * hh, ob);
+        for (int g = 0; g < NG; ++g) {
+          const float2 t = ml[(ipar * NG + g) * 128 + r];
+          mj[g] = t.x;
+          lj[g] = t.y;
+          m = fmaxf(m, t.x);
+        }
+        float denom = 0.f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          mj[g] = fast_exp2((mj[g] - m) * c);   // weight of group g
+          denom += lj[g] * mj[g];
+        }
+        const float inv = 1.0f / denom;
+        constexpr int WCOLS = 64 / NG;          // output channels this thread finishes
+        float acc[WCOLS];
+#pragma unroll
+        for (int j = 0; j < WCOLS; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          uint32_t ob[WCOLS];
+          const uint32_t ta = lane_taddr + Cfg::O_COL + 64 * g + WCOLS * grp;
+          if constexpr (WCOLS == 16) tmem_ld_x16(ta, ob); else tmem_ld_32x32(ta, *reinterpret_cast<uint32_t(*)[32]>(ob));
           tmem_ld_wait();
+          const float wgt = mj[g] * inv;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[32 * hh + j] = __uint_as_float(ob[j]);
+          for (int j = 0; j < WCOLS; ++j) acc[j] = fmaf(__uint_as_float(ob[j]), wgt, acc[j]);
         }
-      }
-      tc_fence_before();
-      if (grp == 1) {
-        if (!mbar_wait(merge_free, ((n & 1u) ^ 1u), abort_flag, ST_TIMEOUT_SOFTMAX)) {
-          ok = false;
-          break;
-        }
-        merge[0 * 128 + r] = m_run;
-        merge[1 * 128 + r] = l_run;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) merge[(2 + j) * 128 + r] = o[j];
-        mbar_arrive(merge_full);   // release semantics order the stores before the arrival
-      } else {
-        if (!mbar_wait(merge_full, n & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
-          ok = false;
-          break;
-        }
-        const float m1 = merge[0 * 128 + r];
-        const float l1 = merge[1 * 128 + r];
-        const float m = fmaxf(m_run, m1);
-        const float f0 = fast_exp2((m_run - m) * c);
-        const float f1 = fast_exp2((m1 - m) * c);
-        const float inv = 1.0f / (l_run * f0 + l1 * f1);
-        const float g0 = f0 * inv, g1 = f1 * inv;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) o[j] = o[j] * g0 + merge[(2 + j) * 128 + r] * g1;
-        mbar_arrive(merge_free);
+        tc_fence_before();
         if (q_ok) {
           const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.H +
                                  (it.h0 + zh)) * p.W + (it.w0 + zw);
-          __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64;
+          __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64 + WCOLS * grp;
 #pragma unroll
-          for (int j = 0; j < 64; j += 8) {
+          for (int j = 0; j < WCOLS; j += 8) {
             uint4 v4;
-            v4.x = pack_bf16(o[j], o[j + 1]);
-            v4.y = pack_bf16(o[j + 2], o[j + 3]);
-            v4.z = pack_bf16(o[j + 4], o[j + 5]);
-            v4.w = pack_bf16(o[j + 6], o[j + 7]);
+            v4.x = pack_bf16(acc[j], acc[j + 1]);
+            v4.y = pack_bf16(acc[j + 2], acc[j + 3]);
+            v4.z = pack_bf16(acc[j + 4], acc[j + 5]);
+            v4.w = pack_bf16(acc[j + 6], acc[j + 7]);
             *reinterpret_cast<uint4*>(op + j) = v4;
           }
         }
@@ -648,7 +632,7 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
                                        Cfg::TOTAL);
   if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
   const int grid = p.n_items < sm_count ? p.n_items : sm_count;
-  kern<<<grid, NA_THREADS, Cfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  kern<<<grid, Cfg::THREADS, Cfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
