@@ -235,9 +235,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(q_full(i), 1);
       mbar_init(q_empty(i), 1);
       mbar_init(s_full(i), 1);
-      mbar_init(p_ready(i), 128 * NG);
+      mbar_init(p_ready(i), 4 * NG);    // one arrival per softmax warp
       mbar_init(o_full(i), 1);
-      mbar_init(ml_ready(i), 128 * NG);
+      mbar_init(ml_ready(i), 4 * NG);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
@@ -527,9 +527,12 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           rs += keep ? (rs0 + rs1) : 0.f;
         }
         l_run += rs;
+        // every lane makes its P stores visible to the tensor core, then one lane arrives for
+        // the warp (512 single arrivals on one barrier word would serialise)
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(p_ready(sb));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready(sb));
         if (++hb == n_hb) { hb = 0; ++ip; }
       }
       if (!ok) break;
@@ -538,7 +541,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // the NG accumulators of its row for its own 64/NG output channels and stores them.
       const uint32_t ipar = n & 1u;
       ml[(ipar * NG + grp) * 128 + r] = make_float2(m_run, l_run);
-      mbar_arrive(ml_ready(ipar));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ml_ready(ipar));
       if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
                      ST_TIMEOUT_SOFTMAX) ||
           !mbar_wait(ml_ready(ipar), (n >> 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
