@@ -72,21 +72,19 @@ struct Na3dCfg {
   static constexpr int SCOLS = (NG == 4) ? 128 : 192;           // TMEM columns per S buffer
   static constexpr int O_COL = 2 * SCOLS;                       // O of group g at O_COL + 64 g
   static constexpr int KV_BYTES = NKEYS * 128;
-  static constexpr int P_ATOMS = (NKEYS + 63) / 64;
-  static constexpr int P_BYTES = P_ATOMS * 16384;
   static constexpr int Q_BYTES = 128 * 128;
-  static constexpr int STAGES = NKEYS <= 128 ? 3 : 2;
   static constexpr int KV_OFF = 2 * Q_BYTES;
-  static constexpr int P_OFF = KV_OFF + STAGES * 2 * KV_BYTES;
-  // Two P buffers when they fit: the softmax of block i+1 then never waits for P V of block i.
-  static constexpr int P_BUFS =
-      (P_OFF + 2 * P_BYTES + 2 * NG * 128 * 8 + 256 <= 227 * 1024) ? 2 : 1;
-  static constexpr int ML_OFF = P_OFF + P_BUFS * P_BYTES;       // [2][NG][128] (max, sum)
-  static constexpr int BAR_OFF = ML_OFF + 2 * NG * 128 * 8;
+  static constexpr int ML_BYTES = 2 * NG * 128 * 8;             // [2][NG][128] (max, sum)
+  // K/V ring as deep as shared memory allows: its depth hides the TMA round trip
+  static constexpr int STAGES_FIT = (227 * 1024 - KV_OFF - ML_BYTES - 256) / (2 * KV_BYTES);
+  static constexpr int STAGES = STAGES_FIT > 6 ? 6 : STAGES_FIT;
+  static constexpr int ML_OFF = KV_OFF + STAGES * 2 * KV_BYTES;
+  static constexpr int BAR_OFF = ML_OFF + ML_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256;
+  static constexpr int PCOLS_ROW = EWP / 2;                     // packed-P columns per key row
   static_assert(NKEYS <= SCOLS && GKEYS % 16 == 0, "key block layout");
   static_assert(O_COL + 64 * NG <= NA_TMEM_COLS, "TMEM budget");
-  static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+  static_assert(TOTAL <= 227 * 1024 && STAGES >= 2, "shared memory budget");
 };
 
 __device__ __forceinline__ int na_window_start(int i, int L, int k) {
@@ -157,6 +155,34 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
         "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]),
+                 "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_x4(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_x2(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1])
+               : "memory");
+}
+// Stores N (4, 8, 10 or 12) consecutive 32-bit columns of this thread's row.
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  static_assert(N == 4 || N == 8 || N == 10 || N == 12, "unsupported column count");
+  if constexpr (N == 4) {
+    tmem_st_x4(taddr, r);
+  } else {
+    tmem_st_x8(taddr, r);
+    if constexpr (N == 10) tmem_st_x2(taddr + 8, r + 8);
+    if constexpr (N == 12) tmem_st_x4(taddr + 8, r + 8);
+  }
+}
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -207,7 +233,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto q_smem = [&](int qb) { return sbase + qb * Cfg::Q_BYTES; };
   auto k_smem = [&](int st) { return sbase + Cfg::KV_OFF + st * 2 * Cfg::KV_BYTES; };
   auto v_smem = [&](int st) { return k_smem(st) + Cfg::KV_BYTES; };
-  const uint32_t p_smem = sbase + Cfg::P_OFF;
   float2* ml = reinterpret_cast<float2*>(smem + Cfg::ML_OFF);
   const uint32_t bar = sbase + Cfg::BAR_OFF;
   // barriers, 8 bytes each
@@ -217,10 +242,10 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto p_ready = [&](uint32_t i) { return bar + 48u + 8u * i; };      // 6,7   (by block parity)
   auto o_full = [&](uint32_t i) { return bar + 64u + 8u * i; };       // 8,9   (by block parity)
   auto ml_ready = [&](uint32_t i) { return bar + 80u + 8u * i; };     // 10,11 (by item parity)
-  auto kv_full = [&](int st) { return bar + 96u + 8u * st; };         // 12..14
-  auto kv_empty = [&](int st) { return bar + 120u + 8u * st; };       // 15..17
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 192);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 200);
+  auto kv_full = [&](int st) { return bar + 96u + 8u * st; };         // 12..17
+  auto kv_empty = [&](int st) { return bar + 144u + 8u * st; };       // 18..23
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 224);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::BAR_OFF + 232);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -305,7 +330,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t q_lo[2] = {lo_of(q_smem(0)), lo_of(q_smem(1))};
       const uint32_t k_lo0 = lo_of(k_smem(0));
       const uint32_t v_lo0 = lo_of(v_smem(0));
-      const uint32_t p_lo = lo_of(p_smem);
       const uint32_t o_tmem = tmem_base + Cfg::O_COL;
 
       // position of the next Q K^T to issue (runs one block ahead of the P V position)
@@ -361,18 +385,17 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tc_fence_after();
           const uint32_t vlo = v_lo0 + pv_st * STAGE_UNITS;
-          const uint32_t plo =
-              p_lo + ((Cfg::P_BUFS == 2 && pv_par) ? static_cast<uint32_t>(Cfg::P_BYTES >> 4) : 0u);
+          const uint32_t p_tmem = tmem_base + (pv_par ? Cfg::SCOLS : 0);   // P aliases S
           const uint32_t acc = i != 0 ? 1u : 0u;   // O accumulates over the blocks of the item
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
 #pragma unroll
             for (int s0 = 0; s0 < GROUP_STEPS; ++s0) {
               const int s = g * GROUP_STEPS + s0;
-              // P: 64-key atoms of 16 KB, 32 bytes per 16-key step inside an atom;
+              // P: bf16 pairs in the group's S columns, 8 columns per 16-key step;
               // V: 16 keys = 16 rows of 128 bytes per step (2048 bytes = 128 units)
-              umma_ss(o_tmem + 64 * g, desc(plo + (s >> 2) * 1024u + (s & 3) * 2u),
-                      desc(vlo + 128u * s), idesc_pv, s0 != 0 ? 1u : acc);
+              umma_ts(o_tmem + 64 * g, p_tmem + g * GKEYS + 8 * s0, desc(vlo + 128u * s),
+                      idesc_pv, s0 != 0 ? 1u : acc);
             }
           }
           umma_commit(kv_empty(pv_st));
@@ -393,8 +416,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int zd = (r >> 3) / p.QH;
     const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t o_taddr = lane_taddr + Cfg::O_COL + 64 * grp;
-    const uint32_t p_row = p_smem + r * 128;
-    const uint32_t sw = static_cast<uint32_t>(r & 7);
     const float c = p.scale_log2e;
     constexpr uint32_t ROWBITS = (1u << RPG) - 1u;
 
@@ -428,7 +449,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
         const uint32_t s_taddr = lane_taddr + (sb ? Cfg::SCOLS : 0) + grp * GKEYS;
-        const uint32_t p_row_b = p_row + ((Cfg::P_BUFS == 2 && sb) ? Cfg::P_BYTES : 0);
         const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
         const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + RPG * grp)) & ROWBITS) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
@@ -461,11 +481,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool grow = (bm - m_run) * c > 8.0f;
         const bool rescale = grow && l_run > 0.f;
         if (grow && !rescale) m_run = bm;
-        // With a single P buffer the previous block's P V must also be finished before pass 2
-        // overwrites the buffer it reads.
-        const bool must_wait = (Cfg::P_BUFS == 1 && i > 0);
         const bool any_rescale = __any_sync(0xffffffffu, rescale);
-        if (must_wait || any_rescale) {
+        if (any_rescale) {
           if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
                          ST_TIMEOUT_SOFTMAX)) {
             ok = false;
@@ -490,14 +507,16 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         const float mc = m_run * c;
 
-        // pass 2: exponentials, row sum, bf16 P into the swizzled A-operand layout
+        // pass 2: exponentials, row sum, bf16 P (two keys per 32-bit column) written over the
+        // already consumed part of this thread's own S segment: P of key row rr goes to columns
+        // [rr*EWP/2, (rr+1)*EWP/2) of the segment, which S rows > rr do not occupy.
         float rs = 0.f;
-        uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
         for (int rr = 0; rr < RPG; ++rr) {
           const bool need = (warp_rows >> rr) & 1u;
           const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
           uint32_t a[EWP];
+          uint32_t pk[Cfg::PCOLS_ROW];
           float rs0 = 0.f, rs1 = 0.f;
           if (need) {
             tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
@@ -505,7 +524,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
 #pragma unroll
           for (int cc = 0; cc < EWP; cc += 2) {
-            const int jj = rr * EWP + cc;   // even, compile-time
             uint32_t packed = 0u;
             if (need && cc < EW) {
               const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, cb[cc] - mc));
@@ -513,23 +531,14 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               if (cc & 2) rs1 += p0 + p1; else rs0 += p0 + p1;
               packed = pack_bf16(p0, p1) & keep;
             }
-            pk[(jj >> 1) & 3] = packed;
-            if ((jj & 7) == 6) {
-              const int j = grp * GKEYS + jj;   // key index within the block
-              const uint32_t addr =
-                  p_row_b + static_cast<uint32_t>(j >> 6) * 16384u +
-                  ((static_cast<uint32_t>((j & 63) >> 3) ^ sw) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]),
-                           "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                           : "memory");
-            }
+            pk[cc >> 1] = packed;
           }
+          tmem_st_cols<Cfg::PCOLS_ROW>(s_taddr + rr * Cfg::PCOLS_ROW, pk);
           rs += keep ? (rs0 + rs1) : 0.f;
         }
         l_run += rs;
-        // every lane makes its P stores visible to the tensor core, then one lane arrives for
-        // the warp (512 single arrivals on one barrier word would serialise)
-        fence_proxy_async_smem();
+        // every lane completes its P stores, then one lane arrives for the warp
+        tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready(sb));
