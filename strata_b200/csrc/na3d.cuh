@@ -186,6 +186,30 @@ __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) 
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// Packed fp32x2 arithmetic (sm_100): one instruction for two lanes of a 64-bit register pair.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -430,15 +454,24 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int wd = na_window_start(id, p.D, p.kd) - it.bd0;
       const int wh = na_window_start(ih, p.H, p.kh) - it.bh0;
       const int ww = na_window_start(iw, p.W, KW) - it.bw0;
-      float cb[EW];   // additive column mask: 0 inside the window, -1e30 outside
-#pragma unroll
-      for (int cc = 0; cc < EW; ++cc)
-        cb[cc] = (static_cast<unsigned>(cc - ww) < static_cast<unsigned>(KW)) ? 0.f : -1e30f;
       const uint32_t hmask_all = ((1u << p.kh) - 1u) << wh;   // bit = key row of the box
 
-      // Reference maximum m_run and running sum l_run of this thread's key group. The output
-      // accumulator lives in TMEM and is touched only when the reference has to move.
-      float m_run = -1e30f, l_run = 0.f;
+      // Scores are handled in scaled form t = s*c - mc (c = scale*log2 e), where mc is the
+      // scaled reference of this thread's key group. nb2 holds, per pair of key columns, the
+      // addend of that form: -mc inside the query's window, -1e30 outside (the column mask).
+      // The output accumulator lives in TMEM and is touched only when the reference moves.
+      float mc = 0.f, l_run = 0.f;
+      uint64_t nb2[EW / 2];
+      auto set_nb = [&](float ref) {
+#pragma unroll
+        for (int k2 = 0; k2 < EW / 2; ++k2) {
+          const float lo = (static_cast<unsigned>(2 * k2 - ww) < static_cast<unsigned>(KW)) ? -ref : -1e30f;
+          const float hi = (static_cast<unsigned>(2 * k2 + 1 - ww) < static_cast<unsigned>(KW)) ? -ref : -1e30f;
+          nb2[k2] = pack2(lo, hi);
+        }
+      };
+      set_nb(0.f);
+      const uint64_t c2 = pack2(c, c);
 
       int ip = 0, hb = 0;
       for (int i = 0; i < nblk; ++i, ++gb) {
@@ -453,7 +486,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + RPG * grp)) & ROWBITS) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
 
-        // pass 1: masked row maximum over this thread's key rows
+        // pass 1: masked maximum of the scaled scores over this thread's key rows
         float bm = -1e30f;
 #pragma unroll
         for (int rr = 0; rr < RPG; ++rr) {
@@ -463,24 +496,23 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_ld_wait();
             float rm0 = -1e30f, rm1 = -1e30f;
 #pragma unroll
-            for (int cc = 0; cc < EW; cc += 4) {
-              rm0 = fmax3(rm0, __uint_as_float(a[cc]) + cb[cc],
-                          __uint_as_float(a[cc + 1]) + cb[cc + 1]);
-              if (cc + 2 < EW)
-                rm1 = fmax3(rm1, __uint_as_float(a[cc + 2]) + cb[cc + 2],
-                            __uint_as_float(a[cc + 3]) + cb[cc + 3]);
+            for (int k2 = 0; k2 < EW / 2; ++k2) {
+              float t0, t1;
+              unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+              if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
             }
             bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
           }
         }
-        // Move the reference only when the block maximum exceeds it by more than 2^8 (P stays
-        // well inside bf16 / fp32 range otherwise) - or adopt it for free while nothing has
-        // been accumulated yet. Moving it rescales the TMEM accumulator, which must wait for
-        // the previous block's P V (o_full of that block's parity; S of the current block being
-        // complete implies P V of block gb-2 is, so the parity wait cannot alias).
-        const bool grow = (bm - m_run) * c > 8.0f;
-        const bool rescale = grow && l_run > 0.f;
-        if (grow && !rescale) m_run = bm;
+        // bm is the block maximum relative to the current reference. The reference moves only
+        // when it is exceeded by more than 2^8 (P stays well inside bf16 / fp32 range
+        // otherwise) - or is adopted for free while nothing has been accumulated yet. Moving
+        // it rescales the TMEM accumulator, which must wait for the previous block's P V
+        // (o_full of that block's parity; S of the current block being complete implies P V of
+        // block gb-2 is, so the parity wait cannot alias).
+        const bool fresh = l_run == 0.f;
+        const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
+        const bool rescale = grow && !fresh;
         const bool any_rescale = __any_sync(0xffffffffu, rescale);
         if (any_rescale) {
           if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
@@ -488,11 +520,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = false;
             break;
           }
-        }
-        if (any_rescale) {
           tc_fence_after();
-          const float alpha = rescale ? fast_exp2((m_run - bm) * c) : 1.0f;
-          if (rescale) m_run = bm;
+          const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
           l_run *= alpha;
 #pragma unroll 1
           for (int hh = 0; hh < 4; ++hh) {
@@ -505,38 +534,46 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tmem_st_wait();
         }
-        const float mc = m_run * c;
+        if (grow) {
+          mc += bm;
+          set_nb(mc);
+        }
 
         // pass 2: exponentials, row sum, bf16 P (two keys per 32-bit column) written over the
         // already consumed part of this thread's own S segment: P of key row rr goes to columns
         // [rr*EWP/2, (rr+1)*EWP/2) of the segment, which S rows > rr do not occupy.
-        float rs = 0.f;
+        uint64_t rs2 = 0ull;
 #pragma unroll
         for (int rr = 0; rr < RPG; ++rr) {
           const bool need = (warp_rows >> rr) & 1u;
           const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
           uint32_t a[EWP];
           uint32_t pk[Cfg::PCOLS_ROW];
-          float rs0 = 0.f, rs1 = 0.f;
+          uint64_t rsa = 0ull, rsb = 0ull;
           if (need) {
             tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
             tmem_ld_wait();
           }
 #pragma unroll
-          for (int cc = 0; cc < EWP; cc += 2) {
+          for (int k2 = 0; k2 < Cfg::PCOLS_ROW; ++k2) {
             uint32_t packed = 0u;
-            if (need && cc < EW) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(a[cc]), c, cb[cc] - mc));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(a[cc + 1]), c, cb[cc + 1] - mc));
-              if (cc & 2) rs1 += p0 + p1; else rs0 += p0 + p1;
+            if (need && k2 < EW / 2) {
+              float t0, t1;
+              unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+              if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
               packed = pack_bf16(p0, p1) & keep;
             }
-            pk[cc >> 1] = packed;
+            pk[k2] = packed;
           }
           tmem_st_cols<Cfg::PCOLS_ROW>(s_taddr + rr * Cfg::PCOLS_ROW, pk);
-          rs += keep ? (rs0 + rs1) : 0.f;
+          if (keep) rs2 = fadd2(rs2, fadd2(rsa, rsb));
         }
-        l_run += rs;
+        {
+          float r0, r1;
+          unpack2(rs2, r0, r1);
+          l_run += r0 + r1;
+        }
         // every lane completes its P stores, then one lane arrives for the warp
         tmem_st_wait();
         tc_fence_before();
@@ -549,7 +586,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // item epilogue: publish (max, sum), wait for the last P V, then every thread combines
       // the NG accumulators of its row for its own 64/NG output channels and stores them.
       const uint32_t ipar = n & 1u;
-      ml[(ipar * NG + grp) * 128 + r] = make_float2(m_run, l_run);
+      ml[(ipar * NG + grp) * 128 + r] = make_float2(l_run > 0.f ? mc : -1e30f, l_run);
       __syncwarp();
       if (lane == 0) mbar_arrive(ml_ready(ipar));
       if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
@@ -572,7 +609,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float denom = 0.f;
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
-          mj[g] = fast_exp2((mj[g] - m) * c);   // weight of group g
+          mj[g] = fast_exp2(mj[g] - m);   // weight of group g (references are already scaled)
           denom += lj[g] * mj[g];
         }
         const float inv = 1.0f / denom;
