@@ -183,6 +183,8 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
 }
 
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulation.
+// (A and B must have the same 16-bit format: a half A with a bf16 B is rejected by the
+// hardware as an illegal instruction.)
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, bool a_mn_major,
                                                        bool b_mn_major) {
   return (1u << 4)                                   // D format: f32
