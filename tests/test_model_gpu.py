@@ -115,22 +115,30 @@ def test_whole_model_matches_oracle(wind, gated):
     over = dict(gated_attention=gated, qk_norm=gated, attn_kernel=(3, 5, 5))
     if wind:
         over.update(do_rotate_wind=True, wind_channel_indices=(0, 1))
-    m = _fill_deterministic(_model(**over))
-    # make the block weights large enough that the blocks matter
+    # Seeded default initialisation plus random biases. (The sin-ramp fill of the reference's
+    # characterisation test gives strongly correlated channels; the final LayerNorm then
+    # amplifies single-ulp bf16 differences of the tokens and the comparison measures that
+    # amplification instead of the kernels.)
+    m = _model(**over)
     with torch.no_grad():
+        g = torch.Generator().manual_seed(5)
         for n, p in m.named_parameters():
-            if ".weight" in n and "blocks" in n:
-                p.mul_(4.0)
+            if n.endswith(".bias"):
+                p.copy_(torch.randn(p.shape, generator=g) * 0.05)
     B, H, W = 2, 32, 32
     x = torch.randn(B, 5, 4, H, W, generator=torch.Generator().manual_seed(0))
     idx, lat, lon = _index(B, H, W)
     with torch.inference_mode():
         y = m(x.cuda(), idx)
     state = {k: v.detach().cpu() for k, v in m.state_dict().items()}
-    ref = bo.backbone_forward(x, state, patch=(1, 4, 4), num_heads=2, kernel=(3, 5, 5), num_layers=2,
-                              lat=lat, lon=lon, qk_norm=gated, gated=gated,
-                              wind_channels=(0, 1) if wind else None)
-    assert rel_max_err(y, ref) < TOL_BF16
+    kw = dict(patch=(1, 4, 4), num_heads=2, kernel=(3, 5, 5), num_layers=2, lat=lat, lon=lon,
+              qk_norm=gated, gated=gated, wind_channels=(0, 1) if wind else None)
+    ref = bo.backbone_forward(x, state, **kw)
+    ref_bf16 = bo.backbone_forward(x, state, emulate_bf16=True, **kw)
+    err_fp32, err_bf16 = rel_max_err(y, ref), rel_max_err(y, ref_bf16)
+    print(f"whole model: vs fp32 oracle {err_fp32:.4f}, vs bf16-rounding oracle {err_bf16:.4f}")
+    assert err_fp32 < TOL_BF16
+    assert err_bf16 < TOL_BF16
 
 
 def test_sphere_stepper_is_pad_network_crop():
