@@ -39,6 +39,11 @@ def flops_per_token(C, kernel, ratio=4.0):
     return 6 * C * C + 4 * K * C + 2 * C * C + 4 * ratio * C * C
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/ (same workload, one launch each).
+NCU_TRAFFIC_BYTES = {"na3d_fwd": 1.064e9, "gemm_fc1_gelu": 1.288e9, "gemm_qkv_rope": 1.022e9}
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -196,11 +201,12 @@ def run_gpu_arm(args):
     pos = torch.stack([lat, lon], dim=1).to(dev)
     cos, sin = rope.stereographic_rope_tables(pos, C // heads, 1, rope.default_rope_length_scale(1))
     cos, sin = cos.contiguous(), sin.contiguous()
+    cs = rope.pack_rope_tables(cos, sin)
     ws = torch.empty(ops.block_workspace_bytes(M, C, hidden), dtype=torch.uint8, device=dev)
 
     def step(inp, out):
         ops.block_forward(inp, weights, grid=(D, H, W), num_heads=heads, kernel=kernel,
-                          rope_cos=cos, rope_sin=sin, workspace=ws, out=out)
+                          rope_cos=None, rope_sin=None, rope_cs=cs, workspace=ws, out=out)
 
     def barrier():
         if world > 1:
@@ -224,7 +230,7 @@ def run_gpu_arm(args):
 
     if args.only:
         # profiling aid: run one kernel of the block alone on the bench workload
-        res = kernel_breakdown(torch, ops, x, weights, cos, sin, (D, H, W), heads, kernel, hidden,
+        res = kernel_breakdown(torch, ops, x, weights, cs, (D, H, W), heads, kernel, hidden,
                                iters=args.steps, only=args.only)
         if rank == 0:
             print(json.dumps({"only": args.only, "result": [
@@ -262,7 +268,7 @@ def run_gpu_arm(args):
         sphere = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     # per-kernel breakdown (same sequence as strata_block_forward_bf16, one event pair each)
-    breakdown = kernel_breakdown(torch, ops, x, weights, cos, sin, (D, H, W), heads, kernel, hidden)
+    breakdown = kernel_breakdown(torch, ops, x, weights, cs, (D, H, W), heads, kernel, hidden)
 
     if rank == 0:
         tf_peak, hbm_peak, peak_kind = measured_peaks()
@@ -341,7 +347,7 @@ def sphere_step_bench(torch, dist, world, rank, dev, timed, steps=3):
     return out
 
 
-def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidden, iters=5,
+def kernel_breakdown(torch, ops, x, weights, cs, grid, heads, kernel, hidden, iters=5,
                      only=None):
     """Times each kernel of the block alone (CUDA events on the launching stream) and attaches
     its algorithmic flops / bytes and roofline fraction."""
@@ -351,7 +357,8 @@ def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidd
     M = n_tiles * T
     x2 = x.reshape(M, C)
     xn = ops.layernorm(x2)
-    qkv = ops.qkv_rope(xn, weights["w_qkv"], weights["b_qkv"], C // heads, cos, sin, T, H * W)
+    qkv = ops.qkv_rope(xn, weights["w_qkv"], weights["b_qkv"], C // heads, None, None, T, H * W,
+                       rope_cs=cs)
     q6 = qkv.view(n_tiles, D, H, W, 3, heads, C // heads)
     attn = torch.empty(n_tiles, D, H, W, heads, C // heads, dtype=torch.bfloat16, device=x.device)
     x1 = torch.empty_like(x2)
@@ -361,7 +368,8 @@ def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidd
     items = [
         ("layernorm_rows", lambda: ops.layernorm(x2), "hbm", 0, 4 * M * C),
         ("gemm_qkv_rope", lambda: ops.qkv_rope(xn, weights["w_qkv"], weights["b_qkv"], C // heads,
-                                               cos, sin, T, H * W), "tensor", 6 * C * C * M, 8 * M * C),
+                                               None, None, T, H * W, rope_cs=cs), "tensor",
+         6 * C * C * M, 8 * M * C),
         ("na3d_fwd", lambda: ops.na3d(q6[..., 0, :, :], q6[..., 1, :, :], q6[..., 2, :, :], kernel,
                                       out=attn), "tensor", 4 * K * C * M, 8 * M * C),
         ("gemm_proj_residual", lambda: ops.linear(attn.view(M, C), weights["w_proj"], weights["b_proj"],
@@ -389,7 +397,7 @@ def kernel_breakdown(torch, ops, x, weights, cos, sin, grid, heads, kernel, hidd
         frac = (flop / (ms * 1e-3) / 1e12 / tf_peak) if bound == "tensor" else (
             nbytes / (ms * 1e-3) / 1e9 / hbm_peak)
         out.append({"name": name, "ms": ms, "bound": bound, "flop": flop, "bytes": nbytes,
-                    "frac": frac, "traffic": None})
+                    "frac": frac, "traffic": NCU_TRAFFIC_BYTES.get(name)})
     return out
 
 

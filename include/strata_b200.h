@@ -61,16 +61,17 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
 
 /* qkv[M,3C] = x[M,C] Wqkv[3C,C]^T + b with, fused in the epilogue, optional per-head RMS
  * norm of q and k and the 2-D rotary embedding of q and k by the token's (cos,sin) row.
- * rope_cos/rope_sin: fp32 [n_tiles, hw, head_dim/2]; row m of x is token
+ * rope_cs: [n_tiles, hw, head_dim/2] pairs (cos, sin) in IEEE half, 4 bytes per pair (channel
+ * pair p of a head rotates channels 2p, 2p+1); row m of x is token
  * (tile = m / tokens_per_tile, horizontal cell = m % hw). Column layout of qkv:
  * [q heads | k heads | v heads], each head head_dim wide (nn.Linear(C,3C) reshaped
- * [.., 3, heads, head_dim]). Pass rope_cos = NULL for no rotation.
+ * [.., 3, heads, head_dim]). Pass rope_cs = NULL for no rotation.
  * Replaces attn.qkv + qk norm + stereographic/axial RoPE + head split of the block
  * (tables: screamcast/strata_wrappers.py:636-642). */
 int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                          void* qkv, int64_t ldqkv, int M, int C, int head_dim,
-                         const float* rope_cos, const float* rope_sin, int tokens_per_tile, int hw,
-                         int qk_norm, float qk_eps, void* stream);
+                         const void* rope_cs, int tokens_per_tile, int hw, int qk_norm,
+                         float qk_eps, void* stream);
 
 /* 3-D neighbourhood attention forward (non-causal, dilation 1, head_dim 64).
  * q, k, v, out are token-major: element (b,d,h,w,head,c) lives at
@@ -110,7 +111,7 @@ int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden);
  * C channels innermost, bf16):
  *   xn = LN(x); qkv = rope(xn Wqkv^T + b); a = NA3D(q,k,v); [a *= sigmoid(xn Wg^T + bg)]
  *   x1 = x + a Wp^T + bp; y = x1 + fc2(gelu_tanh(fc1(LN(x1))))
- * x and y are [n_tiles*D*H*W, C]; y may alias x. rope tables as in strata_qkv_rope_bf16
+ * x and y are [n_tiles*D*H*W, C]; y may alias x. rope_cs as in strata_qkv_rope_bf16
  * (NULL = no rotation). workspace: strata_block_workspace_bytes(M, C, hidden) bytes of device
  * scratch, 256-byte aligned, owned by the caller. Seven (eight if gated) kernels are launched
  * on `stream`.
@@ -118,9 +119,9 @@ int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden);
  * screamcast/strata_wrappers.py:314-341,414 (self.strata(x, pos=pos)). */
 int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H, int W, int C,
                               int heads, int hidden, int kd, int kh, int kw,
-                              const strata_block_weights* h_weights, const float* rope_cos,
-                              const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
-                              void* workspace, int64_t workspace_bytes, void* stream);
+                              const strata_block_weights* h_weights, const void* rope_cs,
+                              int qk_norm, float ln_eps, float qk_eps, void* workspace,
+                              int64_t workspace_bytes, void* stream);
 
 /* ---- cubed-sphere tile halo exchange ------------------------------------------------------
  * Gather maps: int32 arrays over the cells of this rank's padded tiles
@@ -196,9 +197,8 @@ int strata_ipc_free(void* dptr);
 int strata_block_forward_static_scratch_bf16(const void* x, void* y, int n_tiles, int D, int H,
                                              int W, int C, int heads, int hidden, int kd, int kh,
                                              int kw, const strata_block_weights* h_weights,
-                                             const float* rope_cos, const float* rope_sin,
-                                             int qk_norm, float ln_eps, float qk_eps,
-                                             void* stream);
+                                             const void* rope_cs, int qk_norm, float ln_eps,
+                                             float qk_eps, void* stream);
 
 #ifdef __cplusplus
 }

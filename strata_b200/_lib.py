@@ -33,7 +33,7 @@ _SIGNATURES = {
                                    c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int64,
                                    c_void_p]),
     "strata_qkv_rope_bf16": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
-                                     c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                     c_int64, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                      c_int, c_float, c_void_p]),
     "strata_na3d_fwd_bf16": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                      c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -41,7 +41,7 @@ _SIGNATURES = {
     "strata_block_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),
     "strata_block_forward_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_int, c_int, POINTER(BlockWeights),
-                                          c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
+                                          c_void_p, c_int, c_float, c_float, c_void_p,
                                           c_int64, c_void_p]),
     "strata_halo_gather_tokens_bf16": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p,
                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -55,7 +55,7 @@ _SIGNATURES = {
     "strata_ipc_free": (c_int, [c_void_p]),
     "strata_block_forward_static_scratch_bf16": (c_int, [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-        POINTER(BlockWeights), c_void_p, c_void_p, c_int, c_float, c_float, c_void_p]),
+        POINTER(BlockWeights), c_void_p, c_int, c_float, c_float, c_void_p]),
 }
 
 

@@ -121,8 +121,8 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
 
 int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                          void* qkv, int64_t ldqkv, int M, int C, int head_dim,
-                         const float* rope_cos, const float* rope_sin, int tokens_per_tile, int hw,
-                         int qk_norm, float qk_eps, void* stream) {
+                         const void* rope_cs, int tokens_per_tile, int hw, int qk_norm,
+                         float qk_eps, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (M == 0 && C > 0) return STRATA_OK;
@@ -133,9 +133,8 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
     return STRATA_ERR_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(qkv) || (bias && !aligned16(bias)))
     return STRATA_ERR_ARG;
-  if ((rope_cos == nullptr) != (rope_sin == nullptr)) return STRATA_ERR_ARG;
-  if (rope_cos) {
-    if (!aligned16(rope_cos) || !aligned16(rope_sin)) return STRATA_ERR_ARG;
+  if (rope_cs) {
+    if (!aligned16(rope_cs)) return STRATA_ERR_ARG;
     if (hw <= 0 || tokens_per_tile <= 0 || tokens_per_tile % hw != 0 || M % tokens_per_tile != 0)
       return STRATA_ERR_ARG;
   }
@@ -145,8 +144,7 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.out = static_cast<__nv_bfloat16*>(qkv);
   p.ldo = ldqkv;
   p.bias = bias;
-  p.rope_cos = rope_cos;
-  p.rope_sin = rope_sin;
+  p.rope_cs = static_cast<const uint32_t*>(rope_cs);
   p.tokens_per_tile = tokens_per_tile > 0 ? tokens_per_tile : 1;
   p.hw = hw > 0 ? hw : 1;
   p.head_dim = head_dim;
@@ -155,8 +153,8 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.qk_eps = qk_eps;
   const auto* A = static_cast<const __nv_bfloat16*>(x);
   const auto* W = static_cast<const __nv_bfloat16*>(w);
-  if (!rope_cos && !qk_norm) return launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
-  if (!rope_cos) return STRATA_ERR_UNSUPPORTED;  // qk norm without rotation: not on the path
+  if (!rope_cs && !qk_norm) return launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
+  if (!rope_cs) return STRATA_ERR_UNSUPPORTED;  // qk norm without rotation: not on the path
   return launch_gemm<EPI_QKV_ROPE>(A, ldx, W, ldw, p, sms, as_stream(stream));
 }
 
@@ -194,9 +192,9 @@ int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden) {
 
 int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H, int W, int C,
                               int heads, int hidden, int kd, int kh, int kw,
-                              const strata_block_weights* wts, const float* rope_cos,
-                              const float* rope_sin, int qk_norm, float ln_eps, float qk_eps,
-                              void* workspace, int64_t workspace_bytes, void* stream) {
+                              const strata_block_weights* wts, const void* rope_cs, int qk_norm,
+                              float ln_eps, float qk_eps, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
   if (!x || !y || !wts || !workspace || n_tiles < 0 || D <= 0 || H <= 0 || W <= 0)
     return STRATA_ERR_ARG;
   if (heads <= 0 || C % heads != 0) return STRATA_ERR_ARG;
@@ -219,8 +217,8 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
   const int tokens_per_tile = D * H * W;
   int r;
   if ((r = strata_layernorm_bf16(x, C, xn, C, M, C, ln_eps, stream)) != 0) return r;
-  if ((r = strata_qkv_rope_bf16(xn, C, wts->w_qkv, C, wts->b_qkv, qkv, 3 * C, M, C, hd, rope_cos,
-                                rope_sin, tokens_per_tile, H * W, qk_norm, qk_eps, stream)) != 0)
+  if ((r = strata_qkv_rope_bf16(xn, C, wts->w_qkv, C, wts->b_qkv, qkv, 3 * C, M, C, hd, rope_cs,
+                                tokens_per_tile, H * W, qk_norm, qk_eps, stream)) != 0)
     return r;
   const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(qkv);
   if ((r = strata_na3d_fwd_bf16(qp, 3 * C, qp + C, 3 * C, qp + 2 * C, 3 * C, attn, C, n_tiles, D, H,
@@ -374,8 +372,8 @@ void* g_static_scratch_addr[kMaxDevices] = {};
 
 extern "C" int strata_block_forward_static_scratch_bf16(
     const void* x, void* y, int n_tiles, int D, int H, int W, int C, int heads, int hidden, int kd,
-    int kh, int kw, const strata_block_weights* wts, const float* rope_cos, const float* rope_sin,
-    int qk_norm, float ln_eps, float qk_eps, void* stream) {
+    int kh, int kw, const strata_block_weights* wts, const void* rope_cs, int qk_norm, float ln_eps,
+    float qk_eps, void* stream) {
   if (n_tiles < 0 || D <= 0 || H <= 0 || W <= 0 || C <= 0 || hidden <= 0) return STRATA_ERR_ARG;
   const int64_t M = static_cast<int64_t>(n_tiles) * D * H * W;
   const int64_t need = strata_block_workspace_bytes(M, C, hidden);
@@ -394,6 +392,6 @@ extern "C" int strata_block_forward_static_scratch_bf16(
     g_static_scratch_addr[dev] = p;
   }
   return strata_block_forward_bf16(x, y, n_tiles, D, H, W, C, heads, hidden, kd, kh, kw, wts,
-                                   rope_cos, rope_sin, qk_norm, ln_eps, qk_eps,
+                                   rope_cs, qk_norm, ln_eps, qk_eps,
                                    g_static_scratch_addr[dev], STRATA_STATIC_SCRATCH_BYTES, stream);
 }

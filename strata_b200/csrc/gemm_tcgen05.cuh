@@ -17,6 +17,8 @@
 //   EPI_QKV_ROPE       y = rope(rmsnorm?(acc + b)) on q,k columns    (attn.qkv + RoPE + pack)
 //   EPI_GATE           y = G[m,n] * sigmoid(acc + b)                 (attn.gate_proj)
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -37,10 +39,10 @@ struct GemmParams {
   const float* bias;          // [N] or nullptr
   const __nv_bfloat16* aux;   // residual (EPI_RESIDUAL) or gated operand (EPI_GATE)
   long long ldaux;
-  // EPI_QKV_ROPE: tables [n_tiles, hw, head_dim/2] fp32; token row m belongs to tile
-  // m / tokens_per_tile and to horizontal position m % hw (depth levels share a table row).
-  const float* rope_cos;
-  const float* rope_sin;
+  // EPI_QKV_ROPE: table [n_tiles, hw, head_dim/2] of (cos, sin) pairs in IEEE half (4 bytes per
+  // rotated channel pair); token row m belongs to tile m / tokens_per_tile and to horizontal
+  // position m % hw (depth levels share a table row).
+  const uint32_t* rope_cs;
   int tokens_per_tile;
   int hw;
   int head_dim;
@@ -88,10 +90,11 @@ __device__ __forceinline__ void tma_store_wait_all() {
 // the warp holds the bias of column n0+l; `aux` holds the residual / gated operand of the same
 // columns (bf16 pairs) for the epilogues that use one; `qk_scale` is the RMS-norm factor of the
 // head these columns belong to (1 when qk norm is off).
-template <int EPI>
-__device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], int m, int n0, bool row_ok,
-                                                 float b_lane, const uint32_t (&aux)[16],
-                                                 float qk_scale, const GemmParams& p) {
+// cs: this row's (cos, sin) half pairs for the 16 channel pairs of these 32 columns.
+template <int EPI, int CS_OFF>
+__device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, float b_lane,
+                                                 const uint32_t (&aux)[16], float qk_scale,
+                                                 const uint32_t (&cs)[32], const GemmParams& p) {
   if (p.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, j);
@@ -112,26 +115,14 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], int m, int n0, 
       v[2 * j + 1] = bf16_hi(aux[j]) / (1.0f + __expf(-v[2 * j + 1]));
     }
   } else if constexpr (EPI == EPI_QKV_ROPE) {
-    if (n0 < p.rope_cols && row_ok) {
-      const int hd = p.head_dim;  // 32 or 64
-      const int half = hd >> 1;
-      const long long trow =
-          static_cast<long long>(m / p.tokens_per_tile) * p.hw + (m % p.hw);
-      const int pj0 = (n0 % hd) >> 1;  // first pair index of these columns within the head
-      const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + trow * half + pj0);
-      const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + trow * half + pj0);
+    if (rotate) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float4 c = __ldg(cp + q);
-        const float4 s = __ldg(sp + q);
-        const float cc[4] = {c.x, c.y, c.z, c.w};
-        const float sn[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float a = v[8 * q + 2 * t] * qk_scale, b = v[8 * q + 2 * t + 1] * qk_scale;
-          v[8 * q + 2 * t] = a * cc[t] - b * sn[t];
-          v[8 * q + 2 * t + 1] = a * sn[t] + b * cc[t];
-        }
+      for (int j = 0; j < 16; ++j) {
+        const float2 t =
+            __half22float2(*reinterpret_cast<const __half2*>(&cs[CS_OFF + j]));  // (cos, sin)
+        const float a = v[2 * j] * qk_scale, b = v[2 * j + 1] * qk_scale;
+        v[2 * j] = a * t.x - b * t.y;
+        v[2 * j + 1] = a * t.y + b * t.x;
       }
     }
   }
@@ -279,6 +270,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m = m_warp + lane;
       const bool row_ok = m < p.M;
       const int n_warp0 = n_tile0 + col_half * HALF_COLS;
+      // EPI_QKV_ROPE: this row's rotation table (one 4-byte (cos, sin) pair per channel pair of
+      // a head) is the same for every q / k head, so it is fetched once per tile - before the
+      // accumulator is waited for, which hides the load latency.
+      uint32_t cs[32];
+      bool rope_tile = false;
+      if constexpr (EPI == EPI_QKV_ROPE) {
+        rope_tile = (p.rope_cs != nullptr) && (n_warp0 < p.rope_cols) && row_ok;
+        if (rope_tile) {
+          const int half = p.head_dim >> 1;
+          const long long trow =
+              static_cast<long long>(m / p.tokens_per_tile) * p.hw + (m % p.hw);
+          const uint4* src = reinterpret_cast<const uint4*>(p.rope_cs + trow * half);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (q * 4 < half) {
+              const uint4 t = __ldg(src + q);
+              cs[4 * q] = t.x; cs[4 * q + 1] = t.y; cs[4 * q + 2] = t.z; cs[4 * q + 3] = t.w;
+            }
+          }
+        }
+      }
       bool acc_ready = false;
 #pragma unroll 1
       for (int c = 0; c < NCHUNK; ++c) {
@@ -375,7 +387,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                              : "memory");
               }
             }
-            gemm_epilogue_32<EPI>(v, m, n0 + 32 * hh, row_ok, b_lane[hh], aux, qk_scale[hh], p);
+            // head_dim 64: the two halves of a chunk use table pairs [0,16) and [16,32);
+            // head_dim 32: each half is a whole head and uses pairs [0,16)
+            const bool rotate = rope_tile && (n0 < p.rope_cols);
+            if (hh == 1 && p.head_dim == 64)
+              gemm_epilogue_32<EPI, 16>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
+            else
+              gemm_epilogue_32<EPI, 0>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);

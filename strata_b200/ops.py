@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
+from .rope import pack_rope_tables
 
 EPI_BIAS = 0
 EPI_GELU = 1
@@ -46,6 +47,24 @@ def _f32_or_none(t, name):
     if t.dtype != torch.float32:
         raise TypeError(f"{name} must be float32")
     return t.contiguous()
+
+
+def _rope_cs(rope_cos, rope_sin, rope_cs, want_shape, device):
+    """Packed half (cos, sin) table for the kernels, from fp32 tables unless already packed."""
+    if rope_cs is None:
+        if rope_cos is None:
+            return None
+        rope_cos = _f32_or_none(rope_cos, "rope_cos")
+        rope_sin = _f32_or_none(rope_sin, "rope_sin")
+        if tuple(rope_cos.shape) != want_shape or tuple(rope_sin.shape) != want_shape:
+            raise ValueError(f"rope tables must be {want_shape}, got {tuple(rope_cos.shape)}")
+        rope_cs = pack_rope_tables(rope_cos, rope_sin)
+    if rope_cs.dtype != torch.float16 or tuple(rope_cs.shape) != (*want_shape, 2):
+        raise ValueError(f"rope_cs must be float16 {(*want_shape, 2)}, got {rope_cs.dtype} "
+                         f"{tuple(rope_cs.shape)}")
+    if not rope_cs.is_cuda:
+        rope_cs = rope_cs.to(device)
+    return rope_cs.contiguous()
 
 
 def layernorm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -97,8 +116,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 def qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, head_dim: int,
              rope_cos: torch.Tensor | None, rope_sin: torch.Tensor | None, tokens_per_tile: int,
-             hw: int, qk_norm: bool = False, qk_eps: float = 1e-6) -> torch.Tensor:
-    """Fused QKV projection + optional qk RMS norm + rotary embedding; returns [M, 3C]."""
+             hw: int, qk_norm: bool = False, qk_eps: float = 1e-6,
+             rope_cs: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused QKV projection + optional qk RMS norm + rotary embedding; returns [M, 3C].
+    Tables: fp32 rope_cos / rope_sin [n_tiles, hw, head_dim/2], or the packed half table
+    rope_cs (see rope.pack_rope_tables)."""
     _require_cuda_bf16(x, "x")
     _require_cuda_bf16(weight, "weight")
     x2, M, C, ldx = _as_rows(x, "x")
@@ -106,20 +128,14 @@ def qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, h
         raise ValueError(f"qkv weight must be [{3 * C}, {C}], got {tuple(weight.shape)}")
     w = weight if weight.stride(1) == 1 else weight.contiguous()
     bias = _f32_or_none(bias, "bias")
-    rope_cos = _f32_or_none(rope_cos, "rope_cos")
-    rope_sin = _f32_or_none(rope_sin, "rope_sin")
-    if rope_cos is not None:
-        n_tiles = M // max(tokens_per_tile, 1)
-        want = (n_tiles, hw, head_dim // 2)
-        if tuple(rope_cos.shape) != want or tuple(rope_sin.shape) != want:
-            raise ValueError(f"rope tables must be {want}, got {tuple(rope_cos.shape)}")
+    n_tiles = M // max(tokens_per_tile, 1)
+    cs = _rope_cs(rope_cos, rope_sin, rope_cs, (n_tiles, hw, head_dim // 2), x.device)
     out = torch.empty((M, 3 * C), dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().strata_qkv_rope_bf16(
             x2.data_ptr(), ldx, w.data_ptr(), w.stride(0),
             None if bias is None else bias.data_ptr(), out.data_ptr(), 3 * C, M, C, head_dim,
-            None if rope_cos is None else rope_cos.data_ptr(),
-            None if rope_sin is None else rope_sin.data_ptr(), int(tokens_per_tile), int(hw),
+            None if cs is None else cs.data_ptr(), int(tokens_per_tile), int(hw),
             1 if qk_norm else 0, float(qk_eps), _stream_ptr(x)), "strata_qkv_rope_bf16")
     return out
 
@@ -166,7 +182,8 @@ def block_workspace_bytes(M: int, C: int, hidden: int) -> int:
 def block_forward(x: torch.Tensor, weights: dict, *, grid, num_heads: int, kernel,
                   rope_cos: torch.Tensor | None, rope_sin: torch.Tensor | None,
                   qk_norm: bool = False, ln_eps: float = 1e-6, qk_eps: float = 1e-6,
-                  workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
+                  workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                  rope_cs: torch.Tensor | None = None):
     """One backbone block through strata_block_forward_bf16.
 
     x: [n_tiles, D*H*W, C] bf16 contiguous. weights: bf16 'w_*' [out,in] and fp32 'b_*'
@@ -206,17 +223,13 @@ def block_forward(x: torch.Tensor, weights: dict, *, grid, num_heads: int, kerne
             keep.append(b)
         setattr(wstruct, f"w_{name}", None if w is None else w.data_ptr())
         setattr(wstruct, f"b_{name}", None if b is None else b.data_ptr())
-    rc = _f32_or_none(rope_cos, "rope_cos")
-    rs = _f32_or_none(rope_sin, "rope_sin")
-    if rc is not None and tuple(rc.shape) != (n_tiles, H * W, (C // num_heads) // 2):
-        raise ValueError(f"rope tables must be {(n_tiles, H * W, (C // num_heads) // 2)}, "
-                         f"got {tuple(rc.shape)}")
+    cs = _rope_cs(rope_cos, rope_sin, rope_cs, (n_tiles, H * W, (C // num_heads) // 2), x.device)
     import ctypes
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().strata_block_forward_bf16(
             x.data_ptr(), out.data_ptr(), n_tiles, D, H, W, C, num_heads, hidden, kd, kh, kw,
-            ctypes.byref(wstruct), None if rc is None else rc.data_ptr(),
-            None if rs is None else rs.data_ptr(), 1 if qk_norm else 0, float(ln_eps),
+            ctypes.byref(wstruct), None if cs is None else cs.data_ptr(),
+            1 if qk_norm else 0, float(ln_eps),
             float(qk_eps), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
             _stream_ptr(x)), "strata_block_forward_bf16")
     return out

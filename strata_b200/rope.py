@@ -87,3 +87,9 @@ def axial_rope_tables(h: int, w: int, head_dim: int, theta: float = 100.0, devic
     c = build_axial_token_coords(1, h, w, device=device)
     cos, sin = build_axial_rope_cos_sin_2d_continuous(c[:, 0], c[:, 1], head_dim, theta)
     return cos[None], sin[None]
+
+
+def pack_rope_tables(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """[n_tiles, hw, head_dim/2] fp32 cos / sin -> [n_tiles, hw, head_dim/2, 2] IEEE half
+    (cos, sin) pairs: the 4-bytes-per-pair table the fused QKV kernel reads."""
+    return torch.stack([cos, sin], dim=-1).to(torch.float16).contiguous()

@@ -84,8 +84,6 @@ class StrataTransformer3DBlock(nn.Module):
 
     def device_weights(self) -> dict:
         """bf16 weights / fp32 biases for the C ABI, re-cast whenever a parameter changes."""
-        params = [self.attn.qkv.weight, self.attn.proj.weight, self.mlp.layers[0].weight,
-                  self.mlp.layers[2].weight]
         key = tuple((p.data_ptr(), p._version, p.device) for p in self.parameters())
         if self._bf16_cache is not None and key == self._bf16_key:
             return self._bf16_cache
@@ -103,19 +101,19 @@ class StrataTransformer3DBlock(nn.Module):
         if hasattr(self.attn, "gate_proj"):
             cache["w_gate"], cache["b_gate"] = w(self.attn.gate_proj), b(self.attn.gate_proj)
         self._bf16_cache, self._bf16_key = cache, key
-        del params
         return cache
 
-    def forward(self, x: torch.Tensor, grid, rope_cos, rope_sin, workspace=None) -> torch.Tensor:
-        """x: [n_tiles, D*H*W, C] bf16 contiguous; returns the same shape."""
+    def forward(self, x: torch.Tensor, grid, rope_cs, workspace=None) -> torch.Tensor:
+        """x: [n_tiles, D*H*W, C] bf16 contiguous; rope_cs: packed half (cos, sin) table or
+        None; returns the same shape as x."""
         if not self._gelu_is_tanh():
             raise RuntimeError(
                 "the fused MLP kernel implements the tanh GELU the Strata checkpoints were "
                 "trained with; this block's Mlp still holds an exact GELU (the wrapper's "
                 "tanh swap did not run)")
         return ops.block_forward(x, self.device_weights(), grid=grid, num_heads=self.num_heads,
-                                 kernel=self.kernel, rope_cos=rope_cos, rope_sin=rope_sin,
-                                 qk_norm=self.qk_norm, workspace=workspace)
+                                 kernel=self.kernel, rope_cos=None, rope_sin=None,
+                                 rope_cs=rope_cs, qk_norm=self.qk_norm, workspace=workspace)
 
 
 class FinalLayer(nn.Module):
@@ -211,9 +209,10 @@ class StrataTransformer3D(nn.Module):
     def forward_tokens(self, tokens: torch.Tensor, grid, rope_cos, rope_sin) -> torch.Tensor:
         """Runs the block stack on bf16 tokens [n_tiles, D*H*W, C]."""
         ws = self._get_workspace(tokens.shape[0] * tokens.shape[1], tokens.device)
+        cs = None if rope_cos is None else rope.pack_rope_tables(rope_cos, rope_sin)
         x = tokens
         for blk in self.blocks:
-            x = blk(x, grid, rope_cos, rope_sin, workspace=ws)
+            x = blk(x, grid, cs, workspace=ws)
         return x
 
     def forward(self, x: torch.Tensor, pos: torch.Tensor | None = None) -> torch.Tensor:

@@ -43,7 +43,9 @@ def test_static_scratch_block_matches_workspace_block():
     ws_struct = _weights_struct(w)
     lat, lon = tile_latlon(n_tiles, H, W)
     cos, sin = bo.stereographic_rope_tables(lat, lon, C // heads, 1, bo.default_rope_length_scale(1))
+    from strata_b200.rope import pack_rope_tables
     cos, sin = cos.cuda().contiguous(), sin.cuda().contiguous()
+    cs = pack_rope_tables(cos, sin)
     stream = torch.cuda.current_stream().cuda_stream
 
     for call in range(2):                     # two calls in a row share the built-in array
@@ -54,7 +56,7 @@ def test_static_scratch_block_matches_workspace_block():
         got = torch.full_like(x, float("nan"))
         rc = lib.strata_block_forward_static_scratch_bf16(
             x.data_ptr(), got.data_ptr(), n_tiles, D, H, W, C, heads, hidden, *kernel,
-            ctypes.byref(ws_struct), cos.data_ptr(), sin.data_ptr(), 0, 1e-6, 1e-6, stream)
+            ctypes.byref(ws_struct), cs.data_ptr(), 0, 1e-6, 1e-6, stream)
         assert rc == 0, lib.strata_error_string(rc)
         assert _lib.device_status() == 0
         assert not torch.isnan(got).any()
@@ -72,6 +74,6 @@ def test_static_scratch_rejects_oversized_problem():
     s = _lib.BlockWeights()
     rc = lib.strata_block_forward_static_scratch_bf16(
         dummy.data_ptr(), dummy.data_ptr(), n_tiles, D, H, W, C, heads, hidden, 3, 9, 9,
-        ctypes.byref(s), None, None, 0, 1e-6, 1e-6, None)
+        ctypes.byref(s), None, 0, 1e-6, 1e-6, None)
     assert rc == -4
     assert b"64 MiB" in lib.strata_error_string(rc)
