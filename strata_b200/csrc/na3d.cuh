@@ -44,6 +44,12 @@
 #include "common.cuh"
 #include "tensormap.cuh"
 
+// Key-row width up to which four softmax groups are used (wider key blocks need the TMEM
+// columns for S and run with two).
+#ifndef NA_NG4_MAX_EW
+#define NA_NG4_MAX_EW 16
+#endif
+
 namespace strata {
 
 struct Na3dParams {
@@ -63,7 +69,7 @@ constexpr int NA_TMEM_COLS = 512;
 template <int KW>
 struct Na3dCfg {
   static constexpr int EW = NA_QW + KW - 1;
-  static constexpr int NG = (EW <= 16) ? 4 : 2;                 // softmax groups
+  static constexpr int NG = (EW <= NA_NG4_MAX_EW) ? 4 : 2;      // softmax groups
   static constexpr int EWP = (NG == 4) ? (EW + 7) / 8 * 8 : (EW + 3) / 4 * 4;
   static constexpr int NKEYS = 8 * EWP;
   static constexpr int RPG = 8 / NG;                            // key rows per group
@@ -171,12 +177,15 @@ __device__ __forceinline__ void tmem_st_x2(uint32_t taddr, const uint32_t* r) {
                ::"r"(taddr), "r"(r[0]), "r"(r[1])
                : "memory");
 }
-// Stores N (4, 8, 10 or 12) consecutive 32-bit columns of this thread's row.
+// Stores N (4, 6, 8, 10 or 12) consecutive 32-bit columns of this thread's row.
 template <int N>
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
-  static_assert(N == 4 || N == 8 || N == 10 || N == 12, "unsupported column count");
+  static_assert(N == 4 || N == 6 || N == 8 || N == 10 || N == 12, "unsupported column count");
   if constexpr (N == 4) {
     tmem_st_x4(taddr, r);
+  } else if constexpr (N == 6) {
+    tmem_st_x4(taddr, r);
+    tmem_st_x2(taddr + 4, r + 4);
   } else {
     tmem_st_x8(taddr, r);
     if constexpr (N == 10) tmem_st_x2(taddr + 8, r + 8);
@@ -185,30 +194,6 @@ __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) 
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-// Packed fp32x2 arithmetic (sm_100): one instruction for two lanes of a 64-bit register pair.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
