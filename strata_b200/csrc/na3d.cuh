@@ -471,88 +471,132 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + RPG * grp)) & ROWBITS) : 0u;
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
 
-        // pass 1: masked maximum of the scaled scores over this thread's key rows
-        float bm = -1e30f;
+        // The reference of a key group moves only when a block maximum exceeds it by more than
+        // 2^8 (P stays well inside bf16 / fp32 range otherwise) - or is adopted for free while
+        // nothing has been accumulated yet. Moving it rescales the TMEM accumulator, which must
+        // wait for the previous block's P V (o_full of that block's parity; S of the current
+        // block being complete implies P V of block gb-2 is, so the parity wait cannot alias).
+        auto apply_reference = [&](float bm) -> bool {
+          const bool fresh = l_run == 0.f;
+          const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
+          const bool rescale = grow && !fresh;
+          if (__any_sync(0xffffffffu, rescale)) {
+            if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
+                           ST_TIMEOUT_SOFTMAX))
+              return false;
+            tc_fence_after();
+            const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
+            l_run *= alpha;
+#pragma unroll 1
+            for (int hh = 0; hh < 4; ++hh) {
+              uint32_t ob[16];
+              tmem_ld_x16(o_taddr + 16 * hh, ob);
+              tmem_ld_wait();
 #pragma unroll
-        for (int rr = 0; rr < RPG; ++rr) {
-          if ((warp_rows >> rr) & 1u) {
-            uint32_t a[EWP];
-            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
-            tmem_ld_wait();
-            float rm0 = -1e30f, rm1 = -1e30f;
-#pragma unroll
-            for (int k2 = 0; k2 < EW / 2; ++k2) {
-              float t0, t1;
-              unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-              if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
+              for (int j = 0; j < 16; ++j)
+                ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+              tmem_st_x16(o_taddr + 16 * hh, ob);
             }
-            bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
+            tmem_st_wait();
           }
-        }
-        // bm is the block maximum relative to the current reference. The reference moves only
-        // when it is exceeded by more than 2^8 (P stays well inside bf16 / fp32 range
-        // otherwise) - or is adopted for free while nothing has been accumulated yet. Moving
-        // it rescales the TMEM accumulator, which must wait for the previous block's P V
-        // (o_full of that block's parity; S of the current block being complete implies P V of
-        // block gb-2 is, so the parity wait cannot alias).
-        const bool fresh = l_run == 0.f;
-        const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
-        const bool rescale = grow && !fresh;
-        const bool any_rescale = __any_sync(0xffffffffu, rescale);
-        if (any_rescale) {
-          if (!mbar_wait(o_full((gb - 1u) & 1u), ((gb - 1u) >> 1) & 1u, abort_flag,
-                         ST_TIMEOUT_SOFTMAX)) {
+          if (grow) {
+            mc += bm;
+            set_nb(mc);
+          }
+          return true;
+        };
+
+        // While some query of the warp has no reference yet, the block maximum is taken first
+        // (pass 1). Afterwards a block is handled in a single pass against the current reference;
+        // its maximum is tracked on the side and, should it overshoot the 2^8 margin (rare), the
+        // reference is moved and the block is redone before anything is stored.
+        // (With four groups the register budget is too tight for the extra bookkeeping, and the
+        // two-pass form is used for every block.)
+        constexpr bool SINGLE_PASS = (NG == 2);
+        bool settled = SINGLE_PASS ? __any_sync(0xffffffffu, l_run == 0.f) : true;
+        if (settled) {
+          float bm = -1e30f;
+#pragma unroll
+          for (int rr = 0; rr < RPG; ++rr) {
+            if ((warp_rows >> rr) & 1u) {
+              uint32_t a[EWP];
+              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+              tmem_ld_wait();
+              float rm0 = -1e30f, rm1 = -1e30f;
+#pragma unroll
+              for (int k2 = 0; k2 < EW / 2; ++k2) {
+                float t0, t1;
+                unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
+              }
+              bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
+            }
+          }
+          if (!apply_reference(bm)) {
             ok = false;
             break;
           }
-          tc_fence_after();
-          const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
-          l_run *= alpha;
-#pragma unroll 1
-          for (int hh = 0; hh < 4; ++hh) {
-            uint32_t ob[16];
-            tmem_ld_x16(o_taddr + 16 * hh, ob);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
-            tmem_st_x16(o_taddr + 16 * hh, ob);
-          }
-          tmem_st_wait();
-        }
-        if (grow) {
-          mc += bm;
-          set_nb(mc);
         }
 
-        // pass 2: exponentials, row sum, bf16 P (two keys per 32-bit column) written over the
-        // already consumed part of this thread's own S segment: P of key row rr goes to columns
-        // [rr*EWP/2, (rr+1)*EWP/2) of the segment, which S rows > rr do not occupy.
-        uint64_t rs2 = 0ull;
+        // exponentials, row sum and bf16 P (two keys per 32-bit column), held in registers
+        // until the block is known to be final
+        uint32_t pk[RPG][Cfg::PCOLS_ROW];
+        uint64_t rs2;
+#pragma unroll 1
+        while (true) {
+          rs2 = 0ull;
+          float tm0 = -1e30f, tm1 = -1e30f;
 #pragma unroll
-        for (int rr = 0; rr < RPG; ++rr) {
-          const bool need = (warp_rows >> rr) & 1u;
-          const uint32_t keep = ((rowmask >> rr) & 1u) ? 0xffffffffu : 0u;
-          uint32_t a[EWP];
-          uint32_t pk[Cfg::PCOLS_ROW];
-          uint64_t rsa = 0ull, rsb = 0ull;
-          if (need) {
-            tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
-            tmem_ld_wait();
-          }
-#pragma unroll
-          for (int k2 = 0; k2 < Cfg::PCOLS_ROW; ++k2) {
-            uint32_t packed = 0u;
-            if (need && k2 < EW / 2) {
-              float t0, t1;
-              unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-              if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
-              packed = pack_bf16(p0, p1) & keep;
+          for (int rr = 0; rr < RPG; ++rr) {
+            const bool need = (warp_rows >> rr) & 1u;
+            const bool mine = (rowmask >> rr) & 1u;
+            const uint32_t keep = mine ? 0xffffffffu : 0u;
+            uint32_t a[EWP];
+            uint64_t rsa = 0ull, rsb = 0ull;
+            float rm0 = -1e30f, rm1 = -1e30f;
+            if (need) {
+              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
+              tmem_ld_wait();
             }
-            pk[k2] = packed;
+#pragma unroll
+            for (int k2 = 0; k2 < Cfg::PCOLS_ROW; ++k2) {
+              uint32_t packed = 0u;
+              if (need && k2 < EW / 2) {
+                float t0, t1;
+                unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                if constexpr (SINGLE_PASS) {
+                  if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
+                }
+                const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
+                packed = pack_bf16(p0, p1) & keep;
+              }
+              pk[rr][k2] = packed;
+            }
+            if constexpr (!SINGLE_PASS)   // final already: store this row's P right away
+              tmem_st_cols<Cfg::PCOLS_ROW>(s_taddr + rr * Cfg::PCOLS_ROW, pk[rr]);
+            if (mine) {
+              rs2 = fadd2(rs2, fadd2(rsa, rsb));
+              tm0 = fmaxf(tm0, rm0);
+              tm1 = fmaxf(tm1, rm1);
+            }
           }
-          tmem_st_cols<Cfg::PCOLS_ROW>(s_taddr + rr * Cfg::PCOLS_ROW, pk);
-          if (keep) rs2 = fadd2(rs2, fadd2(rsa, rsb));
+          if (!SINGLE_PASS || settled) break;
+          const float tmax = fmaxf(tm0, tm1);
+          if (!__any_sync(0xffffffffu, tmax > 8.0f)) break;
+          settled = true;
+          if (!apply_reference(tmax > 8.0f ? tmax : -1e30f)) {
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) break;
+        // P of key row rr goes to columns [rr*EWP/2, (rr+1)*EWP/2) of this thread's own S
+        // segment: the S values are consumed, and no other thread reads this lane.
+        if constexpr (SINGLE_PASS) {
+#pragma unroll
+          for (int rr = 0; rr < RPG; ++rr)
+            tmem_st_cols<Cfg::PCOLS_ROW>(s_taddr + rr * Cfg::PCOLS_ROW, pk[rr]);
         }
         {
           float r0, r1;

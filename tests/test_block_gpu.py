@@ -128,6 +128,25 @@ def test_na3d_matches_oracle(ops, B, D, H, W, nh, kernel):
     assert rel_max_err(o, ref) < TOL_BF16
 
 
+@pytest.mark.parametrize("kernel,shape", [((3, 9, 9), (1, 6, 24, 24, 2)), ((5, 13, 13), (1, 8, 26, 26, 1)),
+                                          ((3, 15, 15), (1, 4, 20, 20, 1))])
+def test_na3d_large_score_range(ops, kernel, shape):
+    # Scores spread over hundreds of log2 units: the running reference of the online softmax
+    # has to move several times per query (rescaling the accumulator, and - in the single-pass
+    # variants - redoing a key block), and later keys dominate earlier ones completely.
+    B, D, H, W, nh = shape
+    g = torch.Generator().manual_seed(77)
+    q = (torch.randn(B, D, H, W, nh, 64, generator=g) * 3).bfloat16()
+    ramp = 1.0 + torch.arange(D).view(1, D, 1, 1, 1, 1) * 1.5 + torch.arange(H).view(1, 1, H, 1, 1, 1) * 0.2
+    k = (torch.randn(B, D, H, W, nh, 64, generator=g) * ramp).bfloat16()
+    v = torch.randn(B, D, H, W, nh, 64, generator=g).bfloat16()
+    o = ops.na3d(q.cuda(), k.cuda(), v.cuda(), kernel)
+    assert _status() == 0
+    assert torch.isfinite(o).all()
+    ref = bo.na3d(q.float(), k.float(), v.float(), kernel)
+    assert rel_max_err(o, ref) < TOL_BF16
+
+
 def test_na3d_packed_qkv_views_and_unwritten_cells(ops):
     B, D, H, W, nh = 2, 4, 16, 16, 2
     g = torch.Generator().manual_seed(5)
