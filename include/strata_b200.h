@@ -149,6 +149,38 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
                                   const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
                                   int T, int halo, int64_t L, void* stream);
 
+/* Per-block K/V halo (token space, halo exchange every block). The packed qkv rows of each rank
+ * live in halo-padded layout [tiles_per_rank, D, P*P, ldqkv] (channels q | k | v, C each); the
+ * interiors are written by strata_qkv_rope_padded_bf16. This call fills the k and v channels of
+ * the halo cells of `qkv` from the owning tiles' interiors (h_peer_qkv[r]: rank r's padded qkv
+ * buffer as mapped into this process), following the same gather maps as above. K is stored by
+ * its owner rotated in the owner's RoPE frame and is re-rotated into this tile's frame with
+ * dcs_a / dcs_b: [tiles_per_rank, P*P, head_dim/2] (cos, sin) half pairs of the angle difference
+ * receiver - sender for the cell's first / second source. New relative to the reference, which
+ * exchanges halos once per model step in field space (scripts/ace/run_screamcast_nudged.py:455). */
+int strata_halo_gather_kv_bf16(void* qkv, const void* const* h_peer_qkv, int world,
+                               const int32_t* src_a, const int32_t* src_b, const void* dcs_a,
+                               const void* dcs_b, int tiles_per_rank, int D, int T, int halo, int C,
+                               int head_dim, int64_t ldqkv, void* stream);
+
+/* strata_qkv_rope_bf16 whose M = n_tiles*pad_D*pad_T*pad_T input rows are the interior tokens of
+ * tiles and whose output rows go to the interior of the halo-padded layout
+ * [n_tiles, pad_D, P*P, ldqkv], P = pad_T + 2*pad_halo (pad_T a multiple of 32). */
+int strata_qkv_rope_padded_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
+                                const float* bias, void* qkv_padded, int64_t ldqkv, int M, int C,
+                                int head_dim, const void* rope_cs, int tokens_per_tile, int hw,
+                                int qk_norm, float qk_eps, int pad_T, int pad_halo, int pad_D,
+                                void* stream);
+
+/* strata_na3d_fwd_bf16 restricted to a query region: only tokens with h in [q_h0, q_h0+q_H) and
+ * w in [q_w0, q_w0+q_W) are queries (the interior of a halo-padded tile); keys come from the
+ * whole [H, W] plane, windows clamp at the plane's (padded) borders, and out is written
+ * compactly as [B, D, q_H, q_W, ldo]. */
+int strata_na3d_fwd_region_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
+                                const void* v, int64_t ldv, void* out, int64_t ldo, int B, int D,
+                                int H, int W, int heads, int head_dim, int kd, int kh, int kw,
+                                float scale, int q_h0, int q_H, int q_w0, int q_W, void* stream);
+
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
  * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work

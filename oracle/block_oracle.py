@@ -344,3 +344,59 @@ def backbone_forward(x: torch.Tensor, state: dict, *, patch, num_heads: int, ker
         y = y.clone()
         y[:, u], y[:, v] = torch.from_numpy(ug), torch.from_numpy(vg)
     return y
+
+
+# --------------------------------------------------------------------------- per-block halo
+def tiled_block_forward(x_all: torch.Tensor, params: dict, *, face: int, tile: int, halo: int,
+                        depth: int, num_heads: int, kernel, lat_deg, lon_deg,
+                        rope_base: float = 100.0, length_scale: float | None = None,
+                        qk_norm: bool = False, gated: bool = False, return_attention: bool = False):
+    """One block over ALL tiles of a cubed sphere with a K/V halo exchange inside the block.
+
+    x_all [G, depth*tile*tile, C] (global tile order); lat_deg / lon_deg [G, tile, tile].
+    Only interior tokens are queries. Every tile sees its neighbours' pre-RoPE keys and values
+    through the copy-halo maps (halo_oracle), and rotates ALL keys of its padded plane in its
+    own stereographic frame (centre = spherical centroid of its interior). Returns [G, ...].
+    """
+    import numpy as np
+    from oracle import halo_oracle as ho
+    G, Ttok, C = x_all.shape
+    T, h, P, D = tile, halo, tile + 2 * halo, depth
+    hd = C // num_heads
+    scale = length_scale or default_rope_length_scale(1)
+    x = x_all.float()
+    xn = F.layer_norm(x, (C,), eps=LN_EPS)
+    qkv = F.linear(xn, params["attn.qkv.weight"].float(), params["attn.qkv.bias"].float())
+    qkv = qkv.reshape(G, D, T, T, 3, num_heads, hd)
+    q, k, v = qkv[..., 0, :, :], qkv[..., 1, :, :], qkv[..., 2, :, :]
+    if qk_norm:
+        q, k = rms_norm(q), rms_norm(k)
+    topo = ho.TileTopology(1, 0, face, tile, halo)
+
+    def pad(t):   # [G, D, T, T, nh, hd] -> [G, D, P, P, nh, hd] via the copy halo
+        lead = t.permute(1, 4, 5, 0, 2, 3).numpy()                       # [D, nh, hd, G, T, T]
+        return torch.from_numpy(ho.padded_local_tiles(lead, topo)).permute(3, 0, 4, 5, 1, 2)
+    kp, vp = pad(k), pad(v)
+    # receiver-frame coordinates of every padded cell
+    la, lo = np.radians(np.asarray(lat_deg)), np.radians(np.asarray(lon_deg))
+    xyz = np.stack([np.cos(la) * np.cos(lo), np.cos(la) * np.sin(lo), np.sin(la)])
+    pxyz = ho.padded_local_tiles(xyz, topo)                              # [3, G, P, P]
+    plat = torch.from_numpy(np.arctan2(pxyz[2], np.hypot(pxyz[0], pxyz[1])))
+    plon = torch.from_numpy(np.arctan2(pxyz[1], pxyz[0]))
+    lat0, lon0 = spherical_centroid(torch.from_numpy(la), torch.from_numpy(lo))
+    px, py = stereographic_projection(plat, plon, lat0, lon0)
+    cos, sin = rope_tables_from_coords((px / scale).flatten(1), (py / scale).flatten(1), hd, rope_base)
+    kp = apply_rope(kp.reshape(G, D, P * P, num_heads, hd), cos, sin).reshape(G, D, P, P, num_heads, hd)
+    qp = torch.zeros(G, D, P, P, num_heads, hd)
+    qp[:, :, h:h + T, h:h + T] = q
+    qp = apply_rope(qp.reshape(G, D, P * P, num_heads, hd), cos, sin).reshape(G, D, P, P, num_heads, hd)
+    o = na3d(qp, kp, vp, kernel)[:, :, h:h + T, h:h + T].reshape(G, Ttok, C)
+    if return_attention:
+        return o
+    if gated:
+        g = F.linear(xn, params["attn.gate_proj.weight"].float(), params["attn.gate_proj.bias"].float())
+        o = o * torch.sigmoid(g)
+    x1 = x + F.linear(o, params["attn.proj.weight"].float(), params["attn.proj.bias"].float())
+    hmid = F.gelu(F.linear(F.layer_norm(x1, (C,), eps=LN_EPS), params["mlp.layers.0.weight"].float(),
+                           params["mlp.layers.0.bias"].float()), approximate="tanh")
+    return x1 + F.linear(hmid, params["mlp.layers.2.weight"].float(), params["mlp.layers.2.bias"].float())

@@ -119,10 +119,10 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
   }
 }
 
-int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+static int qkv_rope_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                          void* qkv, int64_t ldqkv, int M, int C, int head_dim,
                          const void* rope_cs, int tokens_per_tile, int hw, int qk_norm,
-                         float qk_eps, void* stream) {
+                         float qk_eps, int pad_T, int pad_halo, int pad_D, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (M == 0 && C > 0) return STRATA_OK;
@@ -151,6 +151,12 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.rope_cols = 2 * C;
   p.qk_norm = qk_norm;
   p.qk_eps = qk_eps;
+  if (pad_T > 0) {
+    if (pad_T % 32 != 0 || pad_halo < 0 || pad_D < 1 ||
+        M % (pad_D * pad_T * pad_T) != 0)
+      return STRATA_ERR_ARG;
+    p.pad_T = pad_T; p.pad_h = pad_halo; p.pad_D = pad_D;
+  }
   const auto* A = static_cast<const __nv_bfloat16*>(x);
   const auto* W = static_cast<const __nv_bfloat16*>(w);
   if (!rope_cs && !qk_norm) return launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
@@ -158,10 +164,28 @@ int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
   return launch_gemm<EPI_QKV_ROPE>(A, ldx, W, ldw, p, sms, as_stream(stream));
 }
 
-int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
-                         int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W,
-                         int heads, int head_dim, int kd, int kh, int kw, float scale,
-                         void* stream) {
+int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                         void* qkv, int64_t ldqkv, int M, int C, int head_dim,
+                         const void* rope_cs, int tokens_per_tile, int hw, int qk_norm,
+                         float qk_eps, void* stream) {
+  return qkv_rope_impl(x, ldx, w, ldw, bias, qkv, ldqkv, M, C, head_dim, rope_cs, tokens_per_tile,
+                       hw, qk_norm, qk_eps, 0, 0, 0, stream);
+}
+
+int strata_qkv_rope_padded_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw,
+                                const float* bias, void* qkv_padded, int64_t ldqkv, int M, int C,
+                                int head_dim, const void* rope_cs, int tokens_per_tile, int hw,
+                                int qk_norm, float qk_eps, int pad_T, int pad_halo, int pad_D,
+                                void* stream) {
+  if (pad_T <= 0) return STRATA_ERR_ARG;
+  return qkv_rope_impl(x, ldx, w, ldw, bias, qkv_padded, ldqkv, M, C, head_dim, rope_cs,
+                       tokens_per_tile, hw, qk_norm, qk_eps, pad_T, pad_halo, pad_D, stream);
+}
+
+static int na3d_impl(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                     int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W, int heads,
+                     int head_dim, int kd, int kh, int kw, float scale, int q_h0, int q_H, int q_w0,
+                     int q_W, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (!q || !k || !v || !out || B < 0 || D <= 0 || H <= 0 || W <= 0 || heads <= 0)
@@ -177,10 +201,28 @@ int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
   int r = launch_na3d(static_cast<const __nv_bfloat16*>(q), ldq,
                       static_cast<const __nv_bfloat16*>(k), ldk,
                       static_cast<const __nv_bfloat16*>(v), ldv, static_cast<__nv_bfloat16*>(out),
-                      ldo, B, D, H, W, heads, kd, kh, kw, sc, sms, as_stream(stream));
+                      ldo, B, D, H, W, heads, kd, kh, kw, sc, sms, as_stream(stream), q_h0, q_H,
+                      q_w0, q_W);
   if (r == -1) return STRATA_ERR_ARG;
   if (r == -2) return STRATA_ERR_UNSUPPORTED;
   return r;
+}
+
+int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                         int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W,
+                         int heads, int head_dim, int kd, int kh, int kw, float scale,
+                         void* stream) {
+  return na3d_impl(q, ldq, k, ldk, v, ldv, out, ldo, B, D, H, W, heads, head_dim, kd, kh, kw,
+                   scale, 0, -1, 0, -1, stream);
+}
+
+int strata_na3d_fwd_region_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
+                                const void* v, int64_t ldv, void* out, int64_t ldo, int B, int D,
+                                int H, int W, int heads, int head_dim, int kd, int kh, int kw,
+                                float scale, int q_h0, int q_H, int q_w0, int q_W, void* stream) {
+  if (q_h0 < 0 || q_w0 < 0 || q_H < 1 || q_W < 1) return STRATA_ERR_ARG;
+  return na3d_impl(q, ldq, k, ldk, v, ldv, out, ldo, B, D, H, W, heads, head_dim, kd, kh, kw,
+                   scale, q_h0, q_H, q_w0, q_W, stream);
 }
 
 int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden) {
@@ -301,6 +343,41 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
   halo_gather_fields_kernel<<<grid, 256, 0, as_stream(stream)>>>(
       out, pp, src_a, src_b, static_cast<int>(ocells), static_cast<int>(cells),
       static_cast<int>(L));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_halo_gather_kv_bf16(void* qkv, const void* const* h_peer_qkv, int world,
+                               const int32_t* src_a, const int32_t* src_b, const void* dcs_a,
+                               const void* dcs_b, int tiles_per_rank, int D, int T, int halo, int C,
+                               int head_dim, int64_t ldqkv, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!qkv || !h_peer_qkv || !src_a || !src_b || !dcs_a || !dcs_b) return STRATA_ERR_ARG;
+  if (world < 1 || world > HALO_MAX_RANKS) return STRATA_ERR_UNSUPPORTED;
+  if (tiles_per_rank <= 0 || D <= 0 || T <= 0 || halo < 0 || C <= 0 || C % 8 != 0 ||
+      head_dim < 8 || head_dim % 8 != 0 || C % head_dim != 0 || ldqkv < 3 * C || ldqkv % 8 != 0)
+    return STRATA_ERR_ARG;
+  if (!aligned16(qkv) || !aligned16(dcs_a) || !aligned16(dcs_b)) return STRATA_ERR_ARG;
+  if (halo == 0) return STRATA_OK;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_qkv[r] || !aligned16(h_peer_qkv[r])) return STRATA_ERR_ARG;
+    pp.p[r] = h_peer_qkv[r];
+  }
+  const int P = T + 2 * halo;
+  const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
+  if (cells * world > 0x7fffffffLL) return STRATA_ERR_ARG;
+  if (static_cast<long long>(tiles_per_rank) * D > 65535) return STRATA_ERR_UNSUPPORTED;
+  const long long work = static_cast<long long>(P) * P * (2 * C / 8);
+  long long bx = (work + 255) / 256;
+  const long long cap = static_cast<long long>(sms) * 8;
+  if (bx > cap) bx = cap;
+  dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(tiles_per_rank * D));
+  halo_gather_kv_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), pp, src_a, src_b, static_cast<const uint32_t*>(dcs_a),
+      static_cast<const uint32_t*>(dcs_b), P, T, halo, D, C, head_dim, ldqkv,
+      static_cast<int>(cells));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }

@@ -49,7 +49,23 @@ struct GemmParams {
   int rope_cols;   // columns [0, rope_cols) are q and k
   int qk_norm;     // 1: RMS-normalise each head of q and k before the rotation
   float qk_eps;
+  // Output row remap (pad_T > 0): the M input rows are the interior tokens of tiles
+  // [tile, d, i, j] with i, j < pad_T (pad_T a multiple of 32), and row m is stored at row
+  // ((tile*pad_D + d)*P + i + pad_h)*P + j + pad_h of the output, P = pad_T + 2*pad_h: the
+  // interior of halo-padded tiles. A 32-row store box never leaves one interior row.
+  int pad_T, pad_h, pad_D;
 };
+
+// Output row of input row m under the padded-tile remap (identity when it is off).
+__device__ __forceinline__ int gemm_out_row(int m, const GemmParams& p) {
+  if (p.pad_T == 0) return m;
+  const int T = p.pad_T, P = T + 2 * p.pad_h;
+  const int j = m % T;
+  int t = m / T;
+  const int i = t % T;
+  t /= T;   // tile*pad_D + d
+  return (t * P + i + p.pad_h) * P + j + p.pad_h;
+}
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
@@ -410,7 +426,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&tmOut, stage_s, n0, m_warp);
+          tma_store_2d(&tmOut, stage_s, n0, gemm_out_row(m_warp, p));
           tma_store_commit();
         }
       }
@@ -450,7 +466,12 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
     uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M)};
     uint64_t str[1] = {static_cast<uint64_t>(p.ldo) * 2};
     uint32_t box[2] = {64, 32};
-    if (make_tmap_bf16(&tmOut, p.out, 2, dims, str, box) != 0) return -22;
+    uint64_t odims[2] = {dims[0], dims[1]};
+    if (p.pad_T > 0) {
+      const uint64_t P = static_cast<uint64_t>(p.pad_T + 2 * p.pad_h);
+      odims[1] = dims[1] / (static_cast<uint64_t>(p.pad_T) * p.pad_T) * P * P;
+    }
+    if (make_tmap_bf16(&tmOut, p.out, 2, odims, str, box) != 0) return -22;
     tmAux = tmOut;
     if (EPI == EPI_RESIDUAL || EPI == EPI_GATE) {
       uint64_t astr[1] = {static_cast<uint64_t>(p.ldaux) * 2};

@@ -15,6 +15,8 @@
 //
 // HBM-bound (remote part: NVLink-bound): payload bytes read once and written once.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace strata {
@@ -98,6 +100,86 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
       if (pb) v = (v + pb[so]) / 2.0f;
       out[static_cast<long long>(l) * n_out_cells + oc] = v;
     }
+  }
+}
+
+// Per-block K/V halo for tiles whose packed qkv rows live in halo-padded layout
+// [tiles_per_rank, D, P*P, ld] (q | k | v channel blocks of C each): the interiors were written
+// by this rank's QKV GEMM, this kernel fills the K and V channels of the halo cells from the
+// owning tiles' interiors (local or peer memory). K arrives rotated in the SENDER tile's RoPE
+// frame; it is turned into the receiver's frame on the way by the per-cell delta rotation
+// dcs[tile, cell, pair] = (cos, sin)(theta_receiver - theta_sender) (IEEE half pairs), V is
+// copied. Corner-diagonal cells average their two (individually rotated) sources.
+// grid: x over (padded cell, 16-byte vector of the 2C k|v channels), y over (tile, depth).
+__global__ void __launch_bounds__(256)
+halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
+                      const int* __restrict__ src_a, const int* __restrict__ src_b,
+                      const uint32_t* __restrict__ dcs_a, const uint32_t* __restrict__ dcs_b,
+                      int P, int T, int halo, int D, int C, int head_dim, long long ld,
+                      int cells_per_rank) {
+  const int PP = P * P, TT = T * T;
+  const int vpc = (2 * C) >> 3;     // 16-byte vectors of k|v per cell
+  const int kvec = C >> 3;          // the first kvec of them are K
+  const int half = head_dim >> 1;
+  const int tile = blockIdx.y / D;
+  const int d = blockIdx.y - tile * D;
+  const long long total = static_cast<long long>(PP) * vpc;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pc = static_cast<int>(idx / vpc);
+    const int v = static_cast<int>(idx - static_cast<long long>(pc) * vpc);
+    const int pi = pc / P, pj = pc - pi * P;
+    if (pi >= halo && pi < halo + T && pj >= halo && pj < halo + T) continue;   // interior
+    const int a = __ldg(src_a + tile * PP + pc);
+    const int b = __ldg(src_b + tile * PP + pc);
+    const long long chan = static_cast<long long>(C) + (v << 3);   // k|v start after q
+    auto load = [&](int id) {
+      const int rank = id / cells_per_rank;
+      const int local = id - rank * cells_per_rank;
+      const int st = local / TT;
+      const int sc = local - st * TT;
+      const int si = sc / T, sj = sc - si * T;
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(src.p[rank]);
+      const long long row = ((static_cast<long long>(st) * D + d) * P + si + halo) * P + sj + halo;
+      return *reinterpret_cast<const uint4*>(base + row * ld + chan);
+    };
+    auto rotate = [&](const uint4& x, const uint32_t* tab, float (&o)[8]) {
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+      if (v < kvec) {
+        const int p0 = (((v << 3) % head_dim) >> 1);   // first channel pair of this vector
+        const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(
+            tab + (static_cast<long long>(tile) * PP + pc) * half + p0));
+        const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 cs = __half22float2(*reinterpret_cast<const __half2*>(&tw[t]));
+          const float x0 = bf16_lo(w[t]), x1 = bf16_hi(w[t]);
+          o[2 * t] = x0 * cs.x - x1 * cs.y;
+          o[2 * t + 1] = x0 * cs.y + x1 * cs.x;
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          o[2 * t] = bf16_lo(w[t]);
+          o[2 * t + 1] = bf16_hi(w[t]);
+        }
+      }
+    };
+    float ra[8];
+    rotate(load(a), dcs_a, ra);
+    if (b >= 0) {
+      float rb[8];
+      rotate(load(b), dcs_b, rb);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+    }
+    uint4 o4;
+    o4.x = pack_bf16(ra[0], ra[1]);
+    o4.y = pack_bf16(ra[2], ra[3]);
+    o4.z = pack_bf16(ra[4], ra[5]);
+    o4.w = pack_bf16(ra[6], ra[7]);
+    const long long orow = (static_cast<long long>(tile) * D + d) * PP + pc;
+    *reinterpret_cast<uint4*>(qkv + orow * ld + chan) = o4;
   }
 }
 

@@ -57,6 +57,10 @@ struct Na3dParams {
   int kd, kh;            // kernel extents along depth and rows (columns: template KW)
   int QD, QH;            // query tile extents (QW = 8); QD*QH = 16
   int tiles_d, tiles_h, tiles_w;
+  // Query region: only tokens with h in [q_h0, q_h0+q_H), w in [q_w0, q_w0+q_W) are queries
+  // (the interior of a halo-padded tile; the whole plane by default). Keys come from the
+  // whole [H, W] plane. Outputs are written compactly as [B, D, q_H, q_W, ldo].
+  int q_h0, q_H, q_w0, q_W;
   int n_items;           // tiles_d*tiles_h*tiles_w*heads*B
   __nv_bfloat16* out;    // [B, D, H, W, ldo] with head h at channel offset h*64
   long long ldo;
@@ -213,7 +217,7 @@ __device__ __forceinline__ NaItem na_decode_item(int item, const Na3dParams& p) 
   const int td = t % p.tiles_d; t /= p.tiles_d;
   it.head = t % p.heads;
   it.b = t / p.heads;
-  it.d0 = td * p.QD; it.h0 = th * p.QH; it.w0 = tw * NA_QW;
+  it.d0 = td * p.QD; it.h0 = p.q_h0 + th * p.QH; it.w0 = p.q_w0 + tw * NA_QW;
   // key box origin = window start of the tile's first query on each axis
   it.bd0 = na_window_start(it.d0, p.D, p.kd);
   it.bh0 = na_window_start(it.h0, p.H, p.kh);
@@ -433,7 +437,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t gb = 0;
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
       const NaItem it = na_decode_item<KW>(item, p);
-      const bool q_ok = (it.d0 + zd < p.D) && (it.h0 + zh < p.H) && (it.w0 + zw < p.W);
+      const bool q_ok = (it.d0 + zd < p.D) && (it.h0 + zh < p.q_h0 + p.q_H) &&
+                        (it.w0 + zw < p.q_w0 + p.q_W);
       const int id = min(it.d0 + zd, p.D - 1), ih = min(it.h0 + zh, p.H - 1),
                 iw = min(it.w0 + zw, p.W - 1);
       const int wd = na_window_start(id, p.D, p.kd) - it.bd0;
@@ -658,8 +663,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_before();
         if (q_ok) {
-          const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.H +
-                                 (it.h0 + zh)) * p.W + (it.w0 + zw);
+          const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.q_H +
+                                 (it.h0 + zh - p.q_h0)) * p.q_W + (it.w0 + zw - p.q_w0);
           __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64 + WCOLS * grp;
 #pragma unroll
           for (int j = 0; j < WCOLS; j += 8) {
@@ -719,7 +724,8 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
 inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* k, long long ldk,
                        const __nv_bfloat16* v, long long ldv, __nv_bfloat16* out, long long ldo,
                        int B, int D, int H, int W, int heads, int kd, int kh, int kw, float scale,
-                       int sm_count, cudaStream_t stream) {
+                       int sm_count, cudaStream_t stream, int q_h0 = 0, int q_H = -1, int q_w0 = 0,
+                       int q_W = -1) {
   if (kd > D || kh > H || kw > W || kd < 1 || kh < 1 || kw < 1) return -1;
   if (kh > 15 || kd > 15) return -2;
   Na3dParams p{};
@@ -728,9 +734,15 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   // query tile: 2 x 8 x 8, flattened towards the rows when the tensor is shallow
   if (D >= 2) { p.QD = 2; p.QH = 8; } else { p.QD = 1; p.QH = 16; }
   if (p.QH + kh - 1 > 31) return -2;
+  p.q_h0 = q_h0; p.q_w0 = q_w0;
+  p.q_H = q_H < 0 ? H : q_H;
+  p.q_W = q_W < 0 ? W : q_W;
+  if (p.q_h0 < 0 || p.q_w0 < 0 || p.q_H < 1 || p.q_W < 1 || p.q_h0 + p.q_H > H ||
+      p.q_w0 + p.q_W > W)
+    return -1;
   p.tiles_d = (D + p.QD - 1) / p.QD;
-  p.tiles_h = (H + p.QH - 1) / p.QH;
-  p.tiles_w = (W + NA_QW - 1) / NA_QW;
+  p.tiles_h = (p.q_H + p.QH - 1) / p.QH;
+  p.tiles_w = (p.q_W + NA_QW - 1) / NA_QW;
   const long long items = static_cast<long long>(p.tiles_d) * p.tiles_h * p.tiles_w * heads * B;
   if (items > 0x7fffffffLL) return -2;
   p.n_items = static_cast<int>(items);

@@ -233,3 +233,49 @@ def block_forward(x: torch.Tensor, weights: dict, *, grid, num_heads: int, kerne
             float(qk_eps), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
             _stream_ptr(x)), "strata_block_forward_bf16")
     return out
+
+
+def qkv_rope_padded(x: torch.Tensor, weight: torch.Tensor, bias, head_dim: int,
+                    rope_cs: torch.Tensor | None, tokens_per_tile: int, hw: int, out: torch.Tensor,
+                    tile: int, halo: int, depth: int, qk_norm: bool = False,
+                    qk_eps: float = 1e-6) -> torch.Tensor:
+    """Fused QKV projection whose output rows land in the interior of halo-padded tiles.
+    x: [n_tiles*depth*tile*tile, C] interior tokens; out: [n_tiles*depth*P*P, 3C], P = tile+2*halo."""
+    _require_cuda_bf16(x, "x")
+    _require_cuda_bf16(weight, "weight")
+    _require_cuda_bf16(out, "out")
+    x2, M, C, ldx = _as_rows(x, "x")
+    P = tile + 2 * halo
+    n_tiles = M // (depth * tile * tile)
+    if out.dim() != 2 or out.shape != (n_tiles * depth * P * P, 3 * C) or out.stride(1) != 1:
+        raise ValueError(f"out must be [{n_tiles * depth * P * P}, {3 * C}]")
+    w = weight if weight.stride(1) == 1 else weight.contiguous()
+    bias = _f32_or_none(bias, "bias")
+    cs = _rope_cs(None, None, rope_cs, (n_tiles, hw, head_dim // 2), x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_qkv_rope_padded_bf16(
+            x2.data_ptr(), ldx, w.data_ptr(), w.stride(0),
+            None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0), M, C, head_dim,
+            None if cs is None else cs.data_ptr(), int(tokens_per_tile), int(hw),
+            1 if qk_norm else 0, float(qk_eps), int(tile), int(halo), int(depth), _stream_ptr(x)),
+            "strata_qkv_rope_padded_bf16")
+    return out
+
+
+def na3d_region(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel, region,
+                scale: float | None = None) -> torch.Tensor:
+    """Neighbourhood attention where only region = (h0, Hq, w0, Wq) of each [H, W] plane holds
+    queries; returns [B, D, Hq, Wq, heads, 64]."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _require_cuda_bf16(t, n)
+    B, D, H, W, nh, hd = q.shape
+    kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(x) for x in kernel)
+    h0, Hq, w0, Wq = (int(t) for t in region)
+    ldq, ldk, ldv = _token_major(q, "q"), _token_major(k, "k"), _token_major(v, "v")
+    out = torch.empty((B, D, Hq, Wq, nh, hd), dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().strata_na3d_fwd_region_bf16(
+            q.data_ptr(), ldq, k.data_ptr(), ldk, v.data_ptr(), ldv, out.data_ptr(), nh * hd,
+            B, D, H, W, nh, hd, kd, kh, kw, float(scale) if scale else 0.0, h0, Hq, w0, Wq,
+            _stream_ptr(q)), "strata_na3d_fwd_region_bf16")
+    return out
