@@ -222,6 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) {
         // Give loads already in flight time to land before the CTA retires.
+#pragma unroll 1
         for (int i = 0; i < 2000; ++i) __nanosleep(100);
       }
     }

@@ -9,9 +9,14 @@
 //                  neighbouring tiles of the same head, so their key halos meet in L2).
 //   key blocks     the union of a tile's windows is a box of ED x EH x EW keys
 //                  (E* = Q* + k* - 1) starting at the window start of the tile's first query.
-//                  It is streamed as blocks of one depth plane x 8 rows x EWP columns
-//                  (EWP = EW padded, NKEYS = 8*EWP <= 192); TMA zero-fills whatever lies
-//                  outside the tensor.
+//                  The box is cut into units of one depth plane x 4 rows x EWP columns
+//                  (EWP = EW padded) and streamed as blocks of TWO units (NKEYS = 8*EWP <= 192);
+//                  TMA zero-fills whatever lies outside the tensor. Which two units share a
+//                  block is a host-built table: each quarter of the tile (32 queries = one warp
+//                  per softmax group = one SM sub-partition) sees only part of the box, so units
+//                  are paired such that, wherever possible, every quarter finds exactly one
+//                  visible unit in every block - the exponential work is then spread evenly
+//                  over the sub-partitions instead of the busiest quarter setting the pace.
 //   warp 0         TMA producer: Q tile (double-buffered across items) and the K / V blocks into
 //                  a 2-3 stage ring (5-D tensor maps over [B, D, H, W, channels]; 128-byte
 //                  swizzle, a key's 64 channels are one 128-byte row). Runs ahead across items.
@@ -20,9 +25,11 @@
 //                  O_g += P_g V_g (M=128, N=64) for each key group g; O_g stays in TMEM for
 //                  the whole item.
 //   softmax warps  NG groups of 4 warps (NG = 4 for key blocks of up to 128 keys, else 2). A
-//                  query row is shared by one thread of each group; group g owns key rows
-//                  [g*8/NG, (g+1)*8/NG) of every block and keeps its own reference maximum and
-//                  running sum for them - no exchange between groups per block. Per block:
+//                  query row is shared by one thread of each group; with four groups, group g
+//                  owns row g of both units of every block (the producer stores the rows
+//                  group-major), with two groups, group g owns unit g. A group keeps its own
+//                  reference maximum and running sum - no exchange between groups per block.
+//                  Per block:
 //                  pass 1 reads the thread's S row segments from TMEM and takes the masked
 //                  maximum, pass 2 re-reads them, exponentiates, writes bf16 P into the
 //                  swizzled A-operand layout (double-buffered) and adds to the running sum.
@@ -52,6 +59,8 @@
 
 namespace strata {
 
+constexpr int NA_MAX_BLOCKS = 64;   // 16 planes x 8 chunks / 2
+
 struct Na3dParams {
   int B, D, H, W, heads;
   int kd, kh;            // kernel extents along depth and rows (columns: template KW)
@@ -62,6 +71,10 @@ struct Na3dParams {
   // whole [H, W] plane. Outputs are written compactly as [B, D, q_H, q_W, ldo].
   int q_h0, q_H, q_w0, q_W;
   int n_items;           // tiles_d*tiles_h*tiles_w*heads*B
+  int nblk;              // key blocks per item
+  // blk[i][s]: unit in slot s of block i: chunk (4 rows) in bits 0-3, plane in bits 4-7;
+  // bit 15: the slot only repeats another unit to keep the block full - ignore its keys.
+  unsigned short blk[NA_MAX_BLOCKS][2];
   __nv_bfloat16* out;    // [B, D, H, W, ldo] with head h at channel offset h*64
   long long ldo;
   float scale_log2e;
@@ -82,6 +95,7 @@ struct Na3dCfg {
   static constexpr int SCOLS = (NG == 4) ? 128 : 192;           // TMEM columns per S buffer
   static constexpr int O_COL = 2 * SCOLS;                       // O of group g at O_COL + 64 g
   static constexpr int KV_BYTES = NKEYS * 128;
+  static constexpr int ROW_BYTES = EWP * 128;                   // one key row in shared memory
   static constexpr int Q_BYTES = 128 * 128;
   static constexpr int KV_OFF = 2 * Q_BYTES;
   static constexpr int ML_BYTES = 2 * NG * 128 * 8;             // [2][NG][128] (max, sum)
@@ -263,10 +277,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int ED = p.QD + p.kd - 1;
-  const int EH = p.QH + p.kh - 1;
-  const int n_hb = (EH + 7) >> 3;
-  const int nblk = ED * n_hb;
+  const int nblk = p.nblk;
 
   if (threadIdx.x == 0) {
     for (uint32_t i = 0; i < 2; ++i) {
@@ -309,22 +320,38 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(q_empty(qb), ((n >> 1) & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(q_full(qb), Cfg::Q_BYTES);
         tma_load_5d(q_smem(qb), &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full(qb));
-        int ip = 0, hb = 0;
         for (int i = 0; i < nblk; ++i) {
           if (!mbar_wait(kv_empty(st), ph ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
           mbar_expect_tx(kv_full(st), 2 * Cfg::KV_BYTES);
-          tma_load_5d(k_smem(st), &tmK, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
-                      kv_full(st));
-          tma_load_5d(v_smem(st), &tmV, it.head * 64, it.bw0, it.bh0 + 8 * hb, it.bd0 + ip, it.b,
-                      kv_full(st));
-          if (++hb == n_hb) { hb = 0; ++ip; }
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t u = p.blk[i][s];
+            const int kh0 = it.bh0 + 4 * static_cast<int>(u & 15u);
+            const int kd0 = it.bd0 + static_cast<int>((u >> 4) & 15u);
+            if constexpr (NG == 4) {
+              // one load per key row; row r of slot s lands at position 2r + s (group-major)
+#pragma unroll
+              for (int r = 0; r < 4; ++r) {
+                const uint32_t off = (2 * r + s) * Cfg::ROW_BYTES;
+                tma_load_5d(k_smem(st) + off, &tmK, it.head * 64, it.bw0, kh0 + r, kd0, it.b,
+                            kv_full(st));
+                tma_load_5d(v_smem(st) + off, &tmV, it.head * 64, it.bw0, kh0 + r, kd0, it.b,
+                            kv_full(st));
+              }
+            } else {
+              const uint32_t off = s * 4 * Cfg::ROW_BYTES;
+              tma_load_5d(k_smem(st) + off, &tmK, it.head * 64, it.bw0, kh0, kd0, it.b, kv_full(st));
+              tma_load_5d(v_smem(st) + off, &tmV, it.head * 64, it.bw0, kh0, kd0, it.b, kv_full(st));
+            }
+          }
           if (++st == STAGES) { st = 0; ph ^= 1u; }
         }
       }
       if (!ok)
+#pragma unroll 1
         for (int i = 0; i < 2000; ++i) __nanosleep(100);
     }
   } else if (warp == 1) {
@@ -463,7 +490,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       set_nb(0.f);
       const uint64_t c2 = pack2(c, c);
 
-      int ip = 0, hb = 0;
       for (int i = 0; i < nblk; ++i, ++gb) {
         const uint32_t sb = gb & 1u;
         if (!mbar_wait(s_full(sb), (gb >> 1) & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
@@ -472,8 +498,24 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
         const uint32_t s_taddr = lane_taddr + (sb ? Cfg::SCOLS : 0) + grp * GKEYS;
-        const bool dvalid = static_cast<unsigned>(ip - wd) < static_cast<unsigned>(p.kd);
-        const uint32_t rowmask = dvalid ? ((hmask_all >> (8 * hb + RPG * grp)) & ROWBITS) : 0u;
+        // which of this thread's RPG key rows of the block lie inside its query's window
+        uint32_t rowmask;
+        {
+          auto plane_ok = [&](uint32_t u) {
+            return (u >> 15) == 0u &&
+                   static_cast<unsigned>(static_cast<int>((u >> 4) & 15u) - wd) <
+                       static_cast<unsigned>(p.kd);
+          };
+          if constexpr (NG == 4) {
+            const uint32_t u0 = p.blk[i][0], u1 = p.blk[i][1];
+            const uint32_t b0 = plane_ok(u0) ? (hmask_all >> (4u * (u0 & 15u) + grp)) & 1u : 0u;
+            const uint32_t b1 = plane_ok(u1) ? (hmask_all >> (4u * (u1 & 15u) + grp)) & 1u : 0u;
+            rowmask = b0 | (b1 << 1);
+          } else {
+            const uint32_t u = p.blk[i][grp];
+            rowmask = plane_ok(u) ? (hmask_all >> (4u * (u & 15u))) & ROWBITS : 0u;
+          }
+        }
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
 
         // The reference of a key group moves only when a block maximum exceeds it by more than
@@ -613,7 +655,6 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready(sb));
-        if (++hb == n_hb) { hb = 0; ++ip; }
       }
       if (!ok) break;
 
@@ -689,6 +730,77 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// Cuts the key box into (plane, 4-row chunk) units and pairs them into blocks. For every unit
+// the set of tile quarters (32 consecutive query rows: one warp per softmax group) that can
+// see it is worked out for an interior tile; units with disjoint sets are paired first, the
+// unit seen by most quarters choosing the partner that fills most of the remaining ones, so
+// that the per-block work of the busiest quarter is as small as the pairing allows. Windows
+// clamped at a border see fewer units than assumed here; that only affects the balance, the
+// kernel's masks are exact.
+inline int na_build_blocks(Na3dParams& p) {
+  const int ED = p.QD + p.kd - 1;
+  const int EH = p.QH + p.kh - 1;
+  const int NC = (EH + 3) / 4;
+  if (ED > 16 || NC > 8 || ED * NC > 2 * NA_MAX_BLOCKS) return -2;
+  const int n = ED * NC;
+  unsigned char seen[2 * NA_MAX_BLOCKS];
+  bool used[2 * NA_MAX_BLOCKS];
+  for (int pl = 0; pl < ED; ++pl)
+    for (int ch = 0; ch < NC; ++ch) {
+      unsigned m = 0;
+      for (int q = 0; q < 4; ++q)
+        for (int j = 4 * q; j < 4 * q + 4; ++j) {   // (zd, zh) pairs of the quarter
+          const int zh = j % p.QH, zd = j / p.QH;
+          const bool pd = pl >= zd && pl < zd + p.kd;
+          const bool ph = 4 * ch + 3 >= zh && 4 * ch < zh + p.kh;
+          if (pd && ph) m |= 1u << q;
+        }
+      seen[pl * NC + ch] = static_cast<unsigned char>(m);
+      used[pl * NC + ch] = false;
+    }
+  auto pop = [](unsigned m) { return __builtin_popcount(m); };
+  auto code = [&](int u) { return static_cast<unsigned short>((u % NC) | ((u / NC) << 4)); };
+  int nb = 0;
+  // pass 1: disjoint pairs, widest sets first
+  for (int want = 4; want >= 1; --want)
+    for (int u = 0; u < n; ++u) {
+      if (used[u] || pop(seen[u]) != want) continue;
+      int best = -1;
+      for (int v = 0; v < n; ++v)
+        if (!used[v] && v != u && (seen[u] & seen[v]) == 0 &&
+            (best < 0 || pop(seen[v]) > pop(seen[best])))
+          best = v;
+      if (best < 0) continue;
+      used[u] = used[best] = true;
+      p.blk[nb][0] = code(u);
+      p.blk[nb][1] = code(best);
+      ++nb;
+    }
+  // pass 2: whatever is left, in order
+  int pending = -1;
+  for (int u = 0; u < n; ++u) {
+    if (used[u]) continue;
+    if (pending < 0) { pending = u; continue; }
+    p.blk[nb][0] = code(pending);
+    p.blk[nb][1] = code(u);
+    ++nb;
+    pending = -1;
+  }
+  if (pending >= 0) {
+    p.blk[nb][0] = code(pending);
+    p.blk[nb][1] = static_cast<unsigned short>(code(pending) | 0x8000u);
+    ++nb;
+  }
+  p.nblk = nb;
+  return 0;
+}
+
+}  // namespace strata
+
+#include "na3d_narrow.cuh"
+
+namespace strata {
+
 // q/k/v: token-major bf16, element (b,d,h,w,head,c) at base + token*ld + head*64 + c where
 // token = ((b*D + d)*H + h)*W + w. out likewise with ldo.
 template <int KW>
@@ -709,16 +821,32 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
   };
   CUtensorMap tmQ, tmK, tmV;
   if (make(&tmQ, q, ldq, NA_QW, p.QH, p.QD) != 0) return -20;
-  if (make(&tmK, k, ldk, Cfg::EWP, 8, 1) != 0) return -20;
-  if (make(&tmV, v, ldv, Cfg::EWP, 8, 1) != 0) return -20;
-  auto kern = na3d_fwd_kernel<KW>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::TOTAL);
-  if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
-  const int grid = p.n_items < sm_count ? p.n_items : sm_count;
-  kern<<<grid, Cfg::THREADS, Cfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
-  e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+  if constexpr (NA_QW + KW - 1 <= 16) {
+    // narrow key rows: the two-CTAs-per-SM kernel
+    using NCfg = Na3dNarrowCfg<KW>;
+    if (make(&tmK, k, ldk, NCfg::EWP, 4, 1) != 0) return -20;
+    if (make(&tmV, v, ldv, NCfg::EWP, 4, 1) != 0) return -20;
+    auto kern = na3d_fwd_narrow_kernel<KW>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         NCfg::TOTAL);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    const int grid = p.n_items < 2 * sm_count ? p.n_items : 2 * sm_count;
+    kern<<<grid, NCfg::THREADS, NCfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+  } else {
+    constexpr uint32_t KV_BOX_ROWS = Cfg::NG == 4 ? 1 : 4;
+    if (make(&tmK, k, ldk, Cfg::EWP, KV_BOX_ROWS, 1) != 0) return -20;
+    if (make(&tmV, v, ldv, Cfg::EWP, KV_BOX_ROWS, 1) != 0) return -20;
+    auto kern = na3d_fwd_kernel<KW>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::TOTAL);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    const int grid = p.n_items < sm_count ? p.n_items : sm_count;
+    kern<<<grid, Cfg::THREADS, Cfg::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+  }
 }
 
 inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* k, long long ldk,
@@ -746,6 +874,7 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   const long long items = static_cast<long long>(p.tiles_d) * p.tiles_h * p.tiles_w * heads * B;
   if (items > 0x7fffffffLL) return -2;
   p.n_items = static_cast<int>(items);
+  if (na_build_blocks(p) != 0) return -2;
   p.out = out;
   p.ldo = ldo;
   p.scale_log2e = scale * 1.4426950408889634f;
