@@ -115,6 +115,10 @@ NA_CASES = [
     (1, 6, 24, 24, 2, (5, 13, 13)), (1, 1, 32, 32, 2, (1, 9, 9)), (1, 3, 16, 16, 1, (3, 15, 15)),
     (1, 8, 9, 9, 1, (3, 9, 9)),       # window == whole axis: every query sees every key
     (1, 7, 12, 30, 1, (5, 11, 5)), (1, 5, 8, 8, 1, (5, 1, 1)),
+    # wide kernels run with narrower query tiles (4 or 2 columns); shallow tensors leave part of
+    # the 128-row tile without queries
+    (1, 1, 20, 24, 1, (1, 13, 13)), (1, 2, 17, 19, 2, (1, 15, 15)), (1, 9, 16, 18, 1, (5, 15, 15)),
+    (1, 3, 33, 16, 1, (3, 5, 11)),
 ]
 
 
