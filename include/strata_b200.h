@@ -174,12 +174,15 @@ int strata_qkv_rope_padded_bf16(const void* x, int64_t ldx, const void* w, int64
 
 /* strata_na3d_fwd_bf16 restricted to a query region: only tokens with h in [q_h0, q_h0+q_H) and
  * w in [q_w0, q_w0+q_W) are queries (the interior of a halo-padded tile); keys come from the
- * whole [H, W] plane, windows clamp at the plane's (padded) borders, and out is written
- * compactly as [B, D, q_H, q_W, ldo]. */
+ * whole [H, W] plane, windows clamp at the plane's (padded) borders. out is the plane
+ * [B, D, o_H, o_W, ldo] in which query (h, w) lands at (h - o_h0, w - o_w0); the output window
+ * must contain the query region. o_H < 0 or o_W < 0: the query region itself, stored compactly.
+ * A larger window lets several calls (an inner region, then border strips) fill one tensor. */
 int strata_na3d_fwd_region_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
                                 const void* v, int64_t ldv, void* out, int64_t ldo, int B, int D,
                                 int H, int W, int heads, int head_dim, int kd, int kh, int kw,
-                                float scale, int q_h0, int q_H, int q_w0, int q_W, void* stream);
+                                float scale, int q_h0, int q_H, int q_w0, int q_W, int o_h0,
+                                int o_H, int o_w0, int o_W, void* stream);
 
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and

@@ -185,7 +185,7 @@ int strata_qkv_rope_padded_bf16(const void* x, int64_t ldx, const void* w, int64
 static int na3d_impl(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                      int64_t ldv, void* out, int64_t ldo, int B, int D, int H, int W, int heads,
                      int head_dim, int kd, int kh, int kw, float scale, int q_h0, int q_H, int q_w0,
-                     int q_W, void* stream) {
+                     int q_W, int o_h0, int o_H, int o_w0, int o_W, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (!q || !k || !v || !out || B < 0 || D <= 0 || H <= 0 || W <= 0 || heads <= 0)
@@ -202,7 +202,7 @@ static int na3d_impl(const void* q, int64_t ldq, const void* k, int64_t ldk, con
                       static_cast<const __nv_bfloat16*>(k), ldk,
                       static_cast<const __nv_bfloat16*>(v), ldv, static_cast<__nv_bfloat16*>(out),
                       ldo, B, D, H, W, heads, kd, kh, kw, sc, sms, as_stream(stream), q_h0, q_H,
-                      q_w0, q_W);
+                      q_w0, q_W, o_h0, o_H, o_w0, o_W);
   if (r == -1) return STRATA_ERR_ARG;
   if (r == -2) return STRATA_ERR_UNSUPPORTED;
   return r;
@@ -213,16 +213,17 @@ int strata_na3d_fwd_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
                          int heads, int head_dim, int kd, int kh, int kw, float scale,
                          void* stream) {
   return na3d_impl(q, ldq, k, ldk, v, ldv, out, ldo, B, D, H, W, heads, head_dim, kd, kh, kw,
-                   scale, 0, -1, 0, -1, stream);
+                   scale, 0, -1, 0, -1, 0, -1, 0, -1, stream);
 }
 
 int strata_na3d_fwd_region_bf16(const void* q, int64_t ldq, const void* k, int64_t ldk,
                                 const void* v, int64_t ldv, void* out, int64_t ldo, int B, int D,
                                 int H, int W, int heads, int head_dim, int kd, int kh, int kw,
-                                float scale, int q_h0, int q_H, int q_w0, int q_W, void* stream) {
+                                float scale, int q_h0, int q_H, int q_w0, int q_W, int o_h0,
+                                int o_H, int o_w0, int o_W, void* stream) {
   if (q_h0 < 0 || q_w0 < 0 || q_H < 1 || q_W < 1) return STRATA_ERR_ARG;
   return na3d_impl(q, ldq, k, ldk, v, ldv, out, ldo, B, D, H, W, heads, head_dim, kd, kh, kw,
-                   scale, q_h0, q_H, q_w0, q_W, stream);
+                   scale, q_h0, q_H, q_w0, q_W, o_h0, o_H, o_w0, o_W, stream);
 }
 
 int64_t strata_block_workspace_bytes(int64_t M, int C, int hidden) {

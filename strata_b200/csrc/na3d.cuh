@@ -71,8 +71,11 @@ struct Na3dParams {
   int tiles_d, tiles_h, tiles_w;
   // Query region: only tokens with h in [q_h0, q_h0+q_H), w in [q_w0, q_w0+q_W) are queries
   // (the interior of a halo-padded tile; the whole plane by default). Keys come from the
-  // whole [H, W] plane. Outputs are written compactly as [B, D, q_H, q_W, ldo].
+  // whole [H, W] plane. Output plane: [B, D, o_H, o_W, ldo], query (h, w) lands at
+  // (h - o_h0, w - o_w0) - by default the query region itself, stored compactly; a larger
+  // output window lets several launches (an inner region, border strips) fill one tensor.
   int q_h0, q_H, q_w0, q_W;
+  int o_h0, o_H, o_w0, o_W;
   int n_items;           // tiles_d*tiles_h*tiles_w*heads*B
   int nblk;              // key blocks per item
   // blk[i][s]: unit in slot s of block i: chunk (4 rows) in bits 0-3, plane in bits 4-7;
@@ -526,8 +529,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       tc_fence_after();
       {
         const float inv = 1.0f / l_run;
-        const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.q_H +
-                               (it.h0 + zh - p.q_h0)) * p.q_W + (it.w0 + zw - p.q_w0);
+        const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.o_H +
+                               (it.h0 + zh - p.o_h0)) * p.o_W + (it.w0 + zw - p.o_w0);
         __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -662,7 +665,7 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
                        const __nv_bfloat16* v, long long ldv, __nv_bfloat16* out, long long ldo,
                        int B, int D, int H, int W, int heads, int kd, int kh, int kw, float scale,
                        int sm_count, cudaStream_t stream, int q_h0 = 0, int q_H = -1, int q_w0 = 0,
-                       int q_W = -1) {
+                       int q_W = -1, int o_h0 = 0, int o_H = -1, int o_w0 = 0, int o_W = -1) {
   if (kd > D || kh > H || kw > W || kd < 1 || kh < 1 || kw < 1) return -1;
   if (kh > 15 || kd > 15 || kw > 15 || !(kw & 1)) return -2;
   Na3dParams p{};
@@ -686,6 +689,13 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   if (p.q_h0 < 0 || p.q_w0 < 0 || p.q_H < 1 || p.q_W < 1 || p.q_h0 + p.q_H > H ||
       p.q_w0 + p.q_W > W)
     return -1;
+  if (o_H < 0 || o_W < 0) {
+    p.o_h0 = p.q_h0; p.o_H = p.q_H; p.o_w0 = p.q_w0; p.o_W = p.q_W;
+  } else {
+    p.o_h0 = o_h0; p.o_H = o_H; p.o_w0 = o_w0; p.o_W = o_W;
+    if (o_h0 > p.q_h0 || o_w0 > p.q_w0 || o_h0 + o_H < p.q_h0 + p.q_H || o_w0 + o_W < p.q_w0 + p.q_W)
+      return -1;   // the output window must contain the query region
+  }
   p.tiles_d = (D + p.QD - 1) / p.QD;
   p.tiles_h = (p.q_H + p.QH - 1) / p.QH;
   p.tiles_w = (p.q_W + p.QW - 1) / p.QW;

@@ -12,6 +12,12 @@ neighbouring tiles, whose keys and values arrive through peer memory each block:
     attention of the interior queries over the padded K/V planes
     projection, residual, LN, MLP               interior tokens, compact
 
+With overlap=True the exchange runs on a side stream while the main stream already computes the
+attention of the queries whose windows stay inside the tile (they need no halo); the border
+strips follow once the halo has arrived. Everything that is token-wise (LN, the GEMMs) runs in
+chunks of tiles, so that only x, y, the attention output and the padded qkv buffer are ever held
+for all tiles at once.
+
 Stereographic RoPE coordinates are relative to each tile's centre, so a key rotated in its
 owner's frame is wrong for the receiver; the owner stores K in its own frame (it needs that
 for its own queries) and the receiver applies the rotation by the angle difference, a table
@@ -54,7 +60,7 @@ class TiledBlockRunner:
     def __init__(self, topology: TileTopology, *, depth: int, dim: int, num_heads: int, kernel,
                  lat_deg: np.ndarray, lon_deg: np.ndarray, rope_base: float = 100.0,
                  rope_length_scale: float | None = None, device=None, group=None,
-                 timeout_ms: int = 2000):
+                 timeout_ms: int = 2000, overlap: bool = False, chunk_tiles: int | None = None):
         """lat_deg / lon_deg: [total_tiles, T, T] cell centres of ALL tiles in global tile order."""
         T, h = topology.tile_size, topology.halo_width
         kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(v) for v in kernel)
@@ -104,19 +110,27 @@ class TiledBlockRunner:
             return rope.pack_rope_tables(torch.cos(ang).float(), torch.sin(ang).float()
                                          ).reshape(tpr, P * P, hd // 2, 2).to(dev)
         self.dcs_a, self.dcs_b = delta(a), delta(b)
-        # peer-visible padded qkv: [flags | slot 0 | slot 1]
+        # peer-visible padded qkv: [flags | slot 0 | slot 1]. Two alternating slots keep a rank
+        # that is already one block ahead from overwriting what a slower peer still reads; a
+        # single GPU is ordered by its stream and needs one.
         self._slot_bytes = tpr * depth * P * P * 3 * dim * 2
+        self._n_slots = 2 if topology.world_size > 1 else 1
         self._epoch = 0
+        total = self.FLAG_BYTES + self._n_slots * self._slot_bytes
         if topology.world_size > 1:
-            self._shared = PeerSharedBuffer(self.FLAG_BYTES + 2 * self._slot_bytes, group=group)
+            self._shared = PeerSharedBuffer(total, group=group)
             self._local = self._shared.local
         else:
             self._shared = None
-            self._local = torch.zeros(self.FLAG_BYTES + 2 * self._slot_bytes, dtype=torch.uint8,
-                                      device=dev)
+            self._local = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.overlap = bool(overlap)
+        self._side = torch.cuda.Stream(device=dev) if self.overlap else None
+        if chunk_tiles is None:   # hidden activations of a chunk stay below ~4 GB
+            chunk_tiles = max(1, int(4e9 // (depth * T * T * 4 * dim * 2)))
+        self.chunk_tiles = min(int(chunk_tiles), tpr)
 
     def _slot(self, parity: int):
-        off = self.FLAG_BYTES + parity * self._slot_bytes
+        off = self.FLAG_BYTES + (parity % self._n_slots) * self._slot_bytes
         topo = self.topology
         P = topo.padded_tile_size
         rows = topo.tiles_per_rank * self.depth * P * P
@@ -127,15 +141,14 @@ class TiledBlockRunner:
             ptrs = (ctypes.c_void_p * 1)(view.data_ptr())
         return view, ptrs
 
-    def attention(self, xn: torch.Tensor, w_qkv, b_qkv, qk_norm: bool = False) -> torch.Tensor:
-        """LN'ed interior tokens [tiles_per_rank*D*T*T, C] -> attention output, same shape."""
+    def _chunks(self):
+        tpr = self.topology.tiles_per_rank
+        return [(t0, min(t0 + self.chunk_tiles, tpr)) for t0 in range(0, tpr, self.chunk_tiles)]
+
+    def _exchange(self, qkv, ptrs):
+        """Flag barrier (every rank's interiors are published) + K/V halo gather, on the
+        current stream."""
         topo, D, C = self.topology, self.depth, self.dim
-        T, h, P = topo.tile_size, topo.halo_width, topo.padded_tile_size
-        tpr = topo.tiles_per_rank
-        self._epoch += 1
-        qkv, ptrs = self._slot(self._epoch & 1)
-        ops.qkv_rope_padded(xn, w_qkv, b_qkv, C // self.heads, self.rope_cs, D * T * T, T * T, qkv,
-                            tile=T, halo=h, depth=D, qk_norm=qk_norm)
         lib = _lib.load()
         stream = torch.cuda.current_stream().cuda_stream
         if topo.world_size > 1:
@@ -144,24 +157,65 @@ class TiledBlockRunner:
                        "strata_halo_barrier")
         _lib.check(lib.strata_halo_gather_kv_bf16(
             qkv.data_ptr(), ptrs, topo.world_size, self.src_a.data_ptr(), self.src_b.data_ptr(),
-            self.dcs_a.data_ptr(), self.dcs_b.data_ptr(), tpr, D, T, h, C, C // self.heads, 3 * C,
-            stream), "strata_halo_gather_kv_bf16")
+            self.dcs_a.data_ptr(), self.dcs_b.data_ptr(), topo.tiles_per_rank, D, topo.tile_size,
+            topo.halo_width, C, C // self.heads, 3 * C, stream), "strata_halo_gather_kv_bf16")
+
+    def attention(self, xn, w_qkv, b_qkv, qk_norm: bool = False) -> torch.Tensor:
+        """LN'ed interior tokens [tiles_per_rank*D*T*T, C] (a tensor, or a callable
+        chunk(t0, t1) -> rows of tiles [t0, t1)) -> attention output, same shape."""
+        topo, D, C = self.topology, self.depth, self.dim
+        T, h, P = topo.tile_size, topo.halo_width, topo.padded_tile_size
+        tpr = topo.tiles_per_rank
+        self._epoch += 1
+        qkv, ptrs = self._slot(self._epoch)
+        rows_t, prow_t = D * T * T, D * P * P
+        for t0, t1 in self._chunks():
+            xc = xn(t0, t1) if callable(xn) else xn[t0 * rows_t:t1 * rows_t]
+            ops.qkv_rope_padded(xc, w_qkv, b_qkv, C // self.heads, self.rope_cs[t0:t1], rows_t, T * T,
+                                qkv[t0 * prow_t:t1 * prow_t], tile=T, halo=h, depth=D,
+                                qk_norm=qk_norm)
         q6 = qkv.view(tpr, D, P, P, 3, self.heads, C // self.heads)
-        o = ops.na3d_region(q6[..., 0, :, :], q6[..., 1, :, :], q6[..., 2, :, :], self.kernel,
-                            (h, T, h, T))
+        q, k, v = q6[..., 0, :, :], q6[..., 1, :, :], q6[..., 2, :, :]
+        r = max(self.kernel[1], self.kernel[2]) // 2
+        if not self.overlap or T - 2 * r < 8:
+            self._exchange(qkv, ptrs)
+            o = ops.na3d_region(q, k, v, self.kernel, (h, T, h, T))
+            return o.view(tpr * D * T * T, C)
+        # halo exchange on the side stream, inner queries (windows inside the tile) meanwhile
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(ready)
+            self._exchange(qkv, ptrs)
+            arrived = torch.cuda.Event()
+            arrived.record(self._side)
+        o = torch.empty((tpr, D, T, T, self.heads, C // self.heads), dtype=torch.bfloat16,
+                        device=qkv.device)
+        win = (h, T, h, T)
+        ops.na3d_region(q, k, v, self.kernel, (h + r, T - 2 * r, h + r, T - 2 * r), out=o, out_window=win)
+        main.wait_event(arrived)
+        for reg in ((h, r, h, T), (h + T - r, r, h, T),
+                    (h + r, T - 2 * r, h, r), (h + r, T - 2 * r, h + T - r, r)):
+            ops.na3d_region(q, k, v, self.kernel, reg, out=o, out_window=win)
         return o.view(tpr * D * T * T, C)
 
     def block_forward(self, x: torch.Tensor, weights: dict, qk_norm: bool = False) -> torch.Tensor:
         """x: [tiles_per_rank, D*T*T, C] bf16 interior tokens; weights as ops.block_forward."""
         tpr, tokens, C = x.shape
         x2 = x.reshape(tpr * tokens, C)
-        xn = ops.layernorm(x2)
-        attn = self.attention(xn, weights["w_qkv"], weights.get("b_qkv"), qk_norm)
-        if weights.get("w_gate") is not None:
-            attn = ops.linear(xn, weights["w_gate"], weights.get("b_gate"), ops.EPI_GATE, attn)
-        x1 = ops.linear(attn, weights["w_proj"], weights.get("b_proj"), ops.EPI_RESIDUAL, x2)
-        hmid = ops.linear(ops.layernorm(x1), weights["w_fc1"], weights.get("b_fc1"), ops.EPI_GELU)
-        y = ops.linear(hmid, weights["w_fc2"], weights.get("b_fc2"), ops.EPI_RESIDUAL, x1)
+        attn = self.attention(lambda t0, t1: ops.layernorm(x2[t0 * tokens:t1 * tokens]),
+                              weights["w_qkv"], weights.get("b_qkv"), qk_norm)
+        y = torch.empty_like(x2)
+        for t0, t1 in self._chunks():
+            sl = slice(t0 * tokens, t1 * tokens)
+            xc, ac = x2[sl], attn[sl]
+            if weights.get("w_gate") is not None:
+                ac = ops.linear(ops.layernorm(xc), weights["w_gate"], weights.get("b_gate"),
+                                ops.EPI_GATE, ac)
+            x1 = ops.linear(ac, weights["w_proj"], weights.get("b_proj"), ops.EPI_RESIDUAL, xc)
+            hmid = ops.linear(ops.layernorm(x1), weights["w_fc1"], weights.get("b_fc1"), ops.EPI_GELU)
+            ops.linear(hmid, weights["w_fc2"], weights.get("b_fc2"), ops.EPI_RESIDUAL, x1, out=y[sl])
         return y.view(tpr, tokens, C)
 
     def check_status(self) -> None:

@@ -263,19 +263,29 @@ def qkv_rope_padded(x: torch.Tensor, weight: torch.Tensor, bias, head_dim: int,
 
 
 def na3d_region(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel, region,
-                scale: float | None = None) -> torch.Tensor:
+                scale: float | None = None, out: torch.Tensor | None = None,
+                out_window=None) -> torch.Tensor:
     """Neighbourhood attention where only region = (h0, Hq, w0, Wq) of each [H, W] plane holds
-    queries; returns [B, D, Hq, Wq, heads, 64]."""
+    queries; returns [B, D, Hq, Wq, heads, 64]. With `out` [B, D, Ho, Wo, heads, 64] and
+    out_window = (oh0, Ho, ow0, Wo) the queries land at (h - oh0, w - ow0) of that tensor, so
+    several calls can fill one output."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _require_cuda_bf16(t, n)
     B, D, H, W, nh, hd = q.shape
     kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(x) for x in kernel)
     h0, Hq, w0, Wq = (int(t) for t in region)
     ldq, ldk, ldv = _token_major(q, "q"), _token_major(k, "k"), _token_major(v, "v")
-    out = torch.empty((B, D, Hq, Wq, nh, hd), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((B, D, Hq, Wq, nh, hd), dtype=torch.bfloat16, device=q.device)
+        oh0, Ho, ow0, Wo = 0, -1, 0, -1
+    else:
+        _require_cuda_bf16(out, "out")
+        oh0, Ho, ow0, Wo = (int(t) for t in out_window)
+        if tuple(out.shape) != (B, D, Ho, Wo, nh, hd) or not out.is_contiguous():
+            raise ValueError("out must be a contiguous [B, D, Ho, Wo, heads, 64] tensor")
     with torch.cuda.device(q.device):
         _lib.check(_lib.load().strata_na3d_fwd_region_bf16(
             q.data_ptr(), ldq, k.data_ptr(), ldk, v.data_ptr(), ldv, out.data_ptr(), nh * hd,
             B, D, H, W, nh, hd, kd, kh, kw, float(scale) if scale else 0.0, h0, Hq, w0, Wq,
-            _stream_ptr(q)), "strata_na3d_fwd_region_bf16")
+            oh0, Ho, ow0, Wo, _stream_ptr(q)), "strata_na3d_fwd_region_bf16")
     return out

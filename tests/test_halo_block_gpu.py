@@ -41,9 +41,21 @@ def test_padded_qkv_store_and_region_attention_match_plain_path():
     reg = ops.na3d_region(q, k, v, (3, 5, 5), (h, T, h, T))
     # (query tiles start at the region's origin, so keys are summed in a different order)
     assert rel_max_err(reg, full[:, :, h:h + T, h:h + T].float()) < 1e-2
+    # an inner region and four border strips written into one output window give the same
+    # tensor (different query tiling, hence only a tolerance)
+    r = 2
+    o = torch.full((1, 3, T, T, heads, 64), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for region in ((h + r, T - 2 * r, h + r, T - 2 * r), (h, r, h, T), (h + T - r, r, h, T),
+                   (h + r, T - 2 * r, h, r), (h + r, T - 2 * r, h + T - r, r)):
+        ops.na3d_region(q, k, v, (3, 5, 5), region, out=o, out_window=(h, T, h, T))
+    assert not torch.isnan(o).any()
+    assert rel_max_err(o, reg.float()) < 1e-2
+    with pytest.raises(ValueError):   # output window must contain the query region
+        ops.na3d_region(q, k, v, (3, 5, 5), (h, T, h, T), out=o[:, :, :T - 1].contiguous(),
+                        out_window=(h, T - 1, h, T))
 
 
-def _setup(halo, kernel, gated=False, seed=12):
+def _setup(halo, kernel, gated=False, seed=12, **runner_kw):
     from strata_b200.halo_block import TiledBlockRunner
     from strata_b200.topology import TileTopology
     face, tile, D, C, heads = 64, 32, 2, 64, 1
@@ -56,7 +68,7 @@ def _setup(halo, kernel, gated=False, seed=12):
     # between neighbouring tokens are O(0.1 - 1) rad, as on the production grid
     scale = np.radians(90.0 / face)
     run = TiledBlockRunner(topo, depth=D, dim=C, num_heads=heads, kernel=kernel, lat_deg=lat,
-                           lon_deg=lon, rope_length_scale=scale)
+                           lon_deg=lon, rope_length_scale=scale, **runner_kw)
     okw = dict(face=face, tile=tile, halo=halo, depth=D, num_heads=heads, kernel=kernel,
                lat_deg=lat, lon_deg=lon, length_scale=scale)
     return run, topo, p, x, okw
@@ -96,9 +108,14 @@ def _own_frame_coords(okw):
     return (px / okw["length_scale"]).flatten(1), (py / okw["length_scale"]).flatten(1)
 
 
-@pytest.mark.parametrize("gated,qk_norm,kernel,halo", [(False, False, (1, 5, 5), 2), (True, True, (2, 7, 7), 4)])
-def test_tiled_block_matches_oracle(gated, qk_norm, kernel, halo):
-    run, topo, p, x, okw = _setup(halo, kernel, gated=gated)
+@pytest.mark.parametrize("gated,qk_norm,kernel,halo,runner_kw", [
+    (False, False, (1, 5, 5), 2, {}), (True, True, (2, 7, 7), 4, {}),
+    # exchange on a side stream while the inner queries are computed; token-wise stages in chunks
+    (True, False, (2, 7, 7), 4, {"overlap": True, "chunk_tiles": 5}),
+    (False, True, (1, 5, 5), 3, {"overlap": True}),
+])
+def test_tiled_block_matches_oracle(gated, qk_norm, kernel, halo, runner_kw):
+    run, topo, p, x, okw = _setup(halo, kernel, gated=gated, **runner_kw)
     y = run.block_forward(x.cuda(), device_block_weights(p, "cuda"), qk_norm=qk_norm)
     run.check_status()
     ref = bo.tiled_block_forward(x.float(), p, qk_norm=qk_norm, gated=gated, **okw)
@@ -107,13 +124,14 @@ def test_tiled_block_matches_oracle(gated, qk_norm, kernel, halo):
 
 @pytest.mark.skipif(not (torch.cuda.is_available() and torch.cuda.device_count() >= 2),
                     reason="needs 2 GPUs on one node")
-def test_two_rank_tiled_block_stack():
+@pytest.mark.parametrize("overlap", ["0", "1"])
+def test_two_rank_tiled_block_stack(overlap):
     import os, subprocess, sys
     from pathlib import Path
     worker = Path(__file__).resolve().parent / "halo_block_worker.py"
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                         "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                         "29533", str(worker)], capture_output=True, text=True, timeout=600,
-                       env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+                       env={**os.environ, "NCCL_NVLS_ENABLE": "0", "HALO_OVERLAP": overlap})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "HALO BLOCK WORKER OK" in r.stdout
