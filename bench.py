@@ -267,8 +267,18 @@ def run_gpu_arm(args):
     except Exception as exc:  # reported, never fatal for the headline line
         sphere = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
+    # secondary metric: stack of blocks over the sphere's tiles with a K/V halo exchange in
+    # EVERY block (tiles sharded over ranks)
+    torch.cuda.empty_cache()
+    try:
+        tiled = tiled_blocks_bench(torch, dist, world, rank, dev, timed)
+    except Exception as exc:
+        tiled = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    torch.cuda.empty_cache()
+
     # per-kernel breakdown (same sequence as strata_block_forward_bf16, one event pair each)
     breakdown = kernel_breakdown(torch, ops, x, weights, cs, (D, H, W), heads, kernel, hidden)
+    sweep = na3d_sweep(torch, ops) if world == 1 else None
 
     if rank == 0:
         tf_peak, hbm_peak, peak_kind = measured_peaks()
@@ -296,7 +306,7 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world},
-            "sphere_step": sphere,
+            "sphere_step": sphere, "tiled_blocks": tiled, "na3d_sweep": sweep,
             "gpu_launches": 7 * args.steps, "device_status": status, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -345,6 +355,110 @@ def sphere_step_bench(torch, dist, world, rank, dev, timed, steps=3):
     del stepper, net
     torch.cuda.empty_cache()
     return out
+
+
+TILED = dict(faces=6, face_tokens=256, tile_tokens=128, halo_tokens=8, depth=16, dim=768, heads=12,
+             kernel=[5, 13, 13], blocks=12, mlp_ratio=4)
+
+
+def tiled_blocks_bench(torch, dist, world, rank, dev, timed, steps=2):
+    """Strong-scaling companion metric: 12 blocks over 24 tiles of 16x128x128 tokens (dim 768,
+    12 heads, kernel (5,13,13)) with an 8-token K/V halo exchanged through peer memory in every
+    block. Timed once with the exchange in line and once overlapped with the inner-region
+    attention; `ms_per_step` is the faster of the two."""
+    import numpy as np
+    from strata_b200.halo_block import TiledBlockRunner
+    from strata_b200.rollout import equiangular_cubed_sphere_latlon
+    from strata_b200.topology import TileTopology
+    c = TILED
+    face, T, C = c["face_tokens"], c["tile_tokens"], c["dim"]
+    topo = TileTopology(world, rank, face, T, c["halo_tokens"])
+    lat, lon = equiangular_cubed_sphere_latlon(face)
+    full = TileTopology(1, 0, face, T, 0)
+    cut = lambda g: np.stack([g[f, i * T:(i + 1) * T, j * T:(j + 1) * T] for f, i, j in full.global_tiles])
+    lat, lon = cut(lat), cut(lon)
+    gen = torch.Generator().manual_seed(4321)
+    hidden = C * c["mlp_ratio"]
+
+    def tn(*shape):
+        w = torch.empty(*shape)
+        torch.nn.init.trunc_normal_(w, std=0.02, a=-0.04, b=0.04, generator=gen)
+        return w.to(dev, torch.bfloat16)
+    blocks = []
+    for _ in range(c["blocks"]):
+        w = {"w_qkv": tn(3 * C, C), "w_proj": tn(C, C), "w_fc1": tn(hidden, C), "w_fc2": tn(C, hidden)}
+        for k, n in (("b_qkv", 3 * C), ("b_proj", C), ("b_fc1", hidden), ("b_fc2", C)):
+            w[k] = torch.zeros(n, device=dev, dtype=torch.float32)
+        blocks.append(w)
+    tokens = c["depth"] * T * T
+    g = torch.Generator(device=dev).manual_seed(200 + rank)
+    x = torch.randn(topo.tiles_per_rank, tokens, C, device=dev, generator=g).bfloat16()
+    out = {}
+    for mode in ("inline", "overlap"):
+        run = TiledBlockRunner(topo, depth=c["depth"], dim=C, num_heads=c["heads"],
+                               kernel=tuple(c["kernel"]), lat_deg=lat, lon_deg=lon,
+                               rope_length_scale=float(np.radians(90.0 / face)), device=dev,
+                               overlap=(mode == "overlap"))
+
+        def step():
+            y = x
+            for w in blocks:
+                y = run.block_forward(y, w)
+            return y
+        step()
+        out[mode + "_ms"] = timed(step, steps) / steps
+        run.check_status()
+        if mode == "inline":   # the exchange alone (barrier + K/V gather of one block)
+            qkv, ptrs = run._slot(run._epoch)
+
+            def exchange():
+                run._epoch += 1
+                run._exchange(qkv, ptrs)
+            exchange()
+            out["exchange_ms_per_block"] = timed(exchange, 5) / 5
+            P = topo.padded_tile_size
+            halo_cells = topo.tiles_per_rank * c["depth"] * (P * P - T * T)
+            out["exchange_bytes_per_block"] = halo_cells * 2 * C * 2 * 2   # K,V read + written
+        run.close()
+        del run
+        torch.cuda.empty_cache()
+    ms = min(out["inline_ms"], out["overlap_ms"])
+    total_tokens = topo.total_tiles * tokens
+    out.update(ms_per_step=ms, tokens_per_s=total_tokens / (ms * 1e-3), scaling="strong", config=c,
+               tiles_per_rank=topo.tiles_per_rank,
+               tflops=flops_per_token(C, tuple(c["kernel"])) * total_tokens * c["blocks"] / (ms * 1e-3) / 1e12)
+    return out
+
+
+NA_SWEEP = dict(B=8, D=32, H=96, W=96, heads=16, head_dim=64, kernels=[[3, 7, 7], [3, 13, 13], [5, 15, 15]])
+
+
+def na3d_sweep(torch, ops, iters=3):
+    """Standalone neighbourhood attention on Q/K/V [8, 32, 96, 96, 16, 64] for three kernels:
+    milliseconds per launch and algorithmic TFLOP/s (4 * window * head_dim per query and head)."""
+    c = NA_SWEEP
+    shape = (c["B"], c["D"], c["H"], c["W"], c["heads"], c["head_dim"])
+    try:
+        q, k, v = (torch.randn(shape, device="cuda").bfloat16() for _ in range(3))
+        o = torch.empty_like(q)
+        res = []
+        for kern in c["kernels"]:
+            for _ in range(2):
+                ops.na3d(q, k, v, tuple(kern), out=o)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                ops.na3d(q, k, v, tuple(kern), out=o)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            flop = 4.0 * kern[0] * kern[1] * kern[2] * c["head_dim"] * q.numel() / c["head_dim"]
+            res.append({"kernel": kern, "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12})
+        del q, k, v, o
+        torch.cuda.empty_cache()
+        return {"shape": list(shape), "results": res}
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
 
 def kernel_breakdown(torch, ops, x, weights, cs, grid, heads, kernel, hidden, iters=5,

@@ -370,10 +370,11 @@ int strata_halo_gather_kv_bf16(void* qkv, const void* const* h_peer_qkv, int wor
   const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
   if (cells * world > 0x7fffffffLL) return STRATA_ERR_ARG;
   if (static_cast<long long>(tiles_per_rank) * D > 65535) return STRATA_ERR_UNSUPPORTED;
-  const long long work = static_cast<long long>(P) * P * (2 * C / 8);
+  const long long work = (static_cast<long long>(P) * P - static_cast<long long>(T) * T) * (2 * C / 8);
   long long bx = (work + 255) / 256;
   const long long cap = static_cast<long long>(sms) * 8;
   if (bx > cap) bx = cap;
+  if (bx < 1) return STRATA_OK;   // no halo
   dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(tiles_per_rank * D));
   halo_gather_kv_kernel<<<grid, 256, 0, as_stream(stream)>>>(
       static_cast<__nv_bfloat16*>(qkv), pp, src_a, src_b, static_cast<const uint32_t*>(dcs_a),

@@ -110,7 +110,7 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
 // frame; it is turned into the receiver's frame on the way by the per-cell delta rotation
 // dcs[tile, cell, pair] = (cos, sin)(theta_receiver - theta_sender) (IEEE half pairs), V is
 // copied. Corner-diagonal cells average their two (individually rotated) sources.
-// grid: x over (padded cell, 16-byte vector of the 2C k|v channels), y over (tile, depth).
+// grid: x over (halo cell, 16-byte vector of the 2C k|v channels), y over (tile, depth).
 __global__ void __launch_bounds__(256)
 halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
                       const int* __restrict__ src_a, const int* __restrict__ src_b,
@@ -123,13 +123,28 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
   const int half = head_dim >> 1;
   const int tile = blockIdx.y / D;
   const int d = blockIdx.y - tile * D;
-  const long long total = static_cast<long long>(PP) * vpc;
+  // only the halo cells are visited: first the two full-width strips above and below the
+  // interior (2*halo rows of P cells), then the 2*halo side columns of the T interior rows
+  const int n_strip = 2 * halo * P;
+  const int n_halo = n_strip + 2 * halo * T;
+  const long long total = static_cast<long long>(n_halo) * vpc;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int pc = static_cast<int>(idx / vpc);
-    const int v = static_cast<int>(idx - static_cast<long long>(pc) * vpc);
-    const int pi = pc / P, pj = pc - pi * P;
-    if (pi >= halo && pi < halo + T && pj >= halo && pj < halo + T) continue;   // interior
+    const int hc = static_cast<int>(idx / vpc);
+    const int v = static_cast<int>(idx - static_cast<long long>(hc) * vpc);
+    int pi, pj;
+    if (hc < n_strip) {
+      const int row = hc / P;
+      pj = hc - row * P;
+      pi = row < halo ? row : row + T;
+    } else {
+      const int e = hc - n_strip;
+      const int row = e / (2 * halo);
+      const int col = e - row * 2 * halo;
+      pi = halo + row;
+      pj = col < halo ? col : col + T;
+    }
+    const int pc = pi * P + pj;
     const int a = __ldg(src_a + tile * PP + pc);
     const int b = __ldg(src_b + tile * PP + pc);
     const long long chan = static_cast<long long>(C) + (v << 3);   // k|v start after q
