@@ -41,7 +41,7 @@ def flops_per_token(C, kernel, ratio=4.0):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/ (same workload, one launch each).
-NCU_TRAFFIC_BYTES = {"na3d_fwd": 1.064e9, "gemm_fc1_gelu": 1.288e9, "gemm_qkv_rope": 1.022e9}
+NCU_TRAFFIC_BYTES = {"na3d_fwd": 1.143e9, "gemm_fc1_gelu": 1.288e9, "gemm_qkv_rope": 1.022e9}
 
 
 def measured_peaks():
@@ -435,7 +435,9 @@ NA_SWEEP = dict(B=8, D=32, H=96, W=96, heads=16, head_dim=64, kernels=[[3, 7, 7]
 
 def na3d_sweep(torch, ops, iters=3):
     """Standalone neighbourhood attention on Q/K/V [8, 32, 96, 96, 16, 64] for three kernels:
-    milliseconds per launch and algorithmic TFLOP/s (4 * window * head_dim per query and head)."""
+    milliseconds per launch, algorithmic TFLOP/s (4 * window * head_dim per query and head) and
+    algorithmic GB/s (q, k, v read and o written once: the bound of the smallest kernel, whose
+    arithmetic intensity lies below the ridge of the machine)."""
     c = NA_SWEEP
     shape = (c["B"], c["D"], c["H"], c["W"], c["heads"], c["head_dim"])
     try:
@@ -453,7 +455,8 @@ def na3d_sweep(torch, ops, iters=3):
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / iters
             flop = 4.0 * kern[0] * kern[1] * kern[2] * c["head_dim"] * q.numel() / c["head_dim"]
-            res.append({"kernel": kern, "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12})
+            res.append({"kernel": kern, "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12,
+                        "gbs": 4 * q.numel() * 2 / (ms * 1e-3) / 1e9})
         del q, k, v, o
         torch.cuda.empty_cache()
         return {"shape": list(shape), "results": res}
