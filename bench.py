@@ -348,7 +348,13 @@ def sphere_step_bench(torch, dist, world, rank, dev, timed, steps=3):
     # halo exchange alone
     ms_halo = timed(lambda: stepper.halo(x), 5) / 5
     halo_bytes = x.numel() // (c["tile_tokens"] ** 2) * (P * P + c["tile_tokens"] ** 2) * 4
+    # windowed overlap-add un-pad of the padded outputs (alternative to the crop)
+    from strata_b200.halo import NormalizedCopyHaloAdjoint, kbd_window
+    unpad = NormalizedCopyHaloAdjoint(stepper.halo, window=kbd_window(P))
+    ypad = stepper.halo(x)
+    ms_unpad = timed(lambda: unpad(ypad), 5) / 5
     out = dict(ms_per_step=ms, halo_ms=ms_halo, halo_gbs=halo_bytes / (ms_halo * 1e-3) / 1e9,
+               unpad_adjoint_ms=ms_unpad, unpad_adjoint_gbs=halo_bytes / (ms_unpad * 1e-3) / 1e9,
                scaling="strong", config=c, tiles_per_rank=topo.tiles_per_rank,
                padded_tokens_per_step=topo.total_tiles * c["depth"] * P * P)
     stepper.close()

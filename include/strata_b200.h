@@ -149,6 +149,19 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
                                   const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
                                   int T, int halo, int64_t L, void* stream);
 
+/* Windowed overlap-add un-pad: the normalised transpose D_w^-1 A^T (w . y) of the field gather A
+ * above (replaces NormalizedHaloAdjoint.forward, screamcast/distributed_halo.py:438-448, whose
+ * transpose runs as a vector-Jacobian product of the regrid plus a reduce_scatter). h_peer_padded[r]:
+ * rank r's published padded tiles [L, tiles_per_rank*P*P] fp32 (P = T + 2*halo). offsets / cell /
+ * coef: for each local interior cell the padded cells copied from it (global padded cell ids
+ * g*P*P + pi*P + pj, coefficient 1 or 1/2), window [P*P], weights [tiles_per_rank*T*T] = the
+ * per-cell sum of coef*window. out: [L, tiles_per_rank*T*T]. Sums run entry by entry in fp32
+ * without fused multiply-add, so the result is reproducible bit for bit on the host. */
+int strata_halo_adjoint_fields_f32(float* out, const void* const* h_peer_padded, int world,
+                                   const int32_t* offsets, const int32_t* cell, const float* coef,
+                                   const float* window, const float* weights, int tiles_per_rank,
+                                   int T, int halo, int64_t L, void* stream);
+
 /* Per-block K/V halo (token space, halo exchange every block). The packed qkv rows of each rank
  * live in halo-padded layout [tiles_per_rank, D, P*P, ldqkv] (channels q | k | v, C each); the
  * interiors are written by strata_qkv_rope_padded_bf16. This call fills the k and v channels of

@@ -209,6 +209,51 @@ def padded_local_tiles(all_tiles: np.ndarray, topo: TileTopology) -> np.ndarray:
                      for t in topo.local_tiles], axis=-3)
 
 
+def halo_adjoint(padded_all: np.ndarray, topo: TileTopology, window: np.ndarray | None = None):
+    """Windowed overlap-add un-pad D_w^-1 A^T (w . y) of the copy-halo exchange A
+    (`padded_local_tiles`), after the reference's NormalizedHaloAdjoint
+    (screamcast/distributed_halo.py:330-448; there A is the KNN regrid, here the copy halo).
+
+    padded_all: (..., total_tiles, P, P) float32, the padded tiles of EVERY rank in global tile
+    order. Returns this rank's (..., tiles_per_rank, T, T).
+
+    A is recovered from `padded_local_tiles` itself, applied to an array of cell labels: the
+    index logic under test is not re-used. Every padded cell is either a copy of one interior
+    cell or the mean of two; the transpose hands its (windowed) value back with coefficient 1 or
+    1/2. Contributions are summed per interior cell in the order of the padded cell ids, every
+    product and sum rounded to float32 (the CUDA kernel keeps the same order: bit-exact).
+    """
+    T, P, G = topo.tile_size, topo.padded_tile_size, topo.total_tiles
+    full = TileTopology(1, 0, topo.face_size, T, topo.halo_width)
+    # labels: two probes with different cell values identify a(p), b(p) of every padded cell
+    ids = np.arange(G * T * T, dtype=np.float64).reshape(G, T, T)
+    pa = padded_local_tiles(ids, full)                    # a, or (a+b)/2
+    pb = padded_local_tiles(ids * ids, full)              # a^2, or (a^2+b^2)/2
+    s, q = pa.reshape(-1), pb.reshape(-1)
+    # single source: q == s^2; two sources: a, b = s +- sqrt(q - s^2)
+    d = np.sqrt(np.maximum(q - s * s, 0.0))
+    a = np.rint(s - d).astype(np.int64)
+    b = np.where(d > 0.25, np.rint(s + d).astype(np.int64), -1)
+    w = np.ones((P, P), np.float32) if window is None else np.asarray(window, np.float32)
+    wflat = np.tile(w.reshape(-1), G)
+    lead = padded_all.shape[:-3]
+    y = padded_all.reshape(*lead, -1).astype(np.float32)
+    wy = (wflat * y).astype(np.float32)
+    n_local = topo.tiles_per_rank * T * T
+    lo = topo.rank * n_local
+    acc = np.zeros((*lead, n_local), np.float32)
+    wsum = np.zeros(n_local, np.float32)
+    for p in range(a.size):                               # padded cells in id order
+        for src, coef in ((a[p], 1.0 if b[p] < 0 else 0.5), (b[p], 0.5)):
+            if src < lo or src >= lo + n_local:
+                continue
+            c = src - lo
+            acc[..., c] = (acc[..., c] + (np.float32(coef) * wy[..., p]).astype(np.float32)
+                           ).astype(np.float32)
+            wsum[c] = np.float32(wsum[c] + np.float32(coef) * wflat[p])
+    return (acc / wsum).astype(np.float32).reshape(*lead, topo.tiles_per_rank, T, T)
+
+
 # --------------------------------------------------------------------------- wind rotation
 def _basis(lat, lon):
     R = (np.cos(lat) * np.cos(lon), np.cos(lat) * np.sin(lon), np.sin(lat))

@@ -348,6 +348,41 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
+int strata_halo_adjoint_fields_f32(float* out, const void* const* h_peer_padded, int world,
+                                   const int32_t* offsets, const int32_t* cell, const float* coef,
+                                   const float* window, const float* weights, int tiles_per_rank,
+                                   int T, int halo, int64_t L, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!out || !h_peer_padded || !offsets || !cell || !coef || !window || !weights)
+    return STRATA_ERR_ARG;
+  if (world < 1 || world > HALO_MAX_RANKS) return STRATA_ERR_UNSUPPORTED;
+  if (tiles_per_rank <= 0 || T <= 0 || halo < 0 || L < 0) return STRATA_ERR_ARG;
+  if (L == 0) return STRATA_OK;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_padded[r]) return STRATA_ERR_ARG;
+    pp.p[r] = h_peer_padded[r];
+  }
+  const int P = T + 2 * halo;
+  const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
+  const long long pcells = static_cast<long long>(tiles_per_rank) * P * P;
+  if (pcells * world > 0x7fffffffLL || L > 0x7fffffffLL) return STRATA_ERR_ARG;
+  long long bx = (cells + 255) / 256;
+  if (bx > 4096) bx = 4096;
+  long long by = L;
+  const long long want = static_cast<long long>(sms) * 16;
+  if (bx * by > want) by = (want + bx - 1) / bx;
+  if (by < 1) by = 1;
+  if (by > 65535) by = 65535;
+  dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(by));
+  halo_adjoint_fields_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      out, pp, offsets, cell, coef, window, weights, static_cast<int>(cells),
+      static_cast<int>(pcells), P * P, static_cast<int>(L));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
 int strata_halo_gather_kv_bf16(void* qkv, const void* const* h_peer_qkv, int world,
                                const int32_t* src_a, const int32_t* src_b, const void* dcs_a,
                                const void* dcs_b, int tiles_per_rank, int D, int T, int halo, int C,

@@ -103,6 +103,39 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
   }
 }
 
+// Windowed overlap-add un-pad (the normalised transpose of the field gather): every interior
+// cell c of this rank collects the padded cells that were copied from it - its own image and
+// its copies in neighbouring tiles' halos, in local or peer memory - as
+//     out[l, c] = ( sum_j coef_j * (window[p_j] * y[l, p_j]) ) / weights[c]
+// with entries offsets[c]..offsets[c+1] sorted by padded cell id. Pull form: no atomics, a
+// fixed summation order, every product and sum rounded separately (no fused multiply-add), so
+// the result is bit-identical to the same loop on the host.
+// Padded sources: [L, tiles_per_rank*P*P] fp32 per rank; out [L, tiles_per_rank*T*T].
+__global__ void __launch_bounds__(256)
+halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
+                           const int* __restrict__ offsets, const int* __restrict__ cell,
+                           const float* __restrict__ coef, const float* __restrict__ window,
+                           const float* __restrict__ weights, int n_cells,
+                           int padded_cells_per_rank, int PP, int L) {
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n_cells; c += gridDim.x * blockDim.x) {
+    const int e0 = __ldg(offsets + c), e1 = __ldg(offsets + c + 1);
+    const float wsum = __ldg(weights + c);
+    for (int l = blockIdx.y; l < L; l += gridDim.y) {
+      const long long so = static_cast<long long>(l) * padded_cells_per_rank;
+      float acc = 0.f;
+      for (int e = e0; e < e1; ++e) {
+        const int p = __ldg(cell + e);
+        const int rank = p / padded_cells_per_rank;
+        const int local = p - rank * padded_cells_per_rank;
+        const float y = static_cast<const float*>(src.p[rank])[so + local];
+        const float wy = __fmul_rn(__ldg(window + local % PP), y);
+        acc = __fadd_rn(acc, __fmul_rn(__ldg(coef + e), wy));
+      }
+      out[static_cast<long long>(l) * n_cells + c] = __fdiv_rn(acc, wsum);
+    }
+  }
+}
+
 // Per-block K/V halo for tiles whose packed qkv rows live in halo-padded layout
 // [tiles_per_rank, D, P*P, ld] (q | k | v channel blocks of C each): the interiors were written
 // by this rank's QKV GEMM, this kernel fills the K and V channels of the halo cells from the

@@ -28,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .topology import TileTopology, halo_source_maps
+from .topology import TileTopology, halo_adjoint_lists, halo_source_maps
 
 
 class _DevPtrTensorView:
@@ -235,6 +235,70 @@ class DistributedTileCopyHaloPadding(torch.nn.Module):
             self._shared.close()
             self._shared = None
 
+
+
+class NormalizedCopyHaloAdjoint(torch.nn.Module):
+    """Windowed overlap-add un-pad: D_w^-1 A^T (w . y) for the copy-halo exchange A.
+
+    Interface of the reference's NormalizedHaloAdjoint (screamcast/distributed_halo.py:330-448):
+    built from the halo module and an optional [P, P] window, `forward(padded[..., tiles_per_rank,
+    P, P]) -> [..., tiles_per_rank, T, T]`, buffers `.window` and `.weights`. With a uniform
+    window it is the Shepard normalisation D^-1 A^T y; a Kaiser-Bessel-derived window
+    (`kbd_window`) down-weights halo copies against the owning tile's own values, as the rollout
+    launcher does (scripts/ace/run_screamcast_nudged.py:622-634).
+
+    Mechanism: each rank publishes its padded tiles in the halo module's peer buffer; after the
+    flag barrier a pull kernel lets every interior cell sum the padded cells that were copied
+    from it, wherever they live, in a fixed order - no reduce_scatter, no atomics.
+    """
+
+    def __init__(self, halo_exchange: DistributedTileCopyHaloPadding, window: torch.Tensor | None = None):
+        super().__init__()
+        self.halo_exchange = halo_exchange
+        topo = halo_exchange.topology
+        P = topo.padded_tile_size
+        dev = halo_exchange.src_a.device
+        w = None if window is None else window.detach().to("cpu", torch.float32).numpy()
+        offsets, cell, coef, weights = halo_adjoint_lists(topo, w)
+        self.register_buffer("_offsets", torch.from_numpy(offsets).to(dev), persistent=False)
+        self._cell = torch.from_numpy(cell).to(dev)
+        self._coef = torch.from_numpy(coef).to(dev)
+        win = torch.ones(P, P) if window is None else window.detach().to("cpu", torch.float32)
+        self.register_buffer("window", win.reshape(-1).to(dev).contiguous(), persistent=False)
+        self.register_buffer("weights", torch.from_numpy(weights).to(dev).reshape(
+            1, 1, topo.tiles_per_rank, topo.tile_size, topo.tile_size), persistent=False)
+
+    def forward(self, padded: torch.Tensor) -> torch.Tensor:
+        topo = self.halo_exchange.topology
+        P, T = topo.padded_tile_size, topo.tile_size
+        *shape, tpr, nx, ny = padded.shape
+        if tpr != topo.tiles_per_rank or nx != P or ny != P:
+            raise ValueError(f"Expected [..., {topo.tiles_per_rank}, {P}, {P}], got {tuple(padded.shape)}")
+        if not padded.is_cuda:
+            raise _lib.StrataLibraryError("halo adjoint needs CUDA tensors (no CPU path)")
+        if padded.dtype != torch.float32:
+            raise TypeError(f"field-space halo adjoint is float32, got {padded.dtype}")
+        L = int(np.prod(shape)) if shape else 1
+        out = torch.empty(*shape, tpr, T, T, dtype=padded.dtype, device=padded.device)
+        if L == 0:
+            return out
+        pc = padded.contiguous()
+        with torch.cuda.device(padded.device):
+            src = self.halo_exchange._publish_and_sync(pc.view(-1).view(torch.uint8))
+            _lib.check(_lib.load().strata_halo_adjoint_fields_f32(
+                out.data_ptr(), src, topo.world_size, self._offsets.data_ptr(), self._cell.data_ptr(),
+                self._coef.data_ptr(), self.window.data_ptr(), self.weights.data_ptr(), tpr, T,
+                topo.halo_width, L, torch.cuda.current_stream().cuda_stream),
+                "strata_halo_adjoint_fields_f32")
+        return out
+
+
+def kbd_window(padded_size: int, beta: float = 10 * np.pi) -> torch.Tensor:
+    """Separable Kaiser-Bessel-derived window [P, P] (the rollout launcher's choice:
+    scripts/ace/run_screamcast_nudged.py:624-630); P must be even."""
+    from scipy.signal.windows import kaiser_bessel_derived
+    w1 = torch.tensor(kaiser_bessel_derived(padded_size, beta), dtype=torch.float32)
+    return w1[None, :] * w1[:, None]
 
 def channel_chunked(fn, chunk: int = 32):
     """Apply a halo module over channel chunks (the reference's rollout driver wraps its halo

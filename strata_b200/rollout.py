@@ -17,7 +17,7 @@ import math
 import numpy as np
 import torch
 
-from .halo import DistributedTileCopyHaloPadding
+from .halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window
 from .topology import TileTopology, apply_maps_numpy, halo_source_maps
 
 
@@ -72,8 +72,14 @@ class TiledSphereStepper(torch.nn.Module):
     `index = {"lat", "lon"}` in radians (index_is_latlon=True) and tile size T + 2*halo.
     """
 
-    def __init__(self, network: torch.nn.Module, topology: TileTopology, device=None, group=None):
+    def __init__(self, network: torch.nn.Module, topology: TileTopology, device=None, group=None,
+                 unpad: str = "crop", window: str | None = None):
+        """unpad: "crop" (drop the halo, `topology.crop`) or "adjoint" (windowed overlap-add of
+        the padded outputs, `--halo-adjoint` of the reference's launcher); window: None
+        (uniform) or "kbd" (`--halo-window`)."""
         super().__init__()
+        if unpad not in ("crop", "adjoint"):
+            raise ValueError(f"unpad must be 'crop' or 'adjoint', got {unpad!r}")
         self.network = network
         self.topology = topology
         plat, plon = padded_tile_latlon(topology)
@@ -81,6 +87,10 @@ class TiledSphereStepper(torch.nn.Module):
         self.halo = DistributedTileCopyHaloPadding(
             topology=topology, lat_deg=torch.from_numpy(plat).float().to(dev),
             lon_deg=torch.from_numpy(plon).float().to(dev), device=dev, group=group)
+        self.unpad = None
+        if unpad == "adjoint":
+            win = kbd_window(topology.padded_tile_size) if window == "kbd" else None
+            self.unpad = NormalizedCopyHaloAdjoint(self.halo, window=win)
         self.register_buffer("lat_rad", torch.deg2rad(self.halo.lat_deg), persistent=False)
         self.register_buffer("lon_rad", torch.deg2rad(self.halo.lon_deg), persistent=False)
 
@@ -89,8 +99,10 @@ class TiledSphereStepper(torch.nn.Module):
         padded = self.halo(x)                                   # [C, D, tpr, P, P]
         xin = padded.permute(2, 0, 1, 3, 4).contiguous()        # tiles become the batch
         y = self.network(xin, {"lat": self.lat_rad, "lon": self.lon_rad})
-        y = self.topology.crop(y)                               # [tpr, C_out, D, T, T]
-        return y.permute(1, 2, 0, 3, 4).contiguous()
+        if self.unpad is None:
+            y = self.topology.crop(y)                           # [tpr, C_out, D, T, T]
+            return y.permute(1, 2, 0, 3, 4).contiguous()
+        return self.unpad(y.permute(1, 2, 0, 3, 4).float().contiguous())
 
     def close(self):
         self.halo.close()

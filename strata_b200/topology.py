@@ -260,3 +260,53 @@ def apply_maps_numpy(all_tiles: np.ndarray, src_a: np.ndarray, src_b: np.ndarray
     va = flat[..., src_a]
     vb = flat[..., np.where(src_b < 0, 0, src_b)]
     return np.where(src_b < 0, va, (va + vb) / 2).astype(all_tiles.dtype)
+
+
+def halo_adjoint_lists(topo: TileTopology, window: np.ndarray | None = None):
+    """Transpose of the halo gather, as pull lists for this rank's interior cells.
+
+    The gather fills padded cell p with x[a(p)] (or the mean of x[a(p)] and x[b(p)]). Its
+    transpose sends every padded cell's value back to the interior cell(s) it was copied from.
+    Seen from an interior cell c that is a list of padded cells - its own image in its own
+    tile, plus its copies in the halos of neighbouring tiles, on whichever rank they live -
+    with a coefficient each (1, or 1/2 for a corner mean).
+
+    Returns (offsets int32 [n_local + 1], cell int32 [n_entries], coef float32 [n_entries],
+    weights float32 [n_local]): entries of local interior cell c are offsets[c]:offsets[c+1],
+    sorted by padded-cell id; `cell` is the GLOBAL padded cell id  g*P*P + pi*P + pj  (g in
+    global tile order, so the owning rank is id // (tiles_per_rank*P*P)); weights[c] =
+    sum coef * window[pi, pj] (window of ones by default) - the normaliser of the windowed
+    overlap-add (reference: NormalizedHaloAdjoint, screamcast/distributed_halo.py:330-448).
+    """
+    T, P = topo.tile_size, topo.padded_tile_size
+    full = TileTopology(1, 0, topo.face_size, T, topo.halo_width)
+    a, b = halo_source_maps(full)                       # [G, P, P], global interior cell ids
+    pid = np.arange(a.size, dtype=np.int64)
+    af, bf = a.reshape(-1).astype(np.int64), b.reshape(-1).astype(np.int64)
+    single = bf < 0
+    src = np.concatenate([af[single], af[~single], bf[~single]])
+    dst = np.concatenate([pid[single], pid[~single], pid[~single]])
+    coef = np.concatenate([np.ones(single.sum(), np.float32),
+                           np.full(2 * (~single).sum(), 0.5, np.float32)])
+    n_local = topo.tiles_per_rank * T * T
+    lo = topo.rank * n_local
+    keep = (src >= lo) & (src < lo + n_local)
+    src, dst, coef = src[keep] - lo, dst[keep], coef[keep]
+    order = np.lexsort((dst, src))
+    src, dst, coef = src[order], dst[order], coef[order]
+    offsets = np.zeros(n_local + 1, dtype=np.int64)
+    np.add.at(offsets, src + 1, 1)
+    offsets = np.cumsum(offsets)
+    if dst.size and dst.max() >= 2 ** 31:
+        raise ValueError("grid too large for 32-bit padded cell ids")
+    w = np.ones((P, P), np.float32) if window is None else np.asarray(window, np.float32)
+    if w.shape != (P, P):
+        raise ValueError(f"window must be [{P}, {P}]")
+    wv = coef * w.reshape(-1)[dst % (P * P)]
+    weights = np.zeros(n_local, dtype=np.float32)
+    # same summation order as the kernel: entry by entry, in float32
+    k = np.arange(dst.size) - offsets[src]
+    for j in range(int(k.max()) + 1 if dst.size else 0):
+        m = k == j
+        weights[src[m]] = (weights[src[m]] + wv[m]).astype(np.float32)
+    return offsets.astype(np.int32), dst.astype(np.int32), coef, weights

@@ -12,7 +12,7 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 from oracle import halo_oracle as ho  # noqa: E402
-from strata_b200.halo import DistributedTileCopyHaloPadding  # noqa: E402
+from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window  # noqa: E402
 from strata_b200.topology import TileTopology  # noqa: E402
 from tests.golden.make_golden import payload  # noqa: E402
 
@@ -47,6 +47,17 @@ def main():
     P = topo.padded_tile_size
     got = out.cpu().reshape(topo.tiles_per_rank, D, P, P, C).permute(1, 4, 0, 2, 3)
     assert torch.equal(got, want), f"rank {rank}: token halo differs"
+    # windowed overlap-add un-pad: every rank's padded tiles differ, sources sit on both GPUs
+    P = topo.padded_tile_size
+    win = kbd_window(P)
+    unpad = NormalizedCopyHaloAdjoint(mod, window=win)
+    g = torch.Generator().manual_seed(9)
+    pad_all = torch.randn(2, topo.total_tiles, P, P, generator=g)
+    for step in range(3):
+        got = unpad((pad_all[:, s:s + topo.tiles_per_rank] + step).cuda())
+        want = ho.halo_adjoint((pad_all + step).numpy(), topo_o, win.numpy())
+        assert np.array_equal(got.cpu().numpy(), want), f"rank {rank} step {step}: halo adjoint differs"
+    mod.check_status()
     dist.barrier()
     mod.close()
     if rank == 0:

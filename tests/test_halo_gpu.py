@@ -97,6 +97,32 @@ def test_shape_validation():
         mod(torch.zeros(1, 24, 5, 4, device="cuda"))
 
 
+
+@pytest.mark.parametrize("window", ["ones", "kbd"])
+def test_halo_adjoint_bit_exact(window):
+    from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window
+    from strata_b200.topology import TileTopology
+    fs, ts, hw = 16, 8, 3
+    topo = TileTopology(1, 0, fs, ts, hw)
+    otopo = ho.TileTopology(1, 0, fs, ts, hw)
+    P = topo.padded_tile_size
+    win = None if window == "ones" else kbd_window(P)
+    pad_mod = DistributedTileCopyHaloPadding(topology=topo)
+    unpad = NormalizedCopyHaloAdjoint(pad_mod, window=win)
+    g = torch.Generator().manual_seed(11)
+    y = torch.randn(2, 3, topo.tiles_per_rank, P, P, generator=g)
+    got = unpad(y.cuda())
+    pad_mod.check_status()
+    want = ho.halo_adjoint(y.numpy(), otopo, None if win is None else win.numpy())
+    assert np.array_equal(got.cpu().numpy(), want)
+    # constant round trip through the real exchange (reference: tests/distributed/
+    # test_distributed_halo.py:105) and crop(pad(x)) == x for the uniform window on
+    # consistent tiles away from the corner means
+    c = torch.full((1, topo.tiles_per_rank, ts, ts), 1.75, device="cuda")
+    assert torch.allclose(unpad(pad_mod(c)), c, rtol=1e-6, atol=0)
+    with pytest.raises(ValueError):
+        unpad(torch.zeros(1, topo.tiles_per_rank, P, P - 1, device="cuda"))
+
 def _two_gpus():
     return torch.cuda.is_available() and torch.cuda.device_count() >= 2
 

@@ -157,3 +157,30 @@ def test_sphere_stepper_is_pad_network_crop():
         want = topo.crop(net(padded, {"lat": step.lat_rad, "lon": step.lon_rad})).permute(1, 2, 0, 3, 4)
     assert torch.equal(y, want)
     step.halo.check_status()
+
+
+def test_sphere_stepper_overlap_add_unpad():
+    # un-pad by windowed overlap-add instead of the crop: with a network that returns its input,
+    # every interior cell becomes a weighted mean of copies of itself - the input comes back
+    # (up to rounding; cells that feed a corner mean also receive that mean back)
+    from strata_b200.rollout import TiledSphereStepper
+    from strata_b200.topology import TileTopology
+
+    class Identity(torch.nn.Module):
+        def forward(self, x, index):
+            return x
+    topo = TileTopology(1, 0, face_size=32, tile_size=16, halo_width=4)
+    step = TiledSphereStepper(Identity(), topo, unpad="adjoint", window="kbd")
+    x = torch.randn(2, 3, topo.tiles_per_rank, 16, 16, device="cuda",
+                    generator=torch.Generator("cuda").manual_seed(2))
+    y = step(x)
+    assert y.shape == x.shape
+    away = torch.ones(16, 16, dtype=torch.bool)      # cells that no corner mean draws from
+    for r in (slice(0, 4), slice(12, 16)):
+        for c in (slice(0, 4), slice(12, 16)):
+            away[r, c] = False
+    assert torch.allclose(y[..., away], x[..., away], rtol=1e-5, atol=1e-6)
+    assert (y - x).abs().max() < 4.0                 # corner cells: a mean of nearby values
+    step.halo.check_status()
+    with pytest.raises(ValueError):
+        TiledSphereStepper(Identity(), topo, unpad="average")
