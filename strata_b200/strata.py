@@ -38,9 +38,45 @@ class PatchEmbed3D(nn.Module):
         self.proj = nn.Conv3d(in_chans, embed_dim, kernel_size=self.patch_size,
                               stride=self.patch_size)
 
+        self._gemm_cache = None
+        self._gemm_key = None
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.proj(x)
         return y.flatten(2).transpose(1, 2)
+
+    def _gemm_weights(self):
+        """The convolution as a GEMM: weight [embed_dim, K] with K = C_in*pv*ph*pw in
+        (c, v, h, w) order, K padded with zero columns to a multiple of 8; bf16, re-cast when
+        a parameter changes."""
+        key = tuple((p.data_ptr(), p._version, p.device) for p in self.proj.parameters())
+        if self._gemm_cache is not None and key == self._gemm_key:
+            return self._gemm_cache
+        w = self.proj.weight.detach()
+        K = w[0].numel()
+        Kp = (K + 7) // 8 * 8
+        wm = torch.zeros(w.shape[0], Kp, dtype=torch.bfloat16, device=w.device)
+        wm[:, :K] = w.reshape(w.shape[0], K)
+        b = None if self.proj.bias is None else self.proj.bias.detach().float().contiguous()
+        self._gemm_cache, self._gemm_key = (wm, b, K, Kp), key
+        return self._gemm_cache
+
+    def tokens_bf16(self, x: torch.Tensor) -> torch.Tensor:
+        """[B, C_in, D, H, W] -> bf16 tokens [B, D'*H'*W', embed_dim] on the tensor cores: the
+        non-overlapping patches are laid out as rows of a [tokens, K] matrix (one strided copy,
+        which also casts to bf16) and multiplied by the convolution weight with the bias epilogue.
+        Same arithmetic as the Conv3d under bf16 autocast, without its channels-first output and
+        the transposing copy that would follow."""
+        B, cin, D, H, W = x.shape
+        pv, ph, pw = self.patch_size
+        d, h, w = D // pv, H // ph, W // pw
+        wm, bias, K, Kp = self._gemm_weights()
+        a = torch.empty(B * d * h * w, Kp, dtype=torch.bfloat16, device=x.device)
+        if Kp != K:
+            a[:, K:].zero_()
+        a.view(B, d, h, w, Kp)[..., :K].view(B, d, h, w, cin, pv, ph, pw).copy_(
+            x.view(B, cin, d, pv, h, ph, w, pw).permute(0, 2, 4, 6, 1, 3, 5, 7))
+        return ops.linear(a, wm, bias).view(B, d * h * w, wm.shape[0])
 
 
 class Mlp(nn.Module):
@@ -122,6 +158,28 @@ class FinalLayer(nn.Module):
     def __init__(self, dim: int, out_features: int):
         super().__init__()
         self.linear = nn.Linear(dim, out_features)
+        self._gemm_cache = None
+        self._gemm_key = None
+
+    def forward_bf16(self, tokens: torch.Tensor) -> torch.Tensor:
+        """bf16 tokens [..., dim] -> fp32 [..., out_features] through the library's LayerNorm
+        and GEMM kernels (output rows padded to a multiple of 8 columns for the store)."""
+        key = tuple((p.data_ptr(), p._version, p.device) for p in self.linear.parameters())
+        if self._gemm_cache is None or key != self._gemm_key:
+            w = self.linear.weight.detach()
+            N = w.shape[0]
+            Np = (N + 7) // 8 * 8
+            wm = torch.zeros(Np, w.shape[1], dtype=torch.bfloat16, device=w.device)
+            wm[:N] = w
+            b = None
+            if self.linear.bias is not None:
+                b = torch.zeros(Np, dtype=torch.float32, device=w.device)
+                b[:N] = self.linear.bias.detach().float()
+            self._gemm_cache, self._gemm_key = (wm, b, N), key
+        wm, b, N = self._gemm_cache
+        lead = tokens.shape[:-1]
+        y = ops.linear(ops.layernorm(tokens.reshape(-1, tokens.shape[-1])), wm, b)
+        return y[:, :N].float().view(*lead, N)
 
 
 class StrataTransformer3D(nn.Module):
@@ -218,14 +276,15 @@ class StrataTransformer3D(nn.Module):
     def forward(self, x: torch.Tensor, pos: torch.Tensor | None = None) -> torch.Tensor:
         B, _, D, H, W = x.shape
         grid = self.token_grid(D, H, W)
-        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=x.is_cuda):
-            tokens = self.patch_embed(x)
-        tokens = tokens.to(torch.bfloat16).contiguous()
+        if isinstance(self.patch_embed, PatchEmbed3D):
+            tokens = self.patch_embed.tokens_bf16(x.contiguous())
+        else:   # a caller-assigned embed module (e.g. the de-aliased variant): run it as it is
+            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=x.is_cuda):
+                tokens = self.patch_embed(x)
+            tokens = tokens.to(torch.bfloat16).contiguous()
         cos, sin = self.rope_tables(pos, B, grid)
         tokens = self.forward_tokens(tokens, grid, cos, sin)
-        y = torch.nn.functional.layer_norm(tokens.float(), (self.embed_dim,), eps=1e-6)
-        y = self.final_layer.linear(y)
-        return self.unpatchify(y, grid)
+        return self.unpatchify(self.final_layer.forward_bf16(tokens), grid)
 
     def unpatchify(self, y: torch.Tensor, grid) -> torch.Tensor:
         B = y.shape[0]
