@@ -197,6 +197,28 @@ int strata_na3d_fwd_region_bf16(const void* q, int64_t ldq, const void* k, int64
                                 float scale, int q_h0, int q_H, int q_w0, int q_W, int o_h0,
                                 int o_H, int o_w0, int o_W, void* stream);
 
+/* Fused pre-processing of the model wrapper (replaces _StrataModelBase._preprocess,
+ * screamcast/strata_wrappers.py:206-238, forward_uv_to_tile, screamcast/wind_rotation.py:49-92,
+ * and the patch gathering of the patch-embedding convolution): x [B, C_in, D, H, W] fp32 ->
+ * a [B*(D/pv)*(H/ph)*(W/pw), lda] bf16, the operand of the patch-embedding GEMM with columns in
+ * (channel, dv, dh, dw) order - the layout of a flattened Conv3d weight - and zeros beyond
+ * K = (C_in + 2*concat_lat)*pv*ph*pw. u_idx, v_idx >= 0: those two channels are the east / north
+ * wind and are rotated into the tangent basis of the tile centre (lat0, lon0 [B], radians);
+ * concat_lat: cos(lat), sin(lat) are appended as channels C_in, C_in+1. lat, lon: [B, H, W]. */
+int strata_preprocess_patches_bf16(const float* x, int B, int C_in, int D, int H, int W,
+                                   const float* lat, const float* lon, const float* lat0,
+                                   const float* lon0, int u_idx, int v_idx, int concat_lat, int pv,
+                                   int ph, int pw, void* a, int64_t lda, void* stream);
+
+/* Fused post-processing (replaces unpatchify + _postprocess, strata_wrappers.py:240-249, and
+ * inverse_tile_to_uv, wind_rotation.py:95-144): y [tokens, ldy] bf16, the final linear layer's
+ * output with columns in (dv, dh, dw, channel) order -> out [B, C_out, D, H, W] fp32, wind
+ * channels rotated back to east / north. */
+int strata_postprocess_fields_f32(const void* y, int64_t ldy, int B, int C_out, int D, int H, int W,
+                                  const float* lat, const float* lon, const float* lat0,
+                                  const float* lon0, int u_idx, int v_idx, int pv, int ph, int pw,
+                                  float* out, void* stream);
+
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
  * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work

@@ -61,6 +61,12 @@ _SIGNATURES = {
     "strata_halo_adjoint_fields_f32": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                c_int64, c_void_p]),
+    "strata_preprocess_patches_bf16": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                               c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
+    "strata_postprocess_fields_f32": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_int, c_int, c_void_p, c_void_p]),
     "strata_halo_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p]),
     "strata_ipc_alloc": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
     "strata_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),

@@ -9,6 +9,7 @@
 #include "layernorm.cuh"
 #include "na3d.cuh"
 #include "halo.cuh"
+#include "prepost.cuh"
 
 using namespace strata;
 
@@ -281,6 +282,64 @@ int strata_block_forward_bf16(const void* x, void* y, int n_tiles, int D, int H,
     return r;
   return strata_linear_bf16(hbuf, hidden, wts->w_fc2, hidden, wts->b_fc2, y, C, M, C, hidden,
                             STRATA_EPI_RESIDUAL, x1, C, stream);
+}
+
+static int prepost_check(int B, int C, int D, int H, int W, int pv, int ph, int pw, const float* lat,
+                         const float* lon, const float* lat0, const float* lon0, int u_idx,
+                         int v_idx, int need_latlon) {
+  if (B < 0 || C <= 0 || D <= 0 || H <= 0 || W <= 0 || pv <= 0 || ph <= 0 || pw <= 0)
+    return STRATA_ERR_ARG;
+  if (D % pv || H % ph || W % pw) return STRATA_ERR_ARG;
+  const bool rot = u_idx >= 0 || v_idx >= 0;
+  if (rot && (u_idx < 0 || v_idx < 0 || u_idx >= C || v_idx >= C || u_idx == v_idx || !lat0 || !lon0))
+    return STRATA_ERR_ARG;
+  if ((rot || need_latlon) && (!lat || !lon)) return STRATA_ERR_ARG;
+  if (static_cast<long long>(B) * (D / pv) * (H / ph) * (W / pw) > 0x7fffffffLL) return STRATA_ERR_ARG;
+  return STRATA_OK;
+}
+
+int strata_preprocess_patches_bf16(const float* x, int B, int C_in, int D, int H, int W,
+                                   const float* lat, const float* lon, const float* lat0,
+                                   const float* lon0, int u_idx, int v_idx, int concat_lat, int pv,
+                                   int ph, int pw, void* a, int64_t lda, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  int r = prepost_check(B, C_in, D, H, W, pv, ph, pw, lat, lon, lat0, lon0, u_idx, v_idx, concat_lat);
+  if (r != STRATA_OK) return r;
+  if (!x || !a) return STRATA_ERR_ARG;
+  const long long K = static_cast<long long>(C_in + (concat_lat ? 2 : 0)) * pv * ph * pw;
+  if (lda < K) return STRATA_ERR_ARG;
+  if (B == 0) return STRATA_OK;
+  PrePostParams p{B, C_in, D, H, W, pv, ph, pw, u_idx < 0 ? -1 : u_idx, u_idx < 0 ? -1 : v_idx,
+                  concat_lat ? 1 : 0, lat, lon, lat0, lon0, lda};
+  const long long npix = static_cast<long long>(B) * H * W;
+  long long blocks = (npix + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  preprocess_patches_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(a), p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_postprocess_fields_f32(const void* y, int64_t ldy, int B, int C_out, int D, int H, int W,
+                                  const float* lat, const float* lon, const float* lat0,
+                                  const float* lon0, int u_idx, int v_idx, int pv, int ph, int pw,
+                                  float* out, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  int r = prepost_check(B, C_out, D, H, W, pv, ph, pw, lat, lon, lat0, lon0, u_idx, v_idx, 0);
+  if (r != STRATA_OK) return r;
+  if (!y || !out || ldy < static_cast<long long>(C_out) * pv * ph * pw) return STRATA_ERR_ARG;
+  if (B == 0) return STRATA_OK;
+  PrePostParams p{B, C_out, D, H, W, pv, ph, pw, u_idx < 0 ? -1 : u_idx, u_idx < 0 ? -1 : v_idx, 0,
+                  lat, lon, lat0, lon0, ldy};
+  const long long npix = static_cast<long long>(B) * H * W;
+  long long blocks = (npix + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  postprocess_fields_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), out, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
 int strata_halo_gather_tokens_bf16(void* out, const void* const* h_peer_src, int world,

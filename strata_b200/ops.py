@@ -289,3 +289,73 @@ def na3d_region(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel, regio
             B, D, H, W, nh, hd, kd, kh, kw, float(scale) if scale else 0.0, h0, Hq, w0, Wq,
             oh0, Ho, ow0, Wo, _stream_ptr(q)), "strata_na3d_fwd_region_bf16")
     return out
+
+
+def _f32_dev(t, name, shape=None):
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA float32 tensor")
+    t = t.contiguous()
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t
+
+
+def preprocess_patches(x: torch.Tensor, lat, lon, lat0=None, lon0=None, wind=None,
+                       concat_lat: bool = False, patch=(1, 1, 1), k_pad: int | None = None):
+    """Fused wind rotation + latitude channels + patch gathering + bf16 cast.
+
+    x [B, C_in, D, H, W] fp32 -> [B*(D/pv)*(H/ph)*(W/pw), Kp] bf16 with columns (channel, dv, dh,
+    dw), K = (C_in + 2*concat_lat)*pv*ph*pw padded with zeros to Kp (default: next multiple of
+    8). lat / lon [B, H, W] radians (needed for rotation or latitude channels); wind = (u, v)
+    channel indices with lat0 / lon0 [B] the tile centres."""
+    if x.dtype != torch.float32 or not x.is_cuda or x.dim() != 5:
+        raise TypeError("x must be a CUDA float32 [B, C, D, H, W] tensor")
+    x = x.contiguous()
+    B, C, D, H, W = x.shape
+    pv, ph, pw = (int(v) for v in patch)
+    K = (C + (2 if concat_lat else 0)) * pv * ph * pw
+    Kp = (K + 7) // 8 * 8 if k_pad is None else int(k_pad)
+    u, v = (-1, -1) if wind is None else (int(wind[0]), int(wind[1]))
+    lat = _f32_dev(lat, "lat", (B, H, W))
+    lon = _f32_dev(lon, "lon", (B, H, W))
+    lat0 = None if lat0 is None else _f32_dev(lat0.reshape(-1), "lat0", (B,))
+    lon0 = None if lon0 is None else _f32_dev(lon0.reshape(-1), "lon0", (B,))
+    if D % pv or H % ph or W % pw:
+        raise ValueError(f"grid {(D, H, W)} is not divisible by the patch {(pv, ph, pw)}")
+    a = torch.empty(B * (D // pv) * (H // ph) * (W // pw), Kp, dtype=torch.bfloat16, device=x.device)
+    p = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_preprocess_patches_bf16(
+            x.data_ptr(), B, C, D, H, W, p(lat), p(lon), p(lat0), p(lon0), u, v,
+            1 if concat_lat else 0, pv, ph, pw, a.data_ptr(), Kp, _stream_ptr(x)),
+            "strata_preprocess_patches_bf16")
+    return a
+
+
+def postprocess_fields(y: torch.Tensor, shape, lat=None, lon=None, lat0=None, lon0=None, wind=None,
+                       patch=(1, 1, 1)) -> torch.Tensor:
+    """Fused unpatchify + inverse wind rotation: y [tokens, >= pv*ph*pw*C_out] bf16 with columns
+    (dv, dh, dw, channel) -> [B, C_out, D, H, W] fp32 (shape = (B, C_out, D, H, W))."""
+    _require_cuda_bf16(y, "y")
+    if y.dim() != 2 or y.stride(1) != 1:
+        raise ValueError("y must be a row-major [tokens, columns] matrix")
+    B, C, D, H, W = (int(v) for v in shape)
+    pv, ph, pw = (int(v) for v in patch)
+    if D % pv or H % ph or W % pw:
+        raise ValueError(f"grid {(D, H, W)} is not divisible by the patch {(pv, ph, pw)}")
+    if y.shape[0] != B * (D // pv) * (H // ph) * (W // pw) or y.shape[1] < C * pv * ph * pw:
+        raise ValueError("y does not match the requested field shape")
+    u, v = (-1, -1) if wind is None else (int(wind[0]), int(wind[1]))
+    lat = _f32_dev(lat, "lat", (B, H, W))
+    lon = _f32_dev(lon, "lon", (B, H, W))
+    lat0 = None if lat0 is None else _f32_dev(lat0.reshape(-1), "lat0", (B,))
+    lon0 = None if lon0 is None else _f32_dev(lon0.reshape(-1), "lon0", (B,))
+    out = torch.empty(B, C, D, H, W, dtype=torch.float32, device=y.device)
+    p = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.load().strata_postprocess_fields_f32(
+            y.data_ptr(), y.stride(0), B, C, D, H, W, p(lat), p(lon), p(lat0), p(lon0), u, v,
+            pv, ph, pw, out.data_ptr(), _stream_ptr(y)), "strata_postprocess_fields_f32")
+    return out

@@ -78,6 +78,14 @@ class PatchEmbed3D(nn.Module):
             x.view(B, cin, d, pv, h, ph, w, pw).permute(0, 2, 4, 6, 1, 3, 5, 7))
         return ops.linear(a, wm, bias).view(B, d * h * w, wm.shape[0])
 
+    def tokens_from_patches(self, a: torch.Tensor, n_tiles: int) -> torch.Tensor:
+        """Rows already gathered and cast (ops.preprocess_patches with k_pad = the padded K of
+        `_gemm_weights`) -> bf16 tokens [n_tiles, tokens, embed_dim]."""
+        wm, bias, _, Kp = self._gemm_weights()
+        if a.shape[1] != Kp:
+            raise ValueError(f"patch matrix has {a.shape[1]} columns, the embedding expects {Kp}")
+        return ops.linear(a, wm, bias).view(n_tiles, -1, wm.shape[0])
+
 
 class Mlp(nn.Module):
     """layers = Sequential(fc1, GELU, fc2); the reference's wrapper swaps the GELU to the tanh
@@ -164,6 +172,11 @@ class FinalLayer(nn.Module):
     def forward_bf16(self, tokens: torch.Tensor) -> torch.Tensor:
         """bf16 tokens [..., dim] -> fp32 [..., out_features] through the library's LayerNorm
         and GEMM kernels (output rows padded to a multiple of 8 columns for the store)."""
+        lead = tokens.shape[:-1]
+        y, N = self.matrix_bf16(tokens)
+        return y[:, :N].float().view(*lead, N)
+
+    def _refresh(self) -> None:
         key = tuple((p.data_ptr(), p._version, p.device) for p in self.linear.parameters())
         if self._gemm_cache is None or key != self._gemm_key:
             w = self.linear.weight.detach()
@@ -176,10 +189,13 @@ class FinalLayer(nn.Module):
                 b = torch.zeros(Np, dtype=torch.float32, device=w.device)
                 b[:N] = self.linear.bias.detach().float()
             self._gemm_cache, self._gemm_key = (wm, b, N), key
+
+    def matrix_bf16(self, tokens: torch.Tensor):
+        """bf16 tokens [..., dim] -> (bf16 [rows, Np], N): the layer's output rows, N valid
+        columns of a row stride padded to a multiple of 8."""
+        self._refresh()
         wm, b, N = self._gemm_cache
-        lead = tokens.shape[:-1]
-        y = ops.linear(ops.layernorm(tokens.reshape(-1, tokens.shape[-1])), wm, b)
-        return y[:, :N].float().view(*lead, N)
+        return ops.linear(ops.layernorm(tokens.reshape(-1, tokens.shape[-1])), wm, b), N
 
 
 class StrataTransformer3D(nn.Module):
@@ -285,6 +301,29 @@ class StrataTransformer3D(nn.Module):
         cos, sin = self.rope_tables(pos, B, grid)
         tokens = self.forward_tokens(tokens, grid, cos, sin)
         return self.unpatchify(self.final_layer.forward_bf16(tokens), grid)
+
+    def fused_path_available(self, x: torch.Tensor) -> bool:
+        """The fused pre/post-processing kernels serve the plain patch embedding on CUDA fp32
+        inputs; anything else (a caller-assigned embed module) goes through `forward`."""
+        return isinstance(self.patch_embed, PatchEmbed3D) and x.is_cuda and x.dtype == torch.float32
+
+    def forward_fused(self, x: torch.Tensor, pos: torch.Tensor | None, *, lat=None, lon=None,
+                      lat0=None, lon0=None, wind=None, concat_lat: bool = False) -> torch.Tensor:
+        """Raw fields in, fields out, with the wrapper's pre- and post-processing inside:
+        x [B, C_raw, D, H, W] fp32 (before wind rotation and latitude channels) ->
+        [B, C_out, D, H, W] fp32 (wind channels rotated back). One kernel gathers, rotates,
+        appends and casts the patch rows, one un-patchifies and rotates back."""
+        B, _, D, H, W = x.shape
+        grid = self.token_grid(D, H, W)
+        _, _, _, Kp = self.patch_embed._gemm_weights()
+        a = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
+                                   patch=self.patch_size, k_pad=Kp)
+        tokens = self.patch_embed.tokens_from_patches(a, B)
+        cos, sin = self.rope_tables(pos, B, grid)
+        tokens = self.forward_tokens(tokens, grid, cos, sin)
+        y, _ = self.final_layer.matrix_bf16(tokens)
+        return ops.postprocess_fields(y, (B, self.out_channels, D, H, W), lat, lon, lat0, lon0,
+                                      wind=wind, patch=self.patch_size)
 
     def unpatchify(self, y: torch.Tensor, grid) -> torch.Tensor:
         B = y.shape[0]

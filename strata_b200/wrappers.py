@@ -281,6 +281,27 @@ class StrataBackboneModel(_StrataModelBase):
         self.strata.rope_length_scale = base * self.strata.patch_size[1]
 
     def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+        if self.strata.fused_path_available(x):
+            return self._forward_fused(x, index)
         x, pos, lat_lon_data = self._preprocess(x, index)
         x = self.strata(x, pos=pos)
         return self._postprocess(x, lat_lon_data)
+
+    def _forward_fused(self, x: torch.Tensor, index) -> torch.Tensor:
+        """Same result as _preprocess -> strata -> _postprocess, with the wind rotation, the
+        latitude channels and the patch gathering done by one kernel on the way in and the
+        un-patchify and inverse rotation by one kernel on the way out."""
+        B = x.shape[0]
+        lat, lon = self.geometry.lat_lon_from_index(index)
+        if lat.shape[0] != B:
+            lat = lat.expand(B, -1, -1)
+            lon = lon.expand(B, -1, -1)
+        lat = lat.to(device=x.device, dtype=torch.float32).contiguous()
+        lon = lon.to(device=x.device, dtype=torch.float32).contiguous()
+        lat0 = lon0 = wind = None
+        if self._do_rotate_wind:
+            lat0, lon0 = TileGeometry.tile_center(lat, lon)
+            wind = self._wind_channel_indices
+        pos = torch.stack([lat, lon], dim=1)
+        return self.strata.forward_fused(x, pos, lat=lat, lon=lon, lat0=lat0, lon0=lon0, wind=wind,
+                                         concat_lat=self._do_concat_latitude)
