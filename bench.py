@@ -250,11 +250,13 @@ def run_gpu_arm(args):
     tokens_job = M * world
     value = tokens_job / (ms_step * 1e-3)
 
-    # end to end: host buffers in, host buffers out, through the same C-ABI call
+    # end to end: pinned host buffers in, pinned host buffers out, through the public host API
+    # (copies and compute pipelined over chunks of tiles, the same C-ABI block call inside)
+    from strata_b200.host_pipeline import HostBlockPipeline
+    pipe = HostBlockPipeline(T, C, hidden, device=dev, chunk_tiles=1)
+
     def e2e_step():
-        x.copy_(x_host, non_blocking=True)
-        step(x, y)
-        y_host.copy_(y, non_blocking=True)
+        pipe.run(x_host, y_host, weights, grid=(D, H, W), num_heads=heads, kernel=kernel, rope_cs=cs)
     for _ in range(2):
         e2e_step()
     e2e_steps = max(2, min(args.steps, 10))

@@ -151,6 +151,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr bool HAS_AUX = (EPI == EPI_RESIDUAL || EPI == EPI_GATE);
+  // Epilogues without an operand to prefetch wait for the staging box as late as possible (the
+  // QKV epilogue keeps the early wait: it has no registers to spare for the longer live ranges).
+  constexpr bool LATE_WAIT = (EPI == EPI_BIAS || EPI == EPI_GELU);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -318,14 +321,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (n0 + lane < p.N) b_lane[0] = __ldg(p.bias + n0 + lane);
           if (n0 + 32 + lane < p.N) b_lane[1] = __ldg(p.bias + n0 + 32 + lane);
         }
-        if (chunk_live) {
-          // staging box free again? (previous TMA store has finished reading it)
-          if (lane == 0) tma_store_wait_read0();
-          __syncwarp();
-          if constexpr (HAS_AUX) {
-            if (lane == 0) {
-              mbar_expect_tx(aux_bar(e), S::STAGING_BYTES);
-              tma_load_2d(stage_s, &tmAux, n0, m_warp, aux_bar(e));
+        if constexpr (!LATE_WAIT) {
+          if (chunk_live) {
+            // staging box free again? (previous TMA store has finished reading it) - a
+            // residual / gated operand is fetched into it right away
+            if (lane == 0) tma_store_wait_read0();
+            __syncwarp();
+            if constexpr (HAS_AUX) {
+              if (lane == 0) {
+                mbar_expect_tx(aux_bar(e), S::STAGING_BYTES);
+                tma_load_2d(stage_s, &tmAux, n0, m_warp, aux_bar(e));
+              }
             }
           }
         }
@@ -411,6 +417,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               gemm_epilogue_32<EPI, 16>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
             else
               gemm_epilogue_32<EPI, 0>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
+            if constexpr (LATE_WAIT) {
+              if (hh == 0) {
+                // the previous chunk's TMA store must have finished reading the staging box
+                // before it is overwritten; waiting only now lets that drain overlap with the
+                // TMEM load and the arithmetic above
+                if (lane == 0) tma_store_wait_read0();
+                __syncwarp();
+              }
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);

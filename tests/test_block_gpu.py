@@ -215,3 +215,31 @@ def test_block_forward_in_place_and_workspace_check(ops):
     with pytest.raises(ValueError):
         ops.block_forward(x, w, grid=grid, num_heads=heads, kernel=(1, 3, 3), rope_cos=None,
                           rope_sin=None, workspace=torch.empty(1024, dtype=torch.uint8, device="cuda"))
+
+
+def test_host_pipeline_matches_device_call(ops):
+    # pinned host tensors in and out, copies pipelined with compute over chunks of tiles: the
+    # result is bit-identical to one device-side call over all tiles
+    from strata_b200.host_pipeline import HostBlockPipeline
+    C, heads, grid, kernel, n_tiles = 128, 2, (2, 16, 16), (1, 5, 5), 5
+    D, H, W = grid
+    p = bo.init_block_params(C, seed=6)
+    w = device_block_weights(p, "cuda")
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(n_tiles, D * H * W, C, generator=g).bfloat16()
+    lat, lon = tile_latlon(n_tiles, H, W)
+    cos, sin = bo.stereographic_rope_tables(lat, lon, C // heads, 1, bo.default_rope_length_scale(1))
+    from strata_b200 import rope
+    cs = rope.pack_rope_tables(cos.cuda(), sin.cuda())
+    want = ops.block_forward(x.cuda(), w, grid=grid, num_heads=heads, kernel=kernel, rope_cos=None,
+                             rope_sin=None, rope_cs=cs)
+    x_host, y_host = x.pin_memory(), torch.empty_like(x).pin_memory()
+    for chunk in (1, 2):
+        pipe = HostBlockPipeline(D * H * W, C, 4 * C, chunk_tiles=chunk, ring=2)
+        y_host.zero_()
+        pipe.run(x_host, y_host, w, grid=grid, num_heads=heads, kernel=kernel, rope_cs=cs)
+        torch.cuda.synchronize()
+        assert torch.equal(y_host, want.cpu())
+    assert _status() == 0
+    with pytest.raises(TypeError):
+        pipe.run(x, y_host, w, grid=grid, num_heads=heads, kernel=kernel)   # not pinned
