@@ -228,6 +228,11 @@ def run_gpu_arm(args):
             ms = float(t.item())
         return ms
 
+    if args.only == "halo_kernels":
+        res = halo_kernels_bench(torch, dev, iters=args.steps)
+        if rank == 0:
+            print(json.dumps({"only": args.only, "result": res}))
+        return
     if args.only:
         # profiling aid: run one kernel of the block alone on the bench workload
         res = kernel_breakdown(torch, ops, x, weights, cs, (D, H, W), heads, kernel, hidden,
@@ -470,6 +475,73 @@ def na3d_sweep(torch, ops, iters=3):
         return {"shape": list(shape), "results": res}
     except Exception as exc:
         return {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def halo_kernels_bench(torch, dev, iters=5):
+    """Times the memory-bound kernels around the block on one GPU (all sources local): field and
+    token halo gathers, the per-block K/V halo gather, the overlap-add un-pad and the fused
+    pre-/post-processing, each with its algorithmic bytes (payload read once + written once) and
+    the fraction of the measured copy bandwidth. Sizes (kept to a few GB so that the same
+    command can run under ncu): 24 tiles of 64x64 cells with a halo of 8, 8 levels, 768 channels
+    in token space, 64 field channels."""
+    import ctypes
+    import numpy as np
+    from strata_b200 import _lib, ops
+    from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window
+    from strata_b200.halo_block import TiledBlockRunner
+    from strata_b200.rollout import equiangular_cubed_sphere_latlon
+    from strata_b200.topology import TileTopology
+    _, hbm_peak, _ = measured_peaks()
+    face, T, h, D, C, CF = 128, 64, 8, 8, 768, 64
+    topo = TileTopology(1, 0, face, T, h)
+    P, tpr = topo.padded_tile_size, topo.tiles_per_rank
+    pad = DistributedTileCopyHaloPadding(topology=topo, device=dev)
+    unpad = NormalizedCopyHaloAdjoint(pad, window=kbd_window(P))
+    fields = torch.randn(CF, D, tpr, T, T, device=dev)
+    padded = pad(fields)
+    lat, lon = equiangular_cubed_sphere_latlon(face)
+    full = TileTopology(1, 0, face, T, 0)
+    cut = lambda g: np.stack([g[f, i * T:(i + 1) * T, j * T:(j + 1) * T] for f, i, j in full.global_tiles])
+    run = TiledBlockRunner(topo, depth=D, dim=C, num_heads=C // 64, kernel=(5, 13, 13),
+                           lat_deg=cut(lat), lon_deg=cut(lon),
+                           rope_length_scale=float(np.radians(90.0 / face)), device=dev)
+    qkv, ptrs = run._slot(1)
+    x5 = torch.randn(tpr, 13, D, P, P, device=dev)
+    latp = torch.rand(tpr, P, P, device=dev)
+    lat0 = torch.rand(tpr, device=dev)
+    a_mat = ops.preprocess_patches(x5, latp, latp, lat0, lat0, wind=(0, 1), concat_lat=True)
+    ymat = torch.randn(tpr * D * P * P, 16, device=dev).bfloat16()
+
+    def exchange():
+        run._epoch += 1
+        run._exchange(qkv, ptrs)
+    halo_cells = tpr * D * (P * P - T * T)
+    items = [
+        ("halo_gather_fields", lambda: pad(fields), fields.numel() * 4 + padded.numel() * 4),
+        ("halo_adjoint_fields", lambda: unpad(padded), fields.numel() * 4 + padded.numel() * 4),
+        ("halo_gather_kv", exchange, halo_cells * 2 * C * 2 * 2),
+        ("preprocess_patches", lambda: ops.preprocess_patches(x5, latp, latp, lat0, lat0, wind=(0, 1),
+                                                              concat_lat=True),
+         x5.numel() * 4 + a_mat.numel() * 2),
+        ("postprocess_fields", lambda: ops.postprocess_fields(ymat, (tpr, 13, D, P, P), latp, latp,
+                                                              lat0, lat0, wind=(0, 1)),
+         ymat.shape[0] * 13 * 2 + tpr * 13 * D * P * P * 4),
+    ]
+    out = []
+    for name, fn, nbytes in items:
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        out.append({"name": name, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                    "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm_peak})
+    run.close()
+    return out
 
 
 def kernel_breakdown(torch, ops, x, weights, cs, grid, heads, kernel, hidden, iters=5,

@@ -101,13 +101,27 @@ preprocess_patches_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict
           vr += vt * q0.n[i];
         }
       }
-      for (int c = 0; c < p.C; ++c) {
-        float val;
-        if (rot && c == p.u_idx) val = ur;
-        else if (rot && c == p.v_idx) val = vr;
-        else val = __ldg(xb + (static_cast<long long>(c) * p.D + d) * plane);
-        ar[c * pvol] = __float2bfloat16(val);
+      auto channel = [&](int c) -> float {
+        if (c >= c_all) return 0.f;                      // padding column
+        if (c >= p.C) return c == p.C ? cl : sl;         // latitude channels
+        if (rot && c == p.u_idx) return ur;
+        if (rot && c == p.v_idx) return vr;
+        return __ldg(xb + (static_cast<long long>(c) * p.D + d) * plane);
+      };
+      if (pvol == 1 && (p.ld & 7) == 0) {
+        // one pixel = one token: the whole row (padding included) goes out in 16-byte stores
+        uint4* ar4 = reinterpret_cast<uint4*>(a + row * p.ld);
+        for (int c8 = 0; c8 < p.ld; c8 += 8) {
+          uint4 o;
+          o.x = pack_bf16(channel(c8), channel(c8 + 1));
+          o.y = pack_bf16(channel(c8 + 2), channel(c8 + 3));
+          o.z = pack_bf16(channel(c8 + 4), channel(c8 + 5));
+          o.w = pack_bf16(channel(c8 + 6), channel(c8 + 7));
+          ar4[c8 >> 3] = o;
+        }
+        continue;
       }
+      for (int c = 0; c < p.C; ++c) ar[c * pvol] = __float2bfloat16(channel(c));
       if (p.concat_lat) {
         ar[p.C * pvol] = __float2bfloat16(cl);
         ar[(p.C + 1) * pvol] = __float2bfloat16(sl);
