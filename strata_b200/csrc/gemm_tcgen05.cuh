@@ -107,10 +107,10 @@ __device__ __forceinline__ void tma_store_wait_all() {
 // columns (bf16 pairs) for the epilogues that use one; `qk_scale` is the RMS-norm factor of the
 // head these columns belong to (1 when qk norm is off).
 // cs: this row's (cos, sin) half pairs for the 16 channel pairs of these 32 columns.
-template <int EPI, int CS_OFF>
+template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, float b_lane,
                                                  const uint32_t (&aux)[16], float qk_scale,
-                                                 const uint32_t (&cs)[32], const GemmParams& p) {
+                                                 const uint32_t (&cs)[16], const GemmParams& p) {
   if (p.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, j);
@@ -135,7 +135,7 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 t =
-            __half22float2(*reinterpret_cast<const __half2*>(&cs[CS_OFF + j]));  // (cos, sin)
+            __half22float2(*reinterpret_cast<const __half2*>(&cs[j]));  // (cos, sin)
         const float a = v[2 * j] * qk_scale, b = v[2 * j + 1] * qk_scale;
         v[2 * j] = a * t.x - b * t.y;
         v[2 * j + 1] = a * t.y + b * t.x;
@@ -151,9 +151,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr bool HAS_AUX = (EPI == EPI_RESIDUAL || EPI == EPI_GATE);
-  // Epilogues without an operand to prefetch wait for the staging box as late as possible (the
-  // QKV epilogue keeps the early wait: it has no registers to spare for the longer live ranges).
-  constexpr bool LATE_WAIT = (EPI == EPI_BIAS || EPI == EPI_GELU);
+  // Epilogues without an operand to prefetch wait for the staging box as late as possible.
+  constexpr bool LATE_WAIT = (EPI == EPI_BIAS || EPI == EPI_GELU || EPI == EPI_QKV_ROPE);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -291,9 +290,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = m < p.M;
       const int n_warp0 = n_tile0 + col_half * HALF_COLS;
       // EPI_QKV_ROPE: this row's rotation table (one 4-byte (cos, sin) pair per channel pair of
-      // a head) is the same for every q / k head, so it is fetched once per tile - before the
-      // accumulator is waited for, which hides the load latency.
-      uint32_t cs[32];
+      // a head: a single 128-byte line for head_dim 64) is the same for every q / k head. It is
+      // pulled into L1 here, before the accumulator is waited for, and read 64 bytes at a time
+      // where a 32-column group needs it - holding it in registers for the whole tile costs
+      // more (spills) than the L1 hits.
+      const uint4* cs_src = nullptr;
       bool rope_tile = false;
       if constexpr (EPI == EPI_QKV_ROPE) {
         rope_tile = (p.rope_cs != nullptr) && (n_warp0 < p.rope_cols) && row_ok;
@@ -301,14 +302,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int half = p.head_dim >> 1;
           const long long trow =
               static_cast<long long>(m / p.tokens_per_tile) * p.hw + (m % p.hw);
-          const uint4* src = reinterpret_cast<const uint4*>(p.rope_cs + trow * half);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (q * 4 < half) {
-              const uint4 t = __ldg(src + q);
-              cs[4 * q] = t.x; cs[4 * q + 1] = t.y; cs[4 * q + 2] = t.z; cs[4 * q + 3] = t.w;
-            }
-          }
+          cs_src = reinterpret_cast<const uint4*>(p.rope_cs + trow * half);
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(cs_src));
         }
       }
       bool acc_ready = false;
@@ -413,10 +408,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // head_dim 64: the two halves of a chunk use table pairs [0,16) and [16,32);
             // head_dim 32: each half is a whole head and uses pairs [0,16)
             const bool rotate = rope_tile && (n0 < p.rope_cols);
-            if (hh == 1 && p.head_dim == 64)
-              gemm_epilogue_32<EPI, 16>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
-            else
-              gemm_epilogue_32<EPI, 0>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
+            uint32_t cs[16];
+            if constexpr (EPI == EPI_QKV_ROPE) {
+              if (rotate) {
+                const uint4* src = cs_src + ((hh == 1 && p.head_dim == 64) ? 4 : 0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 t = __ldg(src + q);
+                  cs[4 * q] = t.x; cs[4 * q + 1] = t.y; cs[4 * q + 2] = t.z; cs[4 * q + 3] = t.w;
+                }
+              }
+            }
+            gemm_epilogue_32<EPI>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
             if constexpr (LATE_WAIT) {
               if (hh == 0) {
                 // the previous chunk's TMA store must have finished reading the staging box
