@@ -116,8 +116,19 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
     for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, j);
   }
   if constexpr (EPI == EPI_GELU) {
+    // tanh GELU on pairs: the polynomial part runs on packed fp32x2 instructions
+    const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+    const uint64_t K0 = pack2(k0, k0), K01 = pack2(k01, k01), HALF = pack2(0.5f, 0.5f);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+    for (int j = 0; j < 16; ++j) {
+      const uint64_t x = pack2(v[2 * j], v[2 * j + 1]);
+      const uint64_t u = fmul2(x, ffma2(fmul2(x, x), K01, K0));
+      float u0, u1;
+      unpack2(u, u0, u1);
+      const uint64_t t = pack2(fast_tanh(u0), fast_tanh(u1));
+      const uint64_t hx = fmul2(x, HALF);
+      unpack2(ffma2(hx, t, hx), v[2 * j], v[2 * j + 1]);
+    }
   } else if constexpr (EPI == EPI_RESIDUAL) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -132,11 +143,15 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
     }
   } else if constexpr (EPI == EPI_QKV_ROPE) {
     if (rotate) {
+      if (p.qk_norm) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= qk_scale;
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 t =
             __half22float2(*reinterpret_cast<const __half2*>(&cs[j]));  // (cos, sin)
-        const float a = v[2 * j] * qk_scale, b = v[2 * j + 1] * qk_scale;
+        const float a = v[2 * j], b = v[2 * j + 1];
         v[2 * j] = a * t.x - b * t.y;
         v[2 * j + 1] = a * t.y + b * t.x;
       }
