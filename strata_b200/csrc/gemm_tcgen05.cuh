@@ -10,6 +10,15 @@
 //               one output row), apply bias and the selected epilogue, store bf16. The
 //               other accumulator is being filled meanwhile.
 //
+// PAIR variant (large problems): two CTAs of a cluster share every MMA (tcgen05 cta_group::2,
+// M = 256): each CTA loads its own 128 rows of A and HALF of the W tile, the instruction reads
+// both halves, and each CTA's tensor memory receives its 128 rows x BN accumulator. A CTA then
+// moves 32 KB per k-block through shared memory instead of 48 KB, which matters because the
+// one-CTA mainloop is bound by shared-memory bandwidth (operand reads + TMA writes), not by the
+// tensor pipe. The first CTA of the pair issues the MMAs; TMA loads of both CTAs signal its
+// stage barriers, its commits arrive on both CTAs' barriers, and both CTAs' epilogue warps hand
+// the accumulator back on its barrier. Everything else (epilogues, staging, stores) is per CTA.
+//
 // Epilogues (the operator each one serves in the Strata block):
 //   EPI_BIAS           y = acc + b                                   (generic Linear)
 //   EPI_GELU           y = gelu_tanh(acc + b)                        (mlp.layers.0 + tanh GELU)
@@ -67,17 +76,21 @@ __device__ __forceinline__ int gemm_out_row(int m, const GemmParams& p) {
   return (t * P + i + p.pad_h) * P + j + p.pad_h;
 }
 
+#ifndef GEMM_USE_PAIRS
+#define GEMM_USE_PAIRS 0
+#endif
+
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 320;
 constexpr int GEMM_EPI_WARPS = 8;
 
-template <int BN>
+template <int BN, bool PAIR = false>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * GEMM_BK * 2;   // a pair splits the W tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256 && !PAIR) ? 4 : 6;
   static constexpr int STAGING_BYTES = 32 * 64 * 2;             // one 32-row x 64-col bf16 box
   static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;      // per epilogue warp
   static constexpr int BAR_OFF = STAGING_OFF + GEMM_EPI_WARPS * STAGING_BYTES;
@@ -159,12 +172,17 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
   }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmOut,
                     const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, PAIR>;
+  // PAIR: this CTA is rank 0 or 1 of a cluster of two that computes 256 x BN tiles together
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int n_units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  constexpr int TILE_M = PAIR ? 2 * GEMM_BM : GEMM_BM;
   constexpr bool HAS_AUX = (EPI == EPI_RESIDUAL || EPI == EPI_GATE);
   // Epilogues without an operand to prefetch wait for the staging box as late as possible.
   constexpr bool LATE_WAIT = (EPI == EPI_BIAS || EPI == EPI_GELU || EPI == EPI_QKV_ROPE);
@@ -186,7 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
@@ -198,7 +216,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(accf_bar(b), 1);
-      mbar_init(acce_bar(b), GEMM_EPI_WARPS);
+      mbar_init(acce_bar(b), PAIR ? 2 * GEMM_EPI_WARPS : GEMM_EPI_WARPS);
     }
     for (int w = 0; w < GEMM_EPI_WARPS; ++w) mbar_init(aux_bar(w), 1);
     *abort_flag = 0;
@@ -210,6 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the partner's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -221,9 +240,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / tiles_n) * GEMM_BM;
-        const int n0 = (t % tiles_n) * BN;
+      for (int t = unit; t < num_tiles && ok; t += n_units) {
+        const int m0 = (t / tiles_n) * TILE_M + static_cast<int>(pair_rank) * GEMM_BM;
+        const int n0 = (t % tiles_n) * BN + (PAIR ? static_cast<int>(pair_rank) * (BN / 2) : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -231,9 +250,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_dst = a_dst + S::A_BYTES;
-          mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmA, kb * GEMM_BK, m0, full_bar(stage));
-          tma_load_2d(b_dst, &tmB, kb * GEMM_BK, n0, full_bar(stage));
+          if constexpr (PAIR) {
+            // both CTAs' loads complete on the FIRST CTA's stage barrier (it issues the MMAs);
+            // that CTA's producer announces the bytes of both (a transaction count may run
+            // ahead of its announcement within a phase)
+            const uint32_t fb = map_to_cta(full_bar(stage), 0);
+            if (pair_rank == 0) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmA, kb * GEMM_BK, m0, fb);
+            tma_load_2d_pair(b_dst, &tmB, kb * GEMM_BK, n0, fb);
+          } else {
+            mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmA, kb * GEMM_BK, m0, full_bar(stage));
+            tma_load_2d(b_dst, &tmB, kb * GEMM_BK, n0, full_bar(stage));
+          }
           if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -245,13 +274,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, BN, false, false);
+    if (lane == 0 && pair_rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, false, false);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = unit; t < num_tiles && ok; t += n_units, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) break;
@@ -270,12 +299,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k) {
             // advance 16 bf16 = 32 bytes along K inside the 128-byte swizzle span
-            umma_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (PAIR)
+              umma_ss_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));
+          if constexpr (PAIR) umma_commit_pair(empty_bar(stage)); else umma_commit(empty_bar(stage));
           if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(accf_bar(buf));
+        if (ok) {
+          if constexpr (PAIR) umma_commit_pair(accf_bar(buf)); else umma_commit(accf_bar(buf));
+        }
       }
     }
   } else {
@@ -295,10 +329,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t aux_phase = 0;
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    const uint32_t acce_remote0 = PAIR ? map_to_cta(acce_bar(0), 0) : 0u;
+    const uint32_t acce_remote1 = PAIR ? map_to_cta(acce_bar(1), 0) : 0u;
+    for (int t = unit; t < num_tiles && ok; t += n_units, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      const int m0 = (t / tiles_n) * GEMM_BM;
+      const int m0 = (t / tiles_n) * TILE_M + static_cast<int>(pair_rank) * GEMM_BM;
       const int n_tile0 = (t % tiles_n) * BN;
       const int m_warp = m0 + quarter * 32;
       const int m = m_warp + lane;
@@ -402,7 +438,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // the accumulator is in registers (or not needed): hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acce_bar(buf));
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(buf ? acce_remote1 : acce_remote0);
+              else mbar_arrive(acce_bar(buf));
+            }
           }
           if (chunk_live) {
             float v[32];
@@ -470,6 +509,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // no signal may reach a CTA that has already left
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -479,7 +519,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // Host launcher. A: [M,K] bf16 row-major with row stride lda (elements); W: [N,K] bf16
 // row-major with row stride ldw. Returns 0, or a negative argument error / CUDA error code.
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* W,
                          long long ldw, const GemmParams& p, int sm_count, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
@@ -492,7 +532,7 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
   {
     uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N)};
     uint64_t str[1] = {static_cast<uint64_t>(ldw) * 2};
-    uint32_t box[2] = {GEMM_BK, static_cast<uint32_t>(BN)};
+    uint32_t box[2] = {GEMM_BK, static_cast<uint32_t>(PAIR ? BN / 2 : BN)};
     if (make_tmap_bf16(&tmB, W, 2, dims, str, box) != 0) return -21;
   }
   CUtensorMap tmOut, tmAux;
@@ -512,13 +552,43 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
       if (make_tmap_bf16(&tmAux, p.aux, 2, dims, astr, box) != 0) return -23;
     }
   }
-  using S = GemmSmem<BN>;
-  auto kern = gemm_tcgen05_kernel<BN, EPI>;
+  using S = GemmSmem<BN, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, EPI, PAIR>;
   {
     // Per-device attribute; setting it on every launch keeps the launcher stateless.
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+  }
+  if constexpr (PAIR) {
+    const int tiles = ((p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((p.N + BN - 1) / BN);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // A persistent grid must be resident at once: not every SM has a partner for a pair, so the
+    // number of clusters that fit is asked for (once per kernel and device), not assumed.
+    static int max_clusters[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return -24;
+    if (max_clusters[dev] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) return -24;
+      max_clusters[dev] = n;
+    }
+    const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, tmAux, p);
+    return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
   }
   const int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
@@ -531,8 +601,12 @@ template <int EPI>
 inline int launch_gemm(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* W, long long ldw,
                        const GemmParams& p, int sm_count, cudaStream_t stream) {
   // 128x256 tiles when the output is wide enough to fill the machine with them.
-  if (p.N >= 256 && (p.N % 256 == 0 || p.N > 512))
+  if (p.N >= 256 && (p.N % 256 == 0 || p.N > 512)) {
+    // large problems: CTA pairs share each MMA (less shared-memory traffic per SM)
+    if (GEMM_USE_PAIRS && p.M >= 1024)
+      return launch_gemm_t<256, EPI, true>(A, lda, W, ldw, p, sm_count, stream);
     return launch_gemm_t<256, EPI>(A, lda, W, ldw, p, sm_count, stream);
+  }
   return launch_gemm_t<128, EPI>(A, lda, W, ldw, p, sm_count, stream);
 }
 
