@@ -6,9 +6,11 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) from the smem
 //               stages into one of two TMEM accumulators (2 x BN fp32 columns), and commits
 //               stage-free / accumulator-full mbarriers.
-//   warps 2-9   epilogue: read the finished accumulator with tcgen05.ld (each thread owns
-//               one output row), apply bias and the selected epilogue, store bf16. The
-//               other accumulator is being filled meanwhile.
+//   warps 2-17  epilogue (16 warps: four per SM sub-partition, because the epilogue of a
+//               128 x 256 tile is bound by the latency of each warp's instruction stream
+//               rather than by issue slots): read the finished accumulator with tcgen05.ld
+//               (each thread owns one output row, 16 columns at a time), apply bias and the
+//               selected epilogue, store bf16. The other accumulator is being filled meanwhile.
 //
 // PAIR variant (large problems): two CTAs of a cluster share every MMA (tcgen05 cta_group::2,
 // M = 256): each CTA loads its own 128 rows of A and HALF of the W tile, the instruction reads
@@ -77,13 +79,13 @@ __device__ __forceinline__ int gemm_out_row(int m, const GemmParams& p) {
 }
 
 #ifndef GEMM_USE_PAIRS
-#define GEMM_USE_PAIRS 0
+#define GEMM_USE_PAIRS 1
 #endif
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 320;
-constexpr int GEMM_EPI_WARPS = 8;
+constexpr int GEMM_EPI_WARPS = 16;
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
 template <int BN, bool PAIR = false>
 struct GemmSmem {
@@ -91,10 +93,10 @@ struct GemmSmem {
   static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * GEMM_BK * 2;   // a pair splits the W tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256 && !PAIR) ? 4 : 6;
-  static constexpr int STAGING_BYTES = 32 * 64 * 2;             // one 32-row x 64-col bf16 box
+  static constexpr int STAGING_BYTES = 32 * 32 * 2;             // one 32-row x 32-col bf16 box
   static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;      // per epilogue warp
   static constexpr int BAR_OFF = STAGING_OFF + GEMM_EPI_WARPS * STAGING_BYTES;
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int BAR_BYTES = 512;
   static constexpr int TOTAL = BAR_OFF + BAR_BYTES + 1024;      // + alignment slack
 };
 
@@ -115,25 +117,26 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
-// Epilogue math on 32 consecutive columns [n0, n0+32) of output row m, in place. Lane l of
-// the warp holds the bias of column n0+l; `aux` holds the residual / gated operand of the same
-// columns (bf16 pairs) for the epilogues that use one; `qk_scale` is the RMS-norm factor of the
-// head these columns belong to (1 when qk norm is off).
-// cs: this row's (cos, sin) half pairs for the 16 channel pairs of these 32 columns.
+// Epilogue math on 16 consecutive columns of output row m, in place. Lane `src_lane0 + j` of
+// the warp holds the bias of column j of the group; `aux` holds the residual / gated operand of
+// the same columns (bf16 pairs) for the epilogues that use one; `qk_scale` is the RMS-norm
+// factor of the head these columns belong to; cs: this row's (cos, sin) half pairs for the 8
+// channel pairs of these 16 columns.
 template <int EPI>
-__device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, float b_lane,
-                                                 const uint32_t (&aux)[16], float qk_scale,
-                                                 const uint32_t (&cs)[16], const GemmParams& p) {
+__device__ __forceinline__ void gemm_epilogue_16(float (&v)[16], bool rotate, float b_lane,
+                                                 int src_lane0, const uint32_t (&aux)[8],
+                                                 float qk_scale, const uint32_t (&cs)[8],
+                                                 const GemmParams& p) {
   if (p.bias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, j);
+    for (int j = 0; j < 16; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, src_lane0 + j);
   }
   if constexpr (EPI == EPI_GELU) {
     // tanh GELU on pairs: the polynomial part runs on packed fp32x2 instructions
     const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
     const uint64_t K0 = pack2(k0, k0), K01 = pack2(k01, k01), HALF = pack2(0.5f, 0.5f);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < 8; ++j) {
       const uint64_t x = pack2(v[2 * j], v[2 * j + 1]);
       const uint64_t u = fmul2(x, ffma2(fmul2(x, x), K01, K0));
       float u0, u1;
@@ -144,13 +147,13 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
     }
   } else if constexpr (EPI == EPI_RESIDUAL) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < 8; ++j) {
       v[2 * j] += bf16_lo(aux[j]);
       v[2 * j + 1] += bf16_hi(aux[j]);
     }
   } else if constexpr (EPI == EPI_GATE) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < 8; ++j) {
       v[2 * j] = bf16_lo(aux[j]) / (1.0f + __expf(-v[2 * j]));
       v[2 * j + 1] = bf16_hi(aux[j]) / (1.0f + __expf(-v[2 * j + 1]));
     }
@@ -158,10 +161,10 @@ __device__ __forceinline__ void gemm_epilogue_32(float (&v)[32], bool rotate, fl
     if (rotate) {
       if (p.qk_norm) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] *= qk_scale;
+        for (int j = 0; j < 16; ++j) v[j] *= qk_scale;
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 8; ++j) {
         const float2 t =
             __half22float2(*reinterpret_cast<const __half2*>(&cs[j]));  // (cos, sin)
         const float a = v[2 * j], b = v[2 * j + 1];
@@ -314,23 +317,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    // Each warp owns 32 output rows (its TMEM lane quarter) x BN/2 columns of the tile and
-    // walks them in 64-column chunks: TMEM -> registers -> math -> 128-byte-swizzled staging
-    // box in shared memory -> TMA store (clipped at the matrix edge by the tensor map). The
-    // residual / gated operand of a chunk is TMA-loaded into the same staging box beforehand.
+    // Each warp owns 32 output rows (its TMEM lane quarter) x BN/4 columns of the tile and
+    // walks them in 32-column sub-chunks of two 16-column groups: TMEM -> registers -> math ->
+    // 64-byte-swizzled staging box (32 rows x 32 columns) in shared memory -> TMA store
+    // (clipped at the matrix edge by the tensor map). The residual / gated operand of a
+    // sub-chunk is TMA-loaded into the same staging box beforehand.
     const int e = warp - 2;
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
-    const int col_half = e >> 2;             // which half of the BN columns
-    constexpr int HALF_COLS = BN / 2;
-    constexpr int NCHUNK = HALF_COLS / 64;
+    const int cg = e >> 2;                   // which quarter of the BN columns
+    constexpr int WARP_COLS = BN / 4;
+    constexpr int NSUB = WARP_COLS / 32;
     const uint32_t stage_s = smem_base + S::STAGING_OFF + e * S::STAGING_BYTES;
-    const uint32_t my_row_s = stage_s + lane * 128;
-    const uint32_t sw = static_cast<uint32_t>(lane & 7);
+    const uint32_t my_row_s = stage_s + lane * 64;
+    const uint32_t sw = static_cast<uint32_t>((lane >> 1) & 3);   // 64-byte swizzle of this row
+    const uint32_t acce_remote0 = PAIR ? map_to_cta(acce_bar(0), 0) : 0u;
+    const uint32_t acce_remote1 = PAIR ? map_to_cta(acce_bar(1), 0) : 0u;
     uint32_t aux_phase = 0;
     int it = 0;
     bool ok = true;
-    const uint32_t acce_remote0 = PAIR ? map_to_cta(acce_bar(0), 0) : 0u;
-    const uint32_t acce_remote1 = PAIR ? map_to_cta(acce_bar(1), 0) : 0u;
     for (int t = unit; t < num_tiles && ok; t += n_units, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
@@ -339,12 +343,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m_warp = m0 + quarter * 32;
       const int m = m_warp + lane;
       const bool row_ok = m < p.M;
-      const int n_warp0 = n_tile0 + col_half * HALF_COLS;
+      const int n_warp0 = n_tile0 + cg * WARP_COLS;
       // EPI_QKV_ROPE: this row's rotation table (one 4-byte (cos, sin) pair per channel pair of
       // a head: a single 128-byte line for head_dim 64) is the same for every q / k head. It is
-      // pulled into L1 here, before the accumulator is waited for, and read 64 bytes at a time
-      // where a 32-column group needs it - holding it in registers for the whole tile costs
-      // more (spills) than the L1 hits.
+      // pulled into L1 here, before the accumulator is waited for, and read 32 bytes at a time
+      // where a 16-column group needs it.
       const uint4* cs_src = nullptr;
       bool rope_tile = false;
       if constexpr (EPI == EPI_QKV_ROPE) {
@@ -358,15 +361,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       bool acc_ready = false;
+      // per-head RMS factor (qk norm): one extra pass over the head's 64 (or 32) accumulator
+      // columns; with 64-wide heads the warp's 64 columns are exactly one head
+      float qk_scale[NSUB];
+#pragma unroll
+      for (int c = 0; c < NSUB; ++c) qk_scale[c] = 1.f;
 #pragma unroll 1
-      for (int c = 0; c < NCHUNK; ++c) {
-        const int n0 = n_warp0 + c * 64;
+      for (int c = 0; c < NSUB; ++c) {
+        const int n0 = n_warp0 + c * 32;
         const bool chunk_live = (n0 < p.N) && (m_warp < p.M);   // warp-uniform
-        float b_lane[2] = {0.f, 0.f};
-        if (p.bias != nullptr) {
-          if (n0 + lane < p.N) b_lane[0] = __ldg(p.bias + n0 + lane);
-          if (n0 + 32 + lane < p.N) b_lane[1] = __ldg(p.bias + n0 + 32 + lane);
-        }
+        float b_lane = 0.f;
+        if (p.bias != nullptr && n0 + lane < p.N) b_lane = __ldg(p.bias + n0 + lane);
         if constexpr (!LATE_WAIT) {
           if (chunk_live) {
             // staging box free again? (previous TMA store has finished reading it) - a
@@ -390,31 +395,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           acc_ready = true;
         }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                               static_cast<uint32_t>(buf * BN + col_half * HALF_COLS + c * 64);
-        float qk_scale[2] = {1.f, 1.f};
+                               static_cast<uint32_t>(buf * BN + cg * WARP_COLS + c * 32);
         if constexpr (EPI == EPI_QKV_ROPE) {
-          // per-head RMS factor needs the whole head: one extra pass over the accumulator
-          if (chunk_live && p.qk_norm && n0 < p.rope_cols) {
-            float ss[2];
+          if (c == 0 && p.qk_norm && m_warp < p.M && n_warp0 < p.rope_cols && n_warp0 < p.N) {
+            float ss[NSUB];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              uint32_t r[32];
-              tmem_ld_32x32(taddr + 32 * hh, r);
-              tmem_ld_wait();
+            for (int cc = 0; cc < NSUB; ++cc) {
               float acc = 0.f;
+              float bl = 0.f;
+              if (p.bias != nullptr && n_warp0 + 32 * cc + lane < p.N)
+                bl = __ldg(p.bias + n_warp0 + 32 * cc + lane);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float x = __uint_as_float(r[j]) +
-                                (p.bias != nullptr ? __shfl_sync(0xffffffffu, b_lane[hh], j) : 0.f);
-                acc += x * x;
+              for (int g = 0; g < 2; ++g) {
+                uint32_t r[16];
+                tmem_ld_32x16(taddr + 32 * cc + 16 * g, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const float x = __uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bl, 16 * g + j);
+                  acc += x * x;
+                }
               }
-              ss[hh] = acc;
+              ss[cc] = acc;
             }
-            if (p.head_dim == 64) {
-              qk_scale[0] = qk_scale[1] = rsqrtf((ss[0] + ss[1]) * (1.0f / 64.0f) + p.qk_eps);
+            if (p.head_dim == 64 && NSUB == 2) {
+              qk_scale[0] = rsqrtf((ss[0] + ss[NSUB - 1]) * (1.0f / 64.0f) + p.qk_eps);
+              qk_scale[NSUB - 1] = qk_scale[0];
             } else {
-              qk_scale[0] = rsqrtf(ss[0] * (1.0f / 32.0f) + p.qk_eps);
-              qk_scale[1] = rsqrtf(ss[1] * (1.0f / 32.0f) + p.qk_eps);
+#pragma unroll
+              for (int cc = 0; cc < NSUB; ++cc)
+                qk_scale[cc] = rsqrtf(ss[cc] * (1.0f / 32.0f) + p.qk_eps);
             }
           }
         }
@@ -428,13 +438,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t r[32];
+        for (int g = 0; g < 2; ++g) {
+          uint32_t r[16];
           if (chunk_live) {
-            tmem_ld_32x32(taddr + 32 * hh, r);
+            tmem_ld_32x16(taddr + 16 * g, r);
             tmem_ld_wait();
           }
-          if (hh == 1 && c == NCHUNK - 1) {
+          if (g == 1 && c == NSUB - 1) {
             // the accumulator is in registers (or not needed): hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -444,14 +454,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           if (chunk_live) {
-            float v[32];
+            float v[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            uint32_t aux[16];
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            uint32_t aux[8];
             if constexpr (HAS_AUX) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);
+              for (int q = 0; q < 2; ++q) {
+                const uint32_t addr = my_row_s + ((static_cast<uint32_t>(2 * g + q) ^ sw) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(aux[4 * q]), "=r"(aux[4 * q + 1]), "=r"(aux[4 * q + 2]),
                                "=r"(aux[4 * q + 3])
@@ -459,33 +469,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                              : "memory");
               }
             }
-            // head_dim 64: the two halves of a chunk use table pairs [0,16) and [16,32);
-            // head_dim 32: each half is a whole head and uses pairs [0,16)
+            // head_dim 64: the 32-column sub-chunks of a head use table pairs [0,16) and
+            // [16,32); head_dim 32: each sub-chunk is a whole head and uses pairs [0,16)
             const bool rotate = rope_tile && (n0 < p.rope_cols);
-            uint32_t cs[16];
+            uint32_t cs[8];
             if constexpr (EPI == EPI_QKV_ROPE) {
               if (rotate) {
-                const uint4* src = cs_src + ((hh == 1 && p.head_dim == 64) ? 4 : 0);
+                const int pair0 = ((p.head_dim == 64) ? (n0 & 63) >> 1 : 0) + 8 * g;
+                const uint4* src = cs_src + (pair0 >> 2);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const uint4 t = __ldg(src + q);
-                  cs[4 * q] = t.x; cs[4 * q + 1] = t.y; cs[4 * q + 2] = t.z; cs[4 * q + 3] = t.w;
+                for (int q = 0; q < 2; ++q) {
+                  const uint4 t4 = __ldg(src + q);
+                  cs[4 * q] = t4.x; cs[4 * q + 1] = t4.y; cs[4 * q + 2] = t4.z; cs[4 * q + 3] = t4.w;
                 }
               }
             }
-            gemm_epilogue_32<EPI>(v, rotate, b_lane[hh], aux, qk_scale[hh], cs, p);
+            gemm_epilogue_16<EPI>(v, rotate, b_lane, 16 * g, aux, qk_scale[c], cs, p);
             if constexpr (LATE_WAIT) {
-              if (hh == 0) {
-                // the previous chunk's TMA store must have finished reading the staging box
-                // before it is overwritten; waiting only now lets that drain overlap with the
-                // TMEM load and the arithmetic above
+              if (g == 0) {
+                // the previous sub-chunk's TMA store must have finished reading the staging
+                // box before it is overwritten; waiting only now lets that drain overlap with
+                // the TMEM load and the arithmetic above
                 if (lane == 0) tma_store_wait_read0();
                 __syncwarp();
               }
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t addr = my_row_s + ((static_cast<uint32_t>(4 * hh + q) ^ sw) << 4);
+            for (int q = 0; q < 2; ++q) {
+              const uint32_t addr = my_row_s + ((static_cast<uint32_t>(2 * g + q) ^ sw) << 4);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                            "r"(pack_bf16(v[8 * q], v[8 * q + 1])),
                            "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])),
@@ -539,17 +550,17 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
   {
     uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M)};
     uint64_t str[1] = {static_cast<uint64_t>(p.ldo) * 2};
-    uint32_t box[2] = {64, 32};
+    uint32_t box[2] = {32, 32};
     uint64_t odims[2] = {dims[0], dims[1]};
     if (p.pad_T > 0) {
       const uint64_t P = static_cast<uint64_t>(p.pad_T + 2 * p.pad_h);
       odims[1] = dims[1] / (static_cast<uint64_t>(p.pad_T) * p.pad_T) * P * P;
     }
-    if (make_tmap_bf16(&tmOut, p.out, 2, odims, str, box) != 0) return -22;
+    if (make_tmap_bf16(&tmOut, p.out, 2, odims, str, box, TMAP_SWIZZLE_64B) != 0) return -22;
     tmAux = tmOut;
     if (EPI == EPI_RESIDUAL || EPI == EPI_GATE) {
       uint64_t astr[1] = {static_cast<uint64_t>(p.ldaux) * 2};
-      if (make_tmap_bf16(&tmAux, p.aux, 2, dims, astr, box) != 0) return -23;
+      if (make_tmap_bf16(&tmAux, p.aux, 2, dims, astr, box, TMAP_SWIZZLE_64B) != 0) return -23;
     }
   }
   using S = GemmSmem<BN, PAIR>;
@@ -601,7 +612,9 @@ template <int EPI>
 inline int launch_gemm(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* W, long long ldw,
                        const GemmParams& p, int sm_count, cudaStream_t stream) {
   // 128x256 tiles when the output is wide enough to fill the machine with them.
-  if (p.N >= 256 && (p.N % 256 == 0 || p.N > 512)) {
+  // (the QKV epilogue always takes 256-wide tiles: a warp's 64 columns are then one whole
+  // 64-channel head, which the qk norm needs)
+  if ((p.N >= 256 && (p.N % 256 == 0 || p.N > 512)) || EPI == EPI_QKV_ROPE) {
     // large problems: CTA pairs share each MMA (less shared-memory traffic per SM)
     if (GEMM_USE_PAIRS && p.M >= 1024)
       return launch_gemm_t<256, EPI, true>(A, lda, W, ldw, p, sm_count, stream);

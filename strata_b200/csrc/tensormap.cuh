@@ -25,11 +25,14 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+enum TmapSwizzle : int { TMAP_SWIZZLE_128B = 0, TMAP_SWIZZLE_64B = 1 };
+
 // bf16 tensor of `rank` dims (dim 0 innermost, contiguous). strides_bytes[i] is the byte
-// stride of dim i+1 (rank-1 entries). 128-byte swizzle, zero fill outside the tensor.
-// Returns 0 on success.
+// stride of dim i+1 (rank-1 entries). 128-byte swizzle (or 64-byte, for boxes whose inner
+// extent is 64 bytes), zero fill outside the tensor. Returns 0 on success.
 inline int make_tmap_bf16(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box) {
+                          const uint64_t* strides_bytes, const uint32_t* box,
+                          TmapSwizzle swizzle = TMAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return -1;
   cuuint64_t gdim[5];
@@ -44,7 +47,8 @@ inline int make_tmap_bf16(CUtensorMap* tm, const void* base, int rank, const uin
   }
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
                   const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  swizzle == TMAP_SWIZZLE_64B ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
