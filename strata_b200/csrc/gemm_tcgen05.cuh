@@ -439,6 +439,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
+          // head_dim 64: the 32-column sub-chunks of a head use table pairs [0,16) and
+          // [16,32); head_dim 32: each sub-chunk is a whole head and uses pairs [0,16).
+          // The table words are requested before the TMEM load so that the two latencies overlap.
+          const bool rotate = rope_tile && (n0 < p.rope_cols);
+          uint32_t cs[8];
+          if constexpr (EPI == EPI_QKV_ROPE) {
+            if (rotate && chunk_live) {
+              const int pair0 = ((p.head_dim == 64) ? (n0 & 63) >> 1 : 0) + 8 * g;
+              const uint4* src = cs_src + (pair0 >> 2);
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const uint4 t4 = __ldg(src + q);
+                cs[4 * q] = t4.x; cs[4 * q + 1] = t4.y; cs[4 * q + 2] = t4.z; cs[4 * q + 3] = t4.w;
+              }
+            }
+          }
           uint32_t r[16];
           if (chunk_live) {
             tmem_ld_32x16(taddr + 16 * g, r);
@@ -467,21 +483,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                "=r"(aux[4 * q + 3])
                              : "r"(addr)
                              : "memory");
-              }
-            }
-            // head_dim 64: the 32-column sub-chunks of a head use table pairs [0,16) and
-            // [16,32); head_dim 32: each sub-chunk is a whole head and uses pairs [0,16)
-            const bool rotate = rope_tile && (n0 < p.rope_cols);
-            uint32_t cs[8];
-            if constexpr (EPI == EPI_QKV_ROPE) {
-              if (rotate) {
-                const int pair0 = ((p.head_dim == 64) ? (n0 & 63) >> 1 : 0) + 8 * g;
-                const uint4* src = cs_src + (pair0 >> 2);
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                  const uint4 t4 = __ldg(src + q);
-                  cs[4 * q] = t4.x; cs[4 * q + 1] = t4.y; cs[4 * q + 2] = t4.z; cs[4 * q + 3] = t4.w;
-                }
               }
             }
             gemm_epilogue_16<EPI>(v, rotate, b_lane, 16 * g, aux, qk_scale[c], cs, p);
