@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE.json configs[1]): one bf16 Strata backbone block forward over a batch of
+Workload (the reference benchmark's single-GPU configuration): one bf16 Strata backbone block forward over a batch of
 4 tiles of 16 x 64 x 64 tokens, dim 512, 8 heads x 64, 3-D neighbourhood kernel (3,9,9),
 stereographic RoPE, MLP ratio 4 tanh-GELU; N(0,1) activations, trunc-normal(0.02) weights,
 all synthetic. A "step" is one block forward over the batch. With N > 1 GPUs every rank
