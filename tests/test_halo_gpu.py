@@ -138,3 +138,27 @@ def test_two_rank_peer_halo():
                        env={**__import__("os").environ, "NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "HALO WORKER OK" in r.stdout
+
+
+def test_barrier_wait_runs_out_and_reports():
+    # failure detection without a fault: a two-rank barrier whose partner never publishes (its
+    # flag word is never written). The wait has a short limit; the kernel returns by itself,
+    # the status word says "peer flag wait timed out", the context stays usable and the status
+    # can be cleared.
+    import ctypes
+    from strata_b200 import _lib
+    lib = _lib.load()
+    assert _lib.device_status() == 0
+    flags = torch.zeros(2, 64, dtype=torch.int32, device="cuda")   # [rank][slot]
+    ptrs = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.strata_halo_barrier(ptrs, 0, 2, 1, 20, stream), "strata_halo_barrier")
+    assert _lib.device_status() == 105          # reported ...
+    assert _lib.device_status() == 0            # ... and cleared by the read
+    assert flags[1, 0].item() == 1 and flags[0, 0].item() == 1   # our own publication happened
+    # the same barrier completes at once when the partner's slot carries the epoch
+    flags[0, 1] = 2
+    _lib.check(lib.strata_halo_barrier(ptrs, 0, 2, 2, 20, stream), "strata_halo_barrier")
+    assert _lib.device_status() == 0
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0         # context still alive
