@@ -149,6 +149,17 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
                                   const int32_t* src_a, const int32_t* src_b, int tiles_per_rank,
                                   int T, int halo, int64_t L, void* stream);
 
+/* k-nearest-neighbour halo: out[l, oc] = sum_j weights[oc, j] * x[l, idx[oc, j]] over this rank's
+ * padded cells oc (replaces DistributedTileKNNHaloPadding_AllGather.forward,
+ * screamcast/distributed_halo.py:305-327: all_gather of every rank's tiles + sparse regrid).
+ * idx: [tiles_per_rank*P*P, k] global interior cell ids g*T*T + i*T + j (owner rank = id /
+ * (tiles_per_rank*T*T)), weights: same shape, fp32; k in {1, 2, 4, 8}. h_peer_src[r]: rank r's
+ * tiles [L, tiles_per_rank*T*T] fp32; out: [L, tiles_per_rank*P*P]. Products and sums are
+ * rounded one by one in source order. */
+int strata_halo_gather_knn_fields_f32(float* out, const void* const* h_peer_src, int world,
+                                      const int32_t* idx, const float* weights, int k,
+                                      int tiles_per_rank, int T, int halo, int64_t L, void* stream);
+
 /* Windowed overlap-add un-pad: the normalised transpose D_w^-1 A^T (w . y) of the field gather A
  * above (replaces NormalizedHaloAdjoint.forward, screamcast/distributed_halo.py:438-448, whose
  * transpose runs as a vector-Jacobian product of the regrid plus a reduce_scatter). h_peer_padded[r]:

@@ -58,6 +58,8 @@ _SIGNATURES = {
                                             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "strata_halo_gather_knn_fields_f32": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p,
+                                                  c_int, c_int, c_int, c_int, c_int64, c_void_p]),
     "strata_halo_adjoint_fields_f32": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                c_int64, c_void_p]),

@@ -407,6 +407,46 @@ int strata_halo_gather_fields_f32(float* out, const void* const* h_peer_src, int
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
+int strata_halo_gather_knn_fields_f32(float* out, const void* const* h_peer_src, int world,
+                                      const int32_t* idx, const float* weights, int k,
+                                      int tiles_per_rank, int T, int halo, int64_t L, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (!out || !h_peer_src || !idx || !weights) return STRATA_ERR_ARG;
+  if (world < 1 || world > HALO_MAX_RANKS) return STRATA_ERR_UNSUPPORTED;
+  if (tiles_per_rank <= 0 || T <= 0 || halo < 0 || L < 0) return STRATA_ERR_ARG;
+  if (k != 1 && k != 2 && k != 4 && k != 8) return STRATA_ERR_UNSUPPORTED;
+  if (L == 0) return STRATA_OK;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (!h_peer_src[r]) return STRATA_ERR_ARG;
+    pp.p[r] = h_peer_src[r];
+  }
+  const int P = T + 2 * halo;
+  const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
+  const long long ocells = static_cast<long long>(tiles_per_rank) * P * P;
+  if (cells * world > 0x7fffffffLL || ocells > 0x7fffffffLL || L > 0x7fffffffLL)
+    return STRATA_ERR_ARG;
+  long long bx = (ocells + 255) / 256;
+  if (bx > 4096) bx = 4096;
+  long long by = L;
+  const long long want = static_cast<long long>(sms) * 16;
+  if (bx * by > want) by = (want + bx - 1) / bx;
+  if (by < 1) by = 1;
+  if (by > 65535) by = 65535;
+  dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(by));
+  cudaStream_t st = as_stream(stream);
+  const int no = static_cast<int>(ocells), nc = static_cast<int>(cells), nl = static_cast<int>(L);
+  switch (k) {
+    case 1: halo_gather_knn_fields_kernel<1><<<grid, 256, 0, st>>>(out, pp, idx, weights, no, nc, nl); break;
+    case 2: halo_gather_knn_fields_kernel<2><<<grid, 256, 0, st>>>(out, pp, idx, weights, no, nc, nl); break;
+    case 4: halo_gather_knn_fields_kernel<4><<<grid, 256, 0, st>>>(out, pp, idx, weights, no, nc, nl); break;
+    default: halo_gather_knn_fields_kernel<8><<<grid, 256, 0, st>>>(out, pp, idx, weights, no, nc, nl); break;
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
 int strata_halo_adjoint_fields_f32(float* out, const void* const* h_peer_padded, int world,
                                    const int32_t* offsets, const int32_t* cell, const float* coef,
                                    const float* window, const float* weights, int tiles_per_rank,

@@ -103,6 +103,38 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
   }
 }
 
+// Weighted gather (k-nearest-neighbour halo): out[l, oc] = sum_j w[oc, j] * x[l, idx[oc, j]]
+// with idx a global interior cell id (owner rank = id / cells_per_rank) - the sparse operator
+// the reference applies to an all-gathered copy of the whole globe, evaluated here by reading
+// the k source cells from the tiles of their owners (local or peer memory). Products and sums
+// are rounded one by one in source order (no fused multiply-add): reproducible on the host.
+// Source buffers [L, cells_per_rank] fp32 per rank; out [L, n_out_cells].
+template <int K>
+__global__ void __launch_bounds__(256)
+halo_gather_knn_fields_kernel(float* __restrict__ out, const PeerPtrs src,
+                              const int* __restrict__ idx, const float* __restrict__ w,
+                              int n_out_cells, int cells_per_rank, int L) {
+  for (int oc = blockIdx.x * blockDim.x + threadIdx.x; oc < n_out_cells;
+       oc += gridDim.x * blockDim.x) {
+    const float* sp[K];
+    float wk[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int id = __ldg(idx + static_cast<long long>(oc) * K + j);
+      const int rank = id / cells_per_rank;
+      sp[j] = static_cast<const float*>(src.p[rank]) + (id - rank * cells_per_rank);
+      wk[j] = __ldg(w + static_cast<long long>(oc) * K + j);
+    }
+    for (int l = blockIdx.y; l < L; l += gridDim.y) {
+      const long long so = static_cast<long long>(l) * cells_per_rank;
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) acc = __fadd_rn(acc, __fmul_rn(wk[j], sp[j][so]));
+      out[static_cast<long long>(l) * n_out_cells + oc] = acc;
+    }
+  }
+}
+
 // Windowed overlap-add un-pad (the normalised transpose of the field gather): every interior
 // cell c of this rank collects the padded cells that were copied from it - its own image and
 // its copies in neighbouring tiles' halos, in local or peer memory - as

@@ -43,6 +43,30 @@ def equiangular_cubed_sphere_latlon(n: int):
     return lat, np.mod(lon, 360.0)
 
 
+def padded_face_latlon(n: int, pad: int):
+    """(lat, lon) in degrees, each [6, n + 2*pad, n + 2*pad]: the faces of
+    `equiangular_cubed_sphere_latlon` continued beyond their edges along the same gnomonic
+    lines, so that every halo cell carries its own true position (what the reference reads from
+    its halo grid files for DistributedTileKNNHaloPadding_AllGather.from_padded_face_grid)."""
+    ang = (np.arange(-pad, n + pad) + 0.5) / n * (math.pi / 2) - math.pi / 4
+    ang = np.clip(ang, -math.pi / 2 + 1e-3, math.pi / 2 - 1e-3)
+    a, b = np.meshgrid(np.tan(ang), np.tan(ang), indexing="xy")
+    m = n + 2 * pad
+    lat = np.empty((6, m, m))
+    lon = np.empty((6, m, m))
+    for f in range(4):
+        x, y, z = np.ones_like(a), a, b
+        lon[f] = np.degrees(np.arctan2(y, x)) + 90.0 * f
+        lat[f] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    x, y, z = -b, a, np.ones_like(a)
+    lon[5] = np.degrees(np.arctan2(y, x))
+    lat[5] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    x, y, z = b, a, -np.ones_like(a)
+    lon[4] = np.degrees(np.arctan2(y, x))
+    lat[4] = np.degrees(np.arctan2(z, np.hypot(x, y)))
+    return lat, np.mod(lon, 360.0)
+
+
 def padded_tile_latlon(topology: TileTopology):
     """lat/lon (degrees) of this rank's padded tiles [tiles_per_rank, P, P]: interior cells
     from the synthetic grid, halo cells copied from the neighbouring tile / face like any other

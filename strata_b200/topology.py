@@ -310,3 +310,50 @@ def halo_adjoint_lists(topo: TileTopology, window: np.ndarray | None = None):
         m = k == j
         weights[src[m]] = (weights[src[m]] + wv[m]).astype(np.float32)
     return offsets.astype(np.int32), dst.astype(np.int32), coef, weights
+
+
+def knn_halo_weights(topo: TileTopology, lon_deg: np.ndarray, lat_deg: np.ndarray,
+                     pad_width_data: int, k: int = 4, eps: float = 1e-7):
+    """k-nearest-neighbour interpolation weights of this rank's padded tiles.
+
+    lon_deg / lat_deg: padded face grids [6, N + 2*pad, N + 2*pad] (degrees) that carry the TRUE
+    coordinates of the cells beyond each face edge (reference input:
+    DistributedTileKNNHaloPadding_AllGather.from_padded_face_grid,
+    screamcast/distributed_halo.py:225-303). Sources are the interior cells of every tile of
+    the globe; every padded cell of a local tile (its window of the padded face grid) gets its
+    k nearest sources on the sphere with inverse-distance weights 1 / (chord distance + eps),
+    normalised. A cell that coincides with a source gets (almost) all the weight: interiors
+    are preserved, halos inside a face reproduce the neighbouring tile, halos across a face
+    edge are interpolated between the neighbouring face's cells.
+
+    Returns (idx int32 [tiles_per_rank*P*P, k] of GLOBAL interior cell ids g*T*T + i*T + j,
+    weights float32 of the same shape).
+    """
+    from scipy.spatial import cKDTree
+    T, h, N = topo.tile_size, topo.halo_width, topo.face_size
+    pw = int(pad_width_data)
+    if lon_deg.shape != lat_deg.shape or lon_deg.shape[0] != 6 or lon_deg.shape[1] != N + 2 * pw:
+        raise ValueError(f"padded face grids must be [6, {N + 2 * pw}, {N + 2 * pw}]")
+    if pw < h:
+        raise ValueError("pad_width_data must cover the halo width")
+
+    def unit(lon, lat):
+        lo, la = np.radians(lon.astype(np.float64)), np.radians(lat.astype(np.float64))
+        return np.stack([np.cos(la) * np.cos(lo), np.cos(la) * np.sin(lo), np.sin(la)], axis=-1)
+    full = TileTopology(1, 0, N, T, h)
+    src = np.concatenate([unit(lon_deg[f, pw + ti * T:pw + (ti + 1) * T, pw + tj * T:pw + (tj + 1) * T],
+                               lat_deg[f, pw + ti * T:pw + (ti + 1) * T, pw + tj * T:pw + (tj + 1) * T]
+                               ).reshape(-1, 3) for f, ti, tj in full.global_tiles])
+    dst = np.concatenate([unit(lon_deg[f, pw + ti * T - h:pw + (ti + 1) * T + h,
+                                       pw + tj * T - h:pw + (tj + 1) * T + h],
+                               lat_deg[f, pw + ti * T - h:pw + (ti + 1) * T + h,
+                                       pw + tj * T - h:pw + (tj + 1) * T + h]).reshape(-1, 3)
+                          for f, ti, tj in topo.local_tiles])
+    if src.shape[0] >= 2 ** 31:
+        raise ValueError("grid too large for 32-bit cell ids")
+    dist, idx = cKDTree(src).query(dst, k=k)
+    if k == 1:
+        dist, idx = dist[:, None], idx[:, None]
+    lam = 1.0 / (dist + eps)
+    lam = lam / lam.sum(axis=1, keepdims=True)
+    return idx.astype(np.int32), lam.astype(np.float32)

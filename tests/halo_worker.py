@@ -12,7 +12,10 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 from oracle import halo_oracle as ho  # noqa: E402
-from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window  # noqa: E402
+from strata_b200.halo import (DistributedTileCopyHaloPadding, DistributedTileKNNHaloPadding,  # noqa: E402
+                              NormalizedCopyHaloAdjoint, kbd_window)
+from strata_b200.rollout import padded_face_latlon  # noqa: E402
+from tests.test_halo_knn import _apply  # noqa: E402
 from strata_b200.topology import TileTopology  # noqa: E402
 from tests.golden.make_golden import payload  # noqa: E402
 
@@ -58,7 +61,20 @@ def main():
         want = ho.halo_adjoint((pad_all + step).numpy(), topo_o, win.numpy())
         assert np.array_equal(got.cpu().numpy(), want), f"rank {rank} step {step}: halo adjoint differs"
     mod.check_status()
+    # k-nearest-neighbour halo: sources on both GPUs, weighted gather through peer memory
+    lat, lon = padded_face_latlon(fs, hw)
+    knn = DistributedTileKNNHaloPadding.from_padded_face_grid(
+        topology=topo, lon=torch.from_numpy(lon).float(), lat=torch.from_numpy(lat).float(),
+        pad_width_data=hw, device=torch.device("cuda", torch.cuda.current_device()))
+    xa = torch.randn(2, topo.total_tiles, ts, ts, generator=torch.Generator().manual_seed(4))
+    for step in range(3):
+        got = knn((xa[:, s:s + topo.tiles_per_rank] * (step + 1)).cuda())
+        want = _apply((xa * (step + 1)).numpy(), knn.knn_idx.cpu().numpy(), knn.knn_weights.cpu().numpy())
+        assert np.array_equal(got.cpu().numpy().reshape(want.shape), want), \
+            f"rank {rank} step {step}: knn halo differs"
+    knn.check_status()
     dist.barrier()
+    knn.close()
     mod.close()
     if rank == 0:
         print("HALO WORKER OK", world)

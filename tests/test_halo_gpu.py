@@ -123,6 +123,30 @@ def test_halo_adjoint_bit_exact(window):
     with pytest.raises(ValueError):
         unpad(torch.zeros(1, topo.tiles_per_rank, P, P - 1, device="cuda"))
 
+
+def test_knn_halo_bit_exact_against_host_evaluation():
+    from strata_b200.halo import DistributedTileKNNHaloPadding
+    from strata_b200.rollout import padded_face_latlon
+    from strata_b200.topology import TileTopology
+    from tests.test_halo_knn import _apply
+    N, T, H, PW = 16, 4, 2, 4
+    lat, lon = padded_face_latlon(N, PW)
+    topo = TileTopology(1, 0, N, T, H)
+    mod = DistributedTileKNNHaloPadding.from_padded_face_grid(
+        topology=topo, lon=torch.from_numpy(lon).float(), lat=torch.from_numpy(lat).float(),
+        pad_width_data=PW, device="cuda")
+    assert mod.lat_deg.shape == (topo.tiles_per_rank, T + 2 * H, T + 2 * H)
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(3, 2, topo.tiles_per_rank, T, T, generator=g)
+    got = mod(x.cuda())
+    mod.check_status()
+    want = _apply(x.numpy(), mod.knn_idx.cpu().numpy(), mod.knn_weights.cpu().numpy())
+    assert np.array_equal(got.cpu().numpy().reshape(want.shape), want)
+    # interiors preserved to the reference's tolerance, topology.crop inverts the padding
+    assert torch.allclose(topo.crop(got).cpu(), x, atol=1e-3, rtol=1e-3)
+    with pytest.raises(TypeError):
+        mod(x.cuda().double())
+
 def _two_gpus():
     return torch.cuda.is_available() and torch.cuda.device_count() >= 2
 

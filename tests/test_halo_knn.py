@@ -1,0 +1,83 @@
+"""k-nearest-neighbour halo weights (host set-up) against a brute-force oracle, and the
+properties the reference's tests check for its KNN halo (tests/test_distributed_tile_halo.py:
+97-293: interiors preserved, interior-tile halo equals the neighbouring tiles' data to 1e-3)."""
+import numpy as np
+import pytest
+
+from oracle import halo_oracle as ho
+from strata_b200.rollout import equiangular_cubed_sphere_latlon, padded_face_latlon
+from strata_b200.topology import TileTopology, knn_halo_weights
+
+N, T, H, PW = 16, 4, 2, 4
+
+
+def _apply(x_all, idx, w):
+    """Host evaluation of the weighted gather in the kernel's order (float32, no FMA)."""
+    lead = x_all.shape[:-3]
+    flat = x_all.reshape(*lead, -1).astype(np.float32)
+    acc = np.zeros((*lead, idx.shape[0]), np.float32)
+    for j in range(idx.shape[1]):
+        acc = (acc + (w[:, j] * flat[..., idx[:, j]]).astype(np.float32)).astype(np.float32)
+    return acc
+
+
+def test_padded_faces_extend_the_face_grid():
+    lat, lon = padded_face_latlon(N, PW)
+    la0, lo0 = equiangular_cubed_sphere_latlon(N)
+    assert np.allclose(lat[:, PW:-PW, PW:-PW], la0) and np.allclose(lon[:, PW:-PW, PW:-PW], lo0)
+
+
+@pytest.mark.parametrize("world,rank", [(1, 0), (2, 1), (3, 2)])
+def test_weights_match_brute_force_and_preserve_interiors(world, rank):
+    lat, lon = padded_face_latlon(N, PW)
+    topo = TileTopology(world, rank, N, T, H)
+    otopo = ho.TileTopology(world, rank, N, T, H)
+    full = ho.TileTopology(1, 0, N, T, H)
+    idx, w = knn_halo_weights(topo, lon, lat, PW)
+    assert np.allclose(w.sum(1), 1.0, atol=1e-6) and (w >= 0).all()
+    # smooth field: product lists and brute-force oracle interpolate to the same values (the
+    # two searches may break ties between equidistant sources differently)
+    la, lo = np.radians(equiangular_cubed_sphere_latlon(N))
+    field = (np.sin(la) * np.cos(lo) + 0.3 * np.cos(2 * la)).astype(np.float32)
+    tiles = np.stack([field[f, i * T:(i + 1) * T, j * T:(j + 1) * T] for f, i, j in full.global_tiles])
+    want, oidx, ow = ho.knn_halo(tiles, otopo, lon, lat, PW)
+    got = _apply(tiles, idx, w).reshape(want.shape)
+    same = (np.sort(idx, 1) == np.sort(oidx, 1)).all(1)
+    assert same.mean() > 0.98
+    assert np.array_equal(got.reshape(-1)[same], want.reshape(-1)[same]) or \
+        np.allclose(got.reshape(-1)[same], want.reshape(-1)[same], atol=1e-6)
+    assert np.allclose(got, want, atol=2e-2)            # tie cells: neighbouring values of a smooth field
+    # interiors: the nearest source of an interior cell is the cell itself, with all the weight
+    P = T + 2 * H
+    s = rank * topo.tiles_per_rank
+    own = (np.arange(topo.tiles_per_rank)[:, None, None] + s) * T * T + \
+        np.arange(T)[None, :, None] * T + np.arange(T)[None, None, :]
+    i0 = idx[:, 0].reshape(topo.tiles_per_rank, P, P)[:, H:-H, H:-H]
+    w0 = w[:, 0].reshape(topo.tiles_per_rank, P, P)[:, H:-H, H:-H]
+    assert np.array_equal(i0, own) and (w0 > 0.9999).all()
+
+
+def test_interior_tile_halo_equals_neighbour_data():
+    # the reference's own check (test_distributed_tile_halo.py:249-293): pixel-coded payload,
+    # tile (face 0, ti 1, tj 1), padded tile == the face window, atol = rtol = 1e-3
+    lat, lon = padded_face_latlon(N, PW)
+    topo = TileTopology(1, 0, N, T, H)
+    idx, w = knn_halo_weights(topo, lon, lat, PW)
+    faces = np.zeros((6, N, N), np.float32)
+    for f in range(6):
+        faces[f] = f * 1000 + np.arange(N)[:, None] * N + np.arange(N)[None, :]
+    tiles = np.stack([faces[f, i * T:(i + 1) * T, j * T:(j + 1) * T] for f, i, j in topo.global_tiles])
+    P = T + 2 * H
+    padded = _apply(tiles, idx, w).reshape(topo.total_tiles, P, P)
+    tpd = N // T
+    t = 0 * tpd * tpd + 1 * tpd + 1
+    want = faces[0, T - H:2 * T + H, T - H:2 * T + H]
+    assert np.allclose(padded[t], want, atol=1e-3, rtol=1e-3)
+
+
+def test_bad_grids_are_rejected():
+    lat, lon = padded_face_latlon(N, PW)
+    with pytest.raises(ValueError):
+        knn_halo_weights(TileTopology(1, 0, N, T, H), lon[:, 1:], lat[:, 1:], PW)
+    with pytest.raises(ValueError):
+        knn_halo_weights(TileTopology(1, 0, N, T, 6), lon, lat, PW)
