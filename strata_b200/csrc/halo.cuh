@@ -220,7 +220,7 @@ halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
 // frame; it is turned into the receiver's frame on the way by the per-cell delta rotation
 // dcs[tile, cell, pair] = (cos, sin)(theta_receiver - theta_sender) (IEEE half pairs), V is
 // copied. Corner-diagonal cells average their two (individually rotated) sources.
-// grid: x over (halo cell, 16-byte vector of the 2C k|v channels), y over (tile, depth).
+// grid: x over groups of four halo cells (64 threads per cell), y over (tile, depth).
 __global__ void __launch_bounds__(256)
 halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
                       const int* __restrict__ src_a, const int* __restrict__ src_b,
@@ -237,11 +237,11 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
   // interior (2*halo rows of P cells), then the 2*halo side columns of the T interior rows
   const int n_strip = 2 * halo * P;
   const int n_halo = n_strip + 2 * halo * T;
-  const long long total = static_cast<long long>(n_halo) * vpc;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int hc = static_cast<int>(idx / vpc);
-    const int v = static_cast<int>(idx - static_cast<long long>(hc) * vpc);
+  // 64 threads share a halo cell: its decoding and the source rows are worked out once per
+  // cell, each thread then moves every 64th 16-byte vector of the cell's k|v channels
+  const int sub = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
+  const int cells_per_iter = blockDim.x >> 6;
+  for (int hc = blockIdx.x * cells_per_iter + sub; hc < n_halo; hc += gridDim.x * cells_per_iter) {
     int pi, pj;
     if (hc < n_strip) {
       const int row = hc / P;
@@ -257,23 +257,24 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
     const int pc = pi * P + pj;
     const int a = __ldg(src_a + tile * PP + pc);
     const int b = __ldg(src_b + tile * PP + pc);
-    const long long chan = static_cast<long long>(C) + (v << 3);   // k|v start after q
-    auto load = [&](int id) {
+    auto source_row = [&](int id) -> const __nv_bfloat16* {
       const int rank = id / cells_per_rank;
       const int local = id - rank * cells_per_rank;
       const int st = local / TT;
       const int sc = local - st * TT;
       const int si = sc / T, sj = sc - si * T;
-      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(src.p[rank]);
       const long long row = ((static_cast<long long>(st) * D + d) * P + si + halo) * P + sj + halo;
-      return *reinterpret_cast<const uint4*>(base + row * ld + chan);
+      return static_cast<const __nv_bfloat16*>(src.p[rank]) + row * ld + C;   // k|v start after q
     };
-    auto rotate = [&](const uint4& x, const uint32_t* tab, float (&o)[8]) {
+    const __nv_bfloat16* row_a = source_row(a);
+    const __nv_bfloat16* row_b = b >= 0 ? source_row(b) : nullptr;
+    const long long tab_row = (static_cast<long long>(tile) * PP + pc) * half;
+    __nv_bfloat16* out_row = qkv + ((static_cast<long long>(tile) * D + d) * PP + pc) * ld + C;
+    auto rotate = [&](const uint4& x, const uint32_t* tab, int v, float (&o)[8]) {
       const uint32_t w[4] = {x.x, x.y, x.z, x.w};
       if (v < kvec) {
         const int p0 = (((v << 3) % head_dim) >> 1);   // first channel pair of this vector
-        const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(
-            tab + (static_cast<long long>(tile) * PP + pc) * half + p0));
+        const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(tab + tab_row + p0));
         const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -290,21 +291,22 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
         }
       }
     };
-    float ra[8];
-    rotate(load(a), dcs_a, ra);
-    if (b >= 0) {
-      float rb[8];
-      rotate(load(b), dcs_b, rb);
+    for (int v = lane64; v < vpc; v += 64) {
+      float ra[8];
+      rotate(*reinterpret_cast<const uint4*>(row_a + (v << 3)), dcs_a, v, ra);
+      if (row_b != nullptr) {
+        float rb[8];
+        rotate(*reinterpret_cast<const uint4*>(row_b + (v << 3)), dcs_b, v, rb);
 #pragma unroll
-      for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+        for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+      }
+      uint4 o4;
+      o4.x = pack_bf16(ra[0], ra[1]);
+      o4.y = pack_bf16(ra[2], ra[3]);
+      o4.z = pack_bf16(ra[4], ra[5]);
+      o4.w = pack_bf16(ra[6], ra[7]);
+      *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
     }
-    uint4 o4;
-    o4.x = pack_bf16(ra[0], ra[1]);
-    o4.y = pack_bf16(ra[2], ra[3]);
-    o4.z = pack_bf16(ra[4], ra[5]);
-    o4.w = pack_bf16(ra[6], ra[7]);
-    const long long orow = (static_cast<long long>(tile) * D + d) * PP + pc;
-    *reinterpret_cast<uint4*>(qkv + orow * ld + chan) = o4;
   }
 }
 
