@@ -230,6 +230,32 @@ int strata_postprocess_fields_f32(const void* y, int64_t ldy, int B, int C_out, 
                                   const float* lon0, int u_idx, int v_idx, int pv, int ph, int pw,
                                   float* out, void* stream);
 
+/* Pixel-stage (two-stage model) row kernel: x' = x + gate * y (written to x_out; skipped when y
+ * is NULL; gate NULL means x + y), then out = LN(x') * (1 + scale) + shift with a non-affine
+ * LayerNorm (skipped when out is NULL; shift/scale NULL means plain LN). All operands bf16 rows
+ * of C channels; shift and scale share the row stride ldm (two column blocks of the per-pixel
+ * modulation matrix). Replaces the modulate / gated-residual arithmetic of physicsnemo's
+ * StrataPixel3DBlock (adaln-zero: screamcast train.py:279-299 states shift=0, scale=1, gate=0
+ * at initialisation). */
+int strata_adaln_rows_bf16(const void* x, int64_t ldx, const void* y, int64_t ldy, const void* gate,
+                           int64_t ldg, void* x_out, int64_t ldxo, const void* shift,
+                           const void* scale, int64_t ldm, void* out, int64_t ldo, int M, int C,
+                           float eps, void* stream);
+
+/* In-place RMS norm of the q and k heads (64 channels each) of packed rows [M, 3C]
+ * (qk_norm_pixel of screamcast/strata_wrappers.py:437, non-affine). */
+int strata_qk_norm_rows_bf16(void* qkv, int64_t ld, int64_t M, int C, float eps, void* stream);
+
+/* Conditioning rows of the "bilinear_dw" AdaLN mode (screamcast/strata_wrappers.py:491-495;
+ * parameters adaln_bilinear_dw_conv.{weight,bias} of the parameter manifest
+ * tests/regression_data/pixeldit_*.param_order.txt:253-254): backbone tokens [B, D, h, w, Cb]
+ * bf16 are upsampled bilinearly by `factor` in h and w (half-pixel centres), convolved depthwise
+ * with a ks x ks kernel (zero padding), biased and passed through the tanh GELU; rows
+ * row0 .. row0 + n_rows of the flattened (b, d, y, x) pixel order are written as bf16 [n_rows, Cb]. */
+int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int Cb, int factor,
+                           const float* w_dw, const float* b_dw, int ks, int64_t row0,
+                           int64_t n_rows, void* out, void* stream);
+
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
  * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work

@@ -10,6 +10,7 @@
 #include "na3d.cuh"
 #include "halo.cuh"
 #include "prepost.cuh"
+#include "adaln.cuh"
 
 using namespace strata;
 
@@ -568,6 +569,68 @@ int strata_ipc_free(void* dptr) {
   if (!dptr) return STRATA_ERR_ARG;
   cudaError_t e = cudaFree(dptr);
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+int strata_adaln_rows_bf16(const void* x, int64_t ldx, const void* y, int64_t ldy, const void* gate,
+                           int64_t ldg, void* x_out, int64_t ldxo, const void* shift,
+                           const void* scale, int64_t ldm, void* out, int64_t ldo, int M, int C,
+                           float eps, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (M == 0) return STRATA_OK;
+  if (!x || M < 0 || C <= 0 || C % 8 || ldx % 8 || ldx < C || !aligned16(x)) return STRATA_ERR_ARG;
+  if (!y && !out) return STRATA_ERR_ARG;
+  if (y && (!x_out || !aligned16(y) || !aligned16(x_out) || ldy % 8 || ldy < C || ldxo % 8 ||
+            ldxo < C))
+    return STRATA_ERR_ARG;
+  if (!y && gate) return STRATA_ERR_ARG;
+  if (gate && (!aligned16(gate) || ldg % 8 || ldg < C)) return STRATA_ERR_ARG;
+  if ((shift == nullptr) != (scale == nullptr)) return STRATA_ERR_ARG;
+  if (shift && (!out || !aligned16(shift) || !aligned16(scale) || ldm % 8 || ldm < C))
+    return STRATA_ERR_ARG;
+  if (out && (!aligned16(out) || ldo % 8 || ldo < C)) return STRATA_ERR_ARG;
+  AdalnRowsParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx;
+  p.y = static_cast<const __nv_bfloat16*>(y); p.ldy = ldy;
+  p.gate = static_cast<const __nv_bfloat16*>(gate); p.ldg = ldg;
+  p.xo = static_cast<__nv_bfloat16*>(x_out); p.ldxo = ldxo;
+  p.shift = static_cast<const __nv_bfloat16*>(shift);
+  p.scale = static_cast<const __nv_bfloat16*>(scale); p.ldm = ldm;
+  p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.M = M; p.C = C; p.eps = eps;
+  int r = launch_adaln_rows(p, sms, as_stream(stream));
+  return r == -2 ? STRATA_ERR_ARG : r;
+}
+
+int strata_qk_norm_rows_bf16(void* qkv, int64_t ld, int64_t M, int C, float eps, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (M == 0) return STRATA_OK;
+  if (!qkv || M < 0 || !aligned16(qkv)) return STRATA_ERR_ARG;
+  int r = launch_qk_norm_rows(static_cast<__nv_bfloat16*>(qkv), ld, M, C, eps, sms,
+                              as_stream(stream));
+  return r == -2 ? STRATA_ERR_ARG : r;
+}
+
+int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int Cb, int factor,
+                           const float* w_dw, const float* b_dw, int ks, int64_t row0,
+                           int64_t n_rows, void* out, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (n_rows == 0) return STRATA_OK;
+  if (!tokens || !w_dw || !out || !aligned16(tokens) || !aligned16(out) || B <= 0 || n_rows < 0)
+    return STRATA_ERR_ARG;
+  if (D <= 0 || h <= 0 || w <= 0 || factor <= 0) return STRATA_ERR_ARG;
+  const int64_t pixels = static_cast<int64_t>(B) * D * h * factor * w * factor;
+  if (row0 < 0 || row0 + n_rows > pixels) return STRATA_ERR_ARG;
+  AdalnCondParams p;
+  p.tok = static_cast<const __nv_bfloat16*>(tokens);
+  p.wdw = w_dw; p.bdw = b_dw;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.row0 = row0; p.n_rows = n_rows;
+  p.D = D; p.h = h; p.w = w; p.Cb = Cb; p.factor = factor; p.ks = ks;
+  int r = launch_adaln_cond(p, sms, as_stream(stream));
+  return r == -2 ? STRATA_ERR_ARG : r;
 }
 
 }  // extern "C"

@@ -359,3 +359,84 @@ def postprocess_fields(y: torch.Tensor, shape, lat=None, lon=None, lat0=None, lo
             y.data_ptr(), y.stride(0), B, C, D, H, W, p(lat), p(lon), p(lat0), p(lon0), u, v,
             pv, ph, pw, out.data_ptr(), _stream_ptr(y)), "strata_postprocess_fields_f32")
     return out
+
+
+# ------------------------------------------------------------------ pixel stage (AdaLN blocks)
+def _rows_or_none(t, name, C):
+    if t is None:
+        return None, 0
+    _require_cuda_bf16(t, name)
+    if t.dim() != 2 or t.shape[1] != C or t.stride(1) != 1:
+        raise ValueError(f"{name} must be [M, {C}] rows with unit inner stride")
+    return t.data_ptr(), t.stride(0)
+
+
+def adaln_rows(x: torch.Tensor, *, y: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+               shift: torch.Tensor | None = None, scale: torch.Tensor | None = None,
+               norm: bool = True, eps: float = 1e-6):
+    """One pass over token rows [M, C] (bf16): x <- x + gate * y in place (when y is given;
+    gate None means x + y), then - when `norm` - returns LN(x) * (1 + scale) + shift (plain
+    non-affine LN when shift/scale are None). y, gate, shift, scale may be column slices of wider
+    matrices. Returns the normalised rows, or None when norm is False."""
+    _require_cuda_bf16(x, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [M, C] rows with unit inner stride")
+    M, C = x.shape
+    if y is None and not norm:
+        raise ValueError("nothing to do: give y and/or norm=True")
+    if (shift is None) != (scale is None):
+        raise ValueError("shift and scale come together")
+    yp, ldy = _rows_or_none(y, "y", C)
+    gp, ldg = _rows_or_none(gate, "gate", C)
+    sp, lds = _rows_or_none(shift, "shift", C)
+    cp, ldc = _rows_or_none(scale, "scale", C)
+    if sp is not None and lds != ldc:
+        raise ValueError("shift and scale must share a row stride")
+    out = torch.empty((M, C), dtype=torch.bfloat16, device=x.device) if norm else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().strata_adaln_rows_bf16(
+            x.data_ptr(), x.stride(0), yp, ldy, gp, ldg, x.data_ptr() if yp else None, x.stride(0),
+            sp, cp, lds, None if out is None else out.data_ptr(), C, M, C, float(eps),
+            _stream_ptr(x)), "strata_adaln_rows_bf16")
+    return out
+
+
+def qk_norm_rows_(qkv: torch.Tensor, C: int, eps: float = 1e-6) -> torch.Tensor:
+    """In-place RMS norm of the 64-channel q and k heads of packed rows [M, 3C]."""
+    _require_cuda_bf16(qkv, "qkv")
+    if qkv.dim() != 2 or qkv.shape[1] != 3 * C or qkv.stride(1) != 1:
+        raise ValueError(f"qkv must be [M, {3 * C}] rows")
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.load().strata_qk_norm_rows_bf16(
+            qkv.data_ptr(), qkv.stride(0), qkv.shape[0], int(C), float(eps), _stream_ptr(qkv)),
+            "strata_qk_norm_rows_bf16")
+    return qkv
+
+
+def adaln_cond(tokens: torch.Tensor, w_dw: torch.Tensor, b_dw: torch.Tensor | None, factor: int,
+               row0: int = 0, n_rows: int | None = None, out: torch.Tensor | None = None):
+    """GELU(depthwise conv(bilinear upsample(tokens)) + bias) as bf16 rows. tokens: bf16
+    [B, D, h, w, Cb] contiguous; w_dw fp32 [Cb, ks, ks]; rows row0 .. row0+n_rows of the
+    flattened (b, d, y, x) pixels at resolution (h*factor, w*factor)."""
+    _require_cuda_bf16(tokens, "tokens")
+    if tokens.dim() != 5 or not tokens.is_contiguous():
+        raise ValueError("tokens must be contiguous [B, D, h, w, Cb]")
+    B, D, h, w, Cb = tokens.shape
+    w_dw = _f32_dev(w_dw, "w_dw")
+    if w_dw.dim() != 3 or w_dw.shape[0] != Cb or w_dw.shape[1] != w_dw.shape[2]:
+        raise ValueError(f"w_dw must be [{Cb}, ks, ks]")
+    ks = w_dw.shape[1]
+    b_dw = None if b_dw is None else _f32_dev(b_dw, "b_dw", (Cb,))
+    pixels = B * D * h * factor * w * factor
+    if n_rows is None:
+        n_rows = pixels - row0
+    if out is None:
+        out = torch.empty((n_rows, Cb), dtype=torch.bfloat16, device=tokens.device)
+    elif out.shape != (n_rows, Cb) or not out.is_contiguous() or out.dtype != torch.bfloat16:
+        raise ValueError("out must be contiguous bf16 [n_rows, Cb]")
+    with torch.cuda.device(tokens.device):
+        _lib.check(_lib.load().strata_adaln_cond_bf16(
+            tokens.data_ptr(), B, D, h, w, Cb, int(factor), w_dw.data_ptr(),
+            None if b_dw is None else b_dw.data_ptr(), ks, int(row0), int(n_rows), out.data_ptr(),
+            _stream_ptr(tokens)), "strata_adaln_cond_bf16")
+    return out

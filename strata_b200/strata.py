@@ -263,7 +263,7 @@ class StrataTransformer3D(nn.Module):
             return None, None
         if self.rope_mode == "axial":
             cos, sin = rope.axial_rope_tables(h, w, self.head_dim, self.rope_base,
-                                              device=self.final_layer.linear.weight.device)
+                                              device=self.patch_embed.proj.weight.device)
             return cos.expand(n_tiles, -1, -1).contiguous(), sin.expand(n_tiles, -1, -1).contiguous()
         if pos is None:
             raise ValueError("stereographic RoPE needs pos=[B, 2, H, W] (lat, lon)")

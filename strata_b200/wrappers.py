@@ -305,3 +305,151 @@ class StrataBackboneModel(_StrataModelBase):
         pos = torch.stack([lat, lon], dim=1)
         return self.strata.forward_fused(x, pos, lat=lat, lon=lon, lat0=lat0, lon0=lon0, wind=wind,
                                          concat_lat=self._do_concat_latitude)
+
+
+class StrataModel(_StrataModelBase):
+    """Two-stage model (reference: screamcast/strata_wrappers.py:418-687): a backbone and an
+    AdaLN pixel stage under `self.strata`. Pixel-stage arguments carry the `_pixel` suffix;
+    every other keyword is a backbone argument of `StrataBackboneModel`."""
+
+    _WRAPPER_KEYS = ("do_concat_latitude", "do_rotate_wind", "wind_channel_indices", "grid_type",
+                     "nside", "cubesphere_latlon_path", "index_is_latlon",
+                     "use_dealiased_patch_embed", "dealias_resample_filter")
+
+    def __init__(self, *, embed_dim_pixel: int = 128, n_layers_pixel: int = 4,
+                 num_heads_pixel: int | None = None, mlp_ratio_pixel: float = 4.0,
+                 attn_kernel_pixel: int = 3, gated_attention_pixel: bool = False,
+                 qk_norm_pixel: bool = False, qk_norm_elementwise_affine_pixel: bool = False,
+                 na3d_backend_pixel: Optional[str] = None, do_bf16_mixed_pixel: bool = False,
+                 freeze_semantic: bool = False, freeze_pixel_blocks: bool = False,
+                 use_bilinear_dw_gelu_project_adaln_pixel: bool = False,
+                 use_chunked_depthwise_conv_pixel: bool = True,
+                 first_block_only_adaln_pixel: bool = False, do_rope_2d_pixel: bool = False,
+                 do_rope_2d_stereographic_pixel: bool = False,
+                 do_activation_checkpointing_pixel: bool | float = False, **semantic_kwargs):
+        from .pixel import Strata
+        sk = dict(semantic_kwargs)
+        super().__init__(do_concat_latitude=sk.get("do_concat_latitude", True),
+                         do_rotate_wind=sk.get("do_rotate_wind", False),
+                         wind_channel_indices=sk.get("wind_channel_indices", None),
+                         grid_type=sk.get("grid_type", "healpix"), nside=sk.get("nside", 1024),
+                         cubesphere_latlon_path=sk.get("cubesphere_latlon_path",
+                                                       "data/latlon_ne1024pg2.nc"),
+                         index_is_latlon=sk.get("index_is_latlon", False))
+        if sk.get("use_dealiased_patch_embed", False):
+            raise ValueError("use_dealiased_patch_embed is not supported by this package yet")
+        self._rope_length_scale_base = _resolve_rope_base(sk.get("rope_length_scale"))
+        backbone_config = self._backbone_config(sk)
+        if use_bilinear_dw_gelu_project_adaln_pixel and backbone_config["patch_size"][0] != 1:
+            raise ValueError("use_bilinear_dw_gelu_project_adaln requires patch_size_vert=1 "
+                             "(the bilinear upsample covers H and W only); got patch_size_vert="
+                             f"{backbone_config['patch_size'][0]}")
+        rope_mode_pixel = _rope_mode(do_rope_2d_pixel, do_rope_2d_stereographic_pixel)
+        self.strata = Strata(
+            backbone_config=backbone_config, embed_dim_pixel=embed_dim_pixel,
+            num_layers_pixel=n_layers_pixel, num_heads_pixel=num_heads_pixel,
+            mlp_ratio_pixel=mlp_ratio_pixel, attn_kernel_pixel=attn_kernel_pixel,
+            gated_attention_pixel=gated_attention_pixel, qk_norm_pixel=qk_norm_pixel,
+            qk_norm_affine_pixel=qk_norm_elementwise_affine_pixel,
+            na3d_backend_pixel=na3d_backend_pixel,
+            adaln_mode="bilinear_dw" if use_bilinear_dw_gelu_project_adaln_pixel else "pixel_proj",
+            first_block_only_adaln=first_block_only_adaln_pixel,
+            use_chunked_depthwise_conv=use_chunked_depthwise_conv_pixel,
+            rope_mode_pixel=rope_mode_pixel, rope_base_pixel=100.0,
+            rope_length_scale_pixel=(self._rope_length_scale_base
+                                     if rope_mode_pixel == "stereographic" else 1.0),
+            bf16_mixed_pixel=do_bf16_mixed_pixel,
+            activation_checkpointing_pixel=do_activation_checkpointing_pixel)
+        _use_tanh_gelu(self.strata)
+        if freeze_semantic:
+            for p in self.strata.backbone.parameters():
+                p.requires_grad_(False)
+        if freeze_pixel_blocks:
+            for p in self.strata.pixel_blocks.parameters():
+                p.requires_grad_(False)
+            for p in self.strata.pixel_final_layer.parameters():
+                p.requires_grad_(False)
+
+    def _backbone_config(self, semantic_kwargs: dict) -> dict:
+        """Backbone keywords of the single-stage wrapper -> StrataTransformer3D arguments;
+        unknown keywords raise TypeError as in the reference (strata_wrappers.py:593-596)."""
+        sk = {k: v for k, v in semantic_kwargs.items() if k not in self._WRAPPER_KEYS}
+        sk.pop("rope_length_scale", None)
+        shape = (sk.pop("depth"), sk.pop("height"), sk.pop("width"))
+        patch = sk.pop("patch_size", 1)
+        pv, ph = sk.pop("patch_size_vert", None), sk.pop("patch_size_horiz", None)
+        pv = patch if pv is None else pv
+        ph = patch if ph is None else ph
+        rope_mode = _rope_mode(sk.pop("do_rope_2d", False), sk.pop("do_rope_2d_stereographic", False))
+        config = dict(
+            in_channels=sk.pop("in_chans") + (2 if self._do_concat_latitude else 0),
+            out_channels=sk.pop("base_out_chans"), input_shape=shape, patch_size=(pv, ph, ph),
+            embed_dim=sk.pop("embed_dim", 768), num_heads=sk.pop("num_heads", 16),
+            num_layers=sk.pop("n_layers", 12), mlp_ratio=sk.pop("mlp_ratio", 4.0),
+            qkv_bias=sk.pop("qkv_bias", True), qk_norm=sk.pop("qk_norm", False),
+            qk_norm_affine=sk.pop("qk_norm_elementwise_affine", False),
+            attn_kernel=sk.pop("attn_kernel", 3), na_dilation=sk.pop("na_dilations", 3),
+            do_interleaved_dilation=sk.pop("do_interleaved_dilation", False),
+            do_alt_depthwise_attn=sk.pop("do_alt_depthwise_attn", False),
+            gated_attention=sk.pop("gated_attention", False),
+            na3d_backend=sk.pop("na3d_backend", None), rope_mode=rope_mode, rope_base=100.0,
+            rope_length_scale=(self._rope_length_scale_base * ph
+                               if rope_mode == "stereographic" else 1.0),
+            activation_checkpointing=sk.pop("do_activation_checkpointing", False),
+            bf16_mixed=sk.pop("do_bf16_mixed", False))
+        if sk:
+            raise TypeError(f"Unsupported legacy DiT kwargs for the Strata backbone: {sorted(sk)}")
+        return config
+
+    @property
+    def _out_chans(self) -> int:
+        return self.strata.out_channels
+
+    @property
+    def _depth(self) -> int:
+        return self.strata.depth
+
+    @property
+    def _height(self) -> int:
+        return self.strata.height
+
+    @property
+    def _width(self) -> int:
+        return self.strata.width
+
+    def disable_activation_checkpointing(self) -> None:
+        _ = self.strata.backbone._activation_checkpointing_ratio
+        _ = self.strata._activation_checkpointing_ratio_pixel
+        self.strata.backbone._activation_checkpointing_ratio = 0.0
+        self.strata._activation_checkpointing_ratio_pixel = 0.0
+
+    def set_tile_size(self, height: int, width: int) -> None:
+        self.strata.backbone.set_tile_size(height, width)
+        self.strata.height, self.strata.width = int(height), int(width)
+
+    def set_rope_length_scale(self, base: float) -> None:
+        if base <= 0:
+            raise ValueError(f"rope length scale base must be positive, got {base}")
+        if self.strata.backbone.rope_mode != "stereographic":
+            raise ValueError("set_rope_length_scale is only meaningful for stereographic RoPE")
+        self._rope_length_scale_base = base
+        self.strata.backbone.rope_length_scale = base * self.strata.backbone.patch_size[1]
+
+    def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+        if not (x.is_cuda and x.dtype == torch.float32):
+            raise RuntimeError("the two-stage model runs on CUDA fp32 fields only (its kernels "
+                               "have no CPU fallback)")
+        B = x.shape[0]
+        lat, lon = self.geometry.lat_lon_from_index(index)
+        if lat.shape[0] != B:
+            lat = lat.expand(B, -1, -1)
+            lon = lon.expand(B, -1, -1)
+        lat = lat.to(device=x.device, dtype=torch.float32).contiguous()
+        lon = lon.to(device=x.device, dtype=torch.float32).contiguous()
+        lat0 = lon0 = wind = None
+        if self._do_rotate_wind:
+            lat0, lon0 = TileGeometry.tile_center(lat, lon)
+            wind = self._wind_channel_indices
+        pos = torch.stack([lat, lon], dim=1)
+        return self.strata.forward_fused(x, pos, lat=lat, lon=lon, lat0=lat0, lon0=lon0, wind=wind,
+                                         concat_lat=self._do_concat_latitude)

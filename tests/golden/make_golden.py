@@ -122,7 +122,11 @@ def main(ref_root):
         V_rec=Vr.numpy(),
         mean_lon_pm=tg.mean_longitude(lon, return_0_2pi=False).numpy(),
         rope_scale=np.array([tg.TileGeometry.default_rope_length_scale(s) for s in (1, 2, 4)]))
-    print("wrote", sorted(p.name for p in OUT.glob("*.npz")))
+    # parameter names of the two-stage model, in order (names only; the manifest holds no values)
+    manifest = next(Path(ref_root, "tests", "regression_data").glob("pixeldit_*param_order.txt"))
+    names = [ln.strip() for ln in manifest.read_text().splitlines() if ln.strip()]
+    (OUT / "two_stage_param_names.txt").write_text("\n".join(names) + "\n")
+    print("wrote", sorted(p.name for p in OUT.glob("*.npz")), "two_stage_param_names.txt")
 
 
 if __name__ == "__main__":
