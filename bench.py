@@ -228,6 +228,11 @@ def run_gpu_arm(args):
             ms = float(t.item())
         return ms
 
+    if args.only == "pixel_stage":
+        res = pixel_stage_bench(torch, dev, iters=args.steps)
+        if rank == 0:
+            print(json.dumps({"only": args.only, "result": res}))
+        return
     if args.only == "halo_kernels":
         res = halo_kernels_bench(torch, dev, iters=args.steps)
         if rank == 0:
@@ -542,6 +547,88 @@ def halo_kernels_bench(torch, dev, iters=5):
                     "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm_peak})
     run.close()
     return out
+
+
+PIXEL = dict(depth=24, height=256, width=256, patch=4, backbone_dim=1024, dim=128, heads=2,
+             kernel=(9, 9, 9), qk_norm=True)
+
+
+def pixel_stage_bench(torch, dev, iters=3):
+    """One AdaLN pixel block of the two-stage model at the production channel widths (backbone
+    1024, pixel 128, 2 heads, 9x9x9 attention, bilinear_dw conditioning) on one 24 x 256 x 256
+    pixel tile (1.57 M pixel tokens, 98 k backbone tokens): every kernel of the block alone, with
+    its algorithmic bytes or flops, then the whole block (modulation + forward)."""
+    from strata_b200 import ops
+    from strata_b200.ops import EPI_GELU
+    from strata_b200.pixel import StrataPixel3DBlock
+    tf_peak, hbm_peak, _ = measured_peaks()
+    c = PIXEL
+    D, H, W, f, Cb, C = c["depth"], c["height"], c["width"], c["patch"], c["backbone_dim"], c["dim"]
+    M = D * H * W
+    torch.manual_seed(0)
+    blk = StrataPixel3DBlock(C, c["heads"], 4.0, c["qk_norm"], False, c["kernel"], Cb, adaln=True)
+    blk.mlp.layers[1].approximate = "tanh"
+    with torch.no_grad():
+        blk.adaln_bilinear_dw_proj.weight.normal_(0, 0.5 / Cb ** 0.5)
+    blk = blk.to(dev).eval()
+    wts = blk.device_weights()
+    s = torch.randn(1, D, H // f, W // f, Cb, device=dev).bfloat16()
+    x = torch.randn(M, C, device=dev).bfloat16()
+    n = min(M, 1 << 18)
+    cond = torch.empty(n, Cb, device=dev, dtype=torch.bfloat16)
+    with torch.inference_mode():
+        mod = blk.modulation(s, f)
+        sl = lambda i: mod[:, i * C:(i + 1) * C]
+        xn = ops.adaln_rows(x, shift=sl(0), scale=sl(1))
+        qkv = ops.linear(xn, wts["w_qkv"], wts["b_qkv"])
+        q6 = qkv.view(1, D, H, W, 3, c["heads"], 64)
+        attn = ops.na3d(q6[:, :, :, :, 0], q6[:, :, :, :, 1], q6[:, :, :, :, 2], c["kernel"]).view(-1, C)
+        h = ops.linear(xn, wts["w_fc1"], wts["b_fc1"], EPI_GELU)
+        y = ops.linear(attn, wts["w_proj"], wts["b_proj"])
+        kd, kh, kw = c["kernel"]
+        items = [
+            ("adaln_cond (2^18 pixels)", lambda: ops.adaln_cond(s, wts["w_dw"], wts["b_dw"], f, 0, n, out=cond),
+             "hbm", n * Cb * 2),
+            ("modulation GEMM (2^18 pixels)", lambda: ops.linear(cond, wts["w_mod"], wts["b_mod"], out=mod[:n]),
+             "tensor", 2.0 * n * Cb * 6 * C),
+            ("ln_modulate", lambda: ops.adaln_rows(x, shift=sl(0), scale=sl(1)), "hbm", M * C * 2 * 4),
+            ("qkv GEMM", lambda: ops.linear(xn, wts["w_qkv"], wts["b_qkv"], out=qkv), "hbm", M * C * 2 * 4),
+            ("qk_norm_rows", lambda: ops.qk_norm_rows_(qkv, C), "hbm", M * C * 2 * 4),
+            ("na3d 9x9x9", lambda: ops.na3d(q6[:, :, :, :, 0], q6[:, :, :, :, 1], q6[:, :, :, :, 2],
+                                             c["kernel"]), "tensor", 4.0 * M * C * kd * kh * kw),
+            ("proj GEMM", lambda: ops.linear(attn, wts["w_proj"], wts["b_proj"], out=y), "hbm", M * C * 2 * 2),
+            ("gated residual + ln_modulate", lambda: ops.adaln_rows(x, y=y, gate=sl(2), shift=sl(3), scale=sl(4)),
+             "hbm", M * C * 2 * 7),
+            ("fc1 GEMM + GELU", lambda: ops.linear(xn, wts["w_fc1"], wts["b_fc1"], EPI_GELU, out=h),
+             "hbm", M * C * 2 * 5),
+            ("fc2 GEMM", lambda: ops.linear(h, wts["w_fc2"], wts["b_fc2"], out=y), "hbm", M * C * 2 * 5),
+            ("gated residual", lambda: ops.adaln_rows(x, y=y, gate=sl(5), norm=False), "hbm", M * C * 2 * 4),
+            ("whole block (modulation + forward)", lambda: blk(x, (D, H, W), blk.modulation(s, f), 1),
+             None, 0),
+        ]
+        out = []
+        for name, fn, bound, work in items:
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            r = {"name": name, "ms": ms}
+            if bound == "hbm":
+                r.update(bound="hbm", gbs=work / (ms * 1e-3) / 1e9,
+                         frac=work / (ms * 1e-3) / 1e9 / hbm_peak)
+            elif bound == "tensor":
+                r.update(bound="tensor", tflops=work / (ms * 1e-3) / 1e12,
+                         frac=work / (ms * 1e-3) / 1e12 / tf_peak)
+            else:
+                r.update(pixel_tokens_per_s=M / (ms * 1e-3))
+            out.append(r)
+    return {"config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in c.items()},
+            "pixel_tokens": M, "kernels": out}
 
 
 def kernel_breakdown(torch, ops, x, weights, cs, grid, heads, kernel, hidden, iters=5,

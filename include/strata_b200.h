@@ -251,10 +251,16 @@ int strata_qk_norm_rows_bf16(void* qkv, int64_t ld, int64_t M, int C, float eps,
  * tests/regression_data/pixeldit_*.param_order.txt:253-254): backbone tokens [B, D, h, w, Cb]
  * bf16 are upsampled bilinearly by `factor` in h and w (half-pixel centres), convolved depthwise
  * with a ks x ks kernel (zero padding), biased and passed through the tanh GELU; rows
- * row0 .. row0 + n_rows of the flattened (b, d, y, x) pixel order are written as bf16 [n_rows, Cb]. */
+ * row0 .. row0 + n_rows of the flattened (b, d, y, x) pixel order are written as bf16 [n_rows, Cb]
+ * (fastest when the range covers whole groups of `factor` image rows). */
 int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int Cb, int factor,
                            const float* w_dw, const float* b_dw, int ks, int64_t row0,
-                           int64_t n_rows, void* out, void* stream);
+                           int64_t n_rows, void* out, float* table_ws, void* stream);
+
+/* Floats of device scratch (`table_ws` above) that let strata_adaln_cond_bf16 fold upsample and
+ * convolution into one 3 x 3 token stencil per pixel phase (factor >= 4, ks <= 5, Cb % 32 == 0);
+ * 0 when the geometry has no such form. With table_ws NULL every pixel is evaluated tap by tap. */
+int64_t strata_adaln_cond_table_floats(int Cb, int factor, int ks);
 
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and

@@ -75,7 +75,8 @@ _SIGNATURES = {
     "strata_qk_norm_rows_bf16": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_void_p]),
     "strata_adaln_cond_bf16": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
-                                       c_void_p]),
+                                       c_void_p, c_void_p]),
+    "strata_adaln_cond_table_floats": (c_int64, [c_int, c_int, c_int]),
     "strata_halo_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p]),
     "strata_ipc_alloc": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
     "strata_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),

@@ -206,12 +206,54 @@ struct AdalnCondParams {
   int D, h, w, Cb, factor, ks;
 };
 
-// One thread: one pixel x 8 channels. Every conv tap is an upsampled value, i.e. four token
-// reads; taps outside the H x W image are the convolution's zero padding.
+// Direct evaluation of one pixel x 8 channels: every conv tap is an upsampled value, i.e. four
+// token reads; taps outside the H x W image are the convolution's zero padding.
+__device__ __forceinline__ void cond_direct_pixel(const AdalnCondParams& p, const uint4* base,
+                                                  int nvec, int H, int W, int y, int x, int cv,
+                                                  float (&acc)[8]) {
+  const int r = p.ks >> 1;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = p.bdw ? __ldg(p.bdw + cv * 8 + c) : 0.f;
+  for (int dy = -r; dy <= r; ++dy) {
+    const int py = y + dy;
+    if (py < 0 || py >= H) continue;
+    int r0, r1;
+    float ly0, ly1;
+    bilinear_tap(py, p.factor, p.h, r0, r1, ly0, ly1);
+    for (int dx = -r; dx <= r; ++dx) {
+      const int px = x + dx;
+      if (px < 0 || px >= W) continue;
+      int c0, c1;
+      float lx0, lx1;
+      bilinear_tap(px, p.factor, p.w, c0, c1, lx0, lx1);
+      float a[8], b[8], c[8], d[8];
+      unpack8(__ldg(base + (static_cast<long long>(r0) * p.w + c0) * nvec), a);
+      unpack8(__ldg(base + (static_cast<long long>(r0) * p.w + c1) * nvec), b);
+      unpack8(__ldg(base + (static_cast<long long>(r1) * p.w + c0) * nvec), c);
+      unpack8(__ldg(base + (static_cast<long long>(r1) * p.w + c1) * nvec), d);
+      const int tap = (dy + r) * p.ks + (dx + r);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const float u = ly0 * (lx0 * a[ch] + lx1 * b[ch]) + ly1 * (lx0 * c[ch] + lx1 * d[ch]);
+        acc[ch] = fmaf(__ldg(p.wdw + (cv * 8 + ch) * p.ks * p.ks + tap), u, acc[ch]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void gelu8(float (&acc)[8]) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    const float v = acc[ch];
+    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    acc[ch] = 0.5f * v * (1.0f + fast_tanh(u));
+  }
+}
+
+// One thread: one pixel x 8 channels, direct evaluation (any factor and kernel size).
 __global__ void __launch_bounds__(256) adaln_cond_kernel(const AdalnCondParams p) {
   const int nvec = p.Cb >> 3;
   const int H = p.h * p.factor, W = p.w * p.factor;
-  const int r = p.ks >> 1;
   const long long total = p.n_rows * nvec;
   for (long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -222,53 +264,204 @@ __global__ void __launch_bounds__(256) adaln_cond_kernel(const AdalnCondParams p
     const long long plane = pix / (static_cast<long long>(W) * H);   // b * D + d
     const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
     float acc[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] = p.bdw ? __ldg(p.bdw + cv * 8 + c) : 0.f;
-    for (int dy = -r; dy <= r; ++dy) {
-      const int py = y + dy;
-      if (py < 0 || py >= H) continue;
-      int r0, r1;
-      float ly0, ly1;
-      bilinear_tap(py, p.factor, p.h, r0, r1, ly0, ly1);
-      for (int dx = -r; dx <= r; ++dx) {
-        const int px = x + dx;
-        if (px < 0 || px >= W) continue;
-        int c0, c1;
-        float lx0, lx1;
-        bilinear_tap(px, p.factor, p.w, c0, c1, lx0, lx1);
-        float a[8], b[8], c[8], d[8];
-        unpack8(__ldg(base + (static_cast<long long>(r0) * p.w + c0) * nvec), a);
-        unpack8(__ldg(base + (static_cast<long long>(r0) * p.w + c1) * nvec), b);
-        unpack8(__ldg(base + (static_cast<long long>(r1) * p.w + c0) * nvec), c);
-        unpack8(__ldg(base + (static_cast<long long>(r1) * p.w + c1) * nvec), d);
-        const int tap = (dy + r) * p.ks + (dx + r);
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const float u = ly0 * (lx0 * a[ch] + lx1 * b[ch]) + ly1 * (lx0 * c[ch] + lx1 * d[ch]);
-          acc[ch] = fmaf(__ldg(p.wdw + (cv * 8 + ch) * p.ks * p.ks + tap), u, acc[ch]);
-        }
-      }
-    }
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const float v = acc[ch];
-      const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-      acc[ch] = 0.5f * v * (1.0f + tanhf(u));
-    }
+    cond_direct_pixel(p, base, nvec, H, W, y, x, cv, acc);
+    gelu8(acc);
     reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
   }
 }
 
-inline int launch_adaln_cond(const AdalnCondParams& p, int sm_count, cudaStream_t stream) {
+// Upsample followed by the depthwise conv is linear in the tokens: away from the image border
+// a pixel of the factor x factor cell of token (R, Cc) reads the 3 x 3 tokens around (R, Cc)
+// with weights that depend only on its position inside the cell (the phase) and the channel.
+// This kernel folds the ks x ks taps into that table, [factor^2][9][Cb] fp32. Valid for
+// factor >= 4 and ks <= 5 (then every tap of every phase falls on rows R-1 .. R+1).
+__global__ void adaln_cond_table_kernel(const float* __restrict__ wdw, int Cb, int factor, int ks,
+                                        float* __restrict__ table) {
+  const int n = factor * factor * Cb;
+  const int r = ks >> 1;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
+    const int ch = t % Cb;
+    const int phase = t / Cb;
+    const int phy = phase / factor, phx = phase % factor;
+    float acc[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) acc[k] = 0.f;
+    for (int dy = -r; dy <= r; ++dy) {
+      int r0, r1;
+      float ly0, ly1;
+      bilinear_tap(factor + phy + dy, factor, 4, r0, r1, ly0, ly1);   // cell R = 1 of a 4-row grid
+      for (int dx = -r; dx <= r; ++dx) {
+        int c0, c1;
+        float lx0, lx1;
+        bilinear_tap(factor + phx + dx, factor, 4, c0, c1, lx0, lx1);
+        const float wt = wdw[ch * ks * ks + (dy + r) * ks + (dx + r)];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) {
+          const int j = k / 3, i = k % 3;
+          const float wy = (j == r0 ? ly0 : 0.f) + (j == r1 ? ly1 : 0.f);
+          const float wx = (i == c0 ? lx0 : 0.f) + (i == c1 ? lx1 : 0.f);
+          acc[k] = fmaf(wt, wy * wx, acc[k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 9; ++k) table[(phase * 9 + k) * Cb + ch] = acc[k];
+  }
+}
+
+// One thread: one cell (factor x factor pixels of one backbone token) x 8 channels. A warp
+// holds 8 consecutive cells x 4 consecutive channel vectors, so a table read is one 128-byte
+// line shared by the 8 cells and a token read / row write is 64 contiguous bytes per cell.
+// Interior cells only; the frame of border cells is adaln_cond_frame_kernel's.
+__global__ void __launch_bounds__(256)
+adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table) {
+  const int nvec = p.Cb >> 3;
+  const int ncvg = nvec >> 2;
+  const int f = p.factor;
+  const int H = p.h * f, W = p.w * f;
+  const long long gR0 = p.row0 / W / f;
+  const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
+  const long long n_cells = (gR1 - gR0 + 1) * p.w;
+  const long long n_cell_groups = (n_cells + 7) >> 3;
+  const long long total_warps = n_cell_groups * ncvg;
+  const int lane = threadIdx.x & 31;
+  const long long warps_in_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long wg = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+       wg < total_warps; wg += warps_in_grid) {
+    const int cvg = static_cast<int>(wg / n_cell_groups);
+    const long long cell = (wg % n_cell_groups) * 8 + (lane >> 2);
+    if (cell >= n_cells) continue;
+    const int cv = cvg * 4 + (lane & 3);
+    const long long gR = gR0 + cell / p.w;
+    const int Cc = static_cast<int>(cell % p.w);
+    const long long plane = gR / p.h;
+    const int R = static_cast<int>(gR % p.h);
+    const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
+    // cells on the image border belong to adaln_cond_frame_kernel
+    if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
+    float t[9][8];
+    float bias[8];
+#pragma unroll
+    for (int k = 0; k < 9; ++k)
+      unpack8(__ldg(base + (static_cast<long long>(R - 1 + k / 3) * p.w + (Cc - 1 + k % 3)) * nvec),
+              t[k]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) bias[c] = p.bdw ? __ldg(p.bdw + cv * 8 + c) : 0.f;
+    for (int phy = 0; phy < f; ++phy) {
+      const int y = R * f + phy;
+      for (int phx = 0; phx < f; ++phx) {
+        const int x = Cc * f + phx;
+        const long long pix = (plane * H + y) * W + x;
+        if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
+        float acc[8];
+        const float4* tb =
+            reinterpret_cast<const float4*>(table + static_cast<long long>(phy * f + phx) * 9 * p.Cb) +
+            cv * 2;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = bias[c];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) {
+          const float4 w0 = __ldg(tb + k * (p.Cb >> 2));
+          const float4 w1 = __ldg(tb + k * (p.Cb >> 2) + 1);
+          acc[0] = fmaf(w0.x, t[k][0], acc[0]); acc[1] = fmaf(w0.y, t[k][1], acc[1]);
+          acc[2] = fmaf(w0.z, t[k][2], acc[2]); acc[3] = fmaf(w0.w, t[k][3], acc[3]);
+          acc[4] = fmaf(w1.x, t[k][4], acc[4]); acc[5] = fmaf(w1.y, t[k][5], acc[5]);
+          acc[6] = fmaf(w1.z, t[k][6], acc[6]); acc[7] = fmaf(w1.w, t[k][7], acc[7]);
+        }
+        gelu8(acc);
+        reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
+      }
+    }
+  }
+}
+
+// The frame of border cells (the outermost `factor` pixels on every side of each H x W plane),
+// tap by tap: one thread per (frame pixel, 8 channels), frame pixels enumerated densely - top
+// band, bottom band, then the left and right strips of the rows in between.
+__global__ void __launch_bounds__(256) adaln_cond_frame_kernel(const AdalnCondParams p) {
+  const int nvec = p.Cb >> 3;
+  const int f = p.factor;
+  const int H = p.h * f, W = p.w * f;
+  const long long HW = static_cast<long long>(H) * W;
+  const long long plane0 = p.row0 / HW;
+  const long long plane1 = (p.row0 + p.n_rows - 1) / HW;
+  const int band = f * W;                                   // pixels of the top (or bottom) band
+  const int mid_rows = H > 2 * f ? H - 2 * f : 0;
+  const int strip_w = W >= 2 * f ? 2 * f : W;               // left + right strip of a middle row
+  const long long per_plane =
+      (H >= 2 * f ? 2LL * band : HW) + static_cast<long long>(mid_rows) * strip_w;
+  const long long total = (plane1 - plane0 + 1) * per_plane * nvec;
+  for (long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cv = static_cast<int>(t % nvec);
+    const long long fp = t / nvec;
+    const long long plane = plane0 + fp / per_plane;
+    long long k = fp % per_plane;
+    int y, x;
+    if (H < 2 * f) {
+      y = static_cast<int>(k / W); x = static_cast<int>(k % W);
+    } else if (k < band) {
+      y = static_cast<int>(k / W); x = static_cast<int>(k % W);
+    } else if (k < 2LL * band) {
+      k -= band;
+      y = H - f + static_cast<int>(k / W); x = static_cast<int>(k % W);
+    } else {
+      k -= 2LL * band;
+      y = f + static_cast<int>(k / strip_w);
+      const int sx = static_cast<int>(k % strip_w);
+      x = (W >= 2 * f && sx >= f) ? W - 2 * f + sx : sx;
+    }
+    const long long pix = plane * HW + static_cast<long long>(y) * W + x;
+    if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
+    const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
+    float acc[8];
+    cond_direct_pixel(p, base, nvec, H, W, y, x, cv, acc);
+    gelu8(acc);
+    reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
+  }
+}
+
+// Number of floats of the table the cell kernel needs, or 0 when the geometry takes the
+// direct kernel (small factor, wide conv kernel, channel count not a multiple of 32).
+inline long long adaln_cond_table_floats(int Cb, int factor, int ks) {
+  if (factor < 4 || ks > 5 || Cb % 32 != 0) return 0;
+  return static_cast<long long>(factor) * factor * 9 * Cb;
+}
+
+// table: device scratch of adaln_cond_table_floats() floats, or null for the direct kernel.
+inline int launch_adaln_cond(const AdalnCondParams& p, float* table, int sm_count,
+                             cudaStream_t stream) {
   if (p.Cb % 8 != 0 || p.Cb <= 0 || p.factor <= 0 || p.ks <= 0 || (p.ks & 1) == 0 || p.ks > 9 ||
       p.D <= 0 || p.h <= 0 || p.w <= 0 || p.row0 < 0)
     return -2;
   if (p.n_rows <= 0) return 0;
-  const long long total = p.n_rows * (p.Cb / 8);
-  long long blocks = (total + 255) / 256;
-  const long long cap = static_cast<long long>(sm_count) * 32;
-  if (blocks > cap) blocks = cap;
-  adaln_cond_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+  if (table != nullptr && adaln_cond_table_floats(p.Cb, p.factor, p.ks) > 0) {
+    const int n = p.factor * p.factor * p.Cb;
+    adaln_cond_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(p.wdw, p.Cb, p.factor, p.ks, table);
+    const long long W = static_cast<long long>(p.w) * p.factor;
+    const long long cell_rows = (p.row0 + p.n_rows - 1) / W / p.factor - p.row0 / W / p.factor + 1;
+    const long long warps = (cell_rows * p.w + 7) / 8 * (p.Cb / 32);
+    long long blocks = (warps + 7) / 8;
+    const long long cap = static_cast<long long>(sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    if (p.h > 2 && p.w > 2)
+      adaln_cond_cells_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, table);
+    {
+      const long long H = static_cast<long long>(p.h) * p.factor;
+      const long long planes = (p.row0 + p.n_rows - 1) / (H * W) - p.row0 / (H * W) + 1;
+      const long long frame = H * W - (p.h > 2 && p.w > 2 ? (H - 2 * p.factor) * (W - 2 * p.factor) : 0);
+      long long fb = (planes * frame * (p.Cb / 8) + 255) / 256;
+      const long long fcap = static_cast<long long>(sm_count) * 32;
+      if (fb > fcap) fb = fcap;
+      adaln_cond_frame_kernel<<<static_cast<int>(fb), 256, 0, stream>>>(p);
+    }
+  } else {
+    const long long total = p.n_rows * (p.Cb / 8);
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count) * 32;
+    if (blocks > cap) blocks = cap;
+    adaln_cond_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }

@@ -612,9 +612,13 @@ int strata_qk_norm_rows_bf16(void* qkv, int64_t ld, int64_t M, int C, float eps,
   return r == -2 ? STRATA_ERR_ARG : r;
 }
 
+int64_t strata_adaln_cond_table_floats(int Cb, int factor, int ks) {
+  return adaln_cond_table_floats(Cb, factor, ks);
+}
+
 int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int Cb, int factor,
                            const float* w_dw, const float* b_dw, int ks, int64_t row0,
-                           int64_t n_rows, void* out, void* stream) {
+                           int64_t n_rows, void* out, float* table_ws, void* stream) {
   const int sms = current_sm_count();
   if (sms <= 0) return STRATA_ERR_NO_DEVICE;
   if (n_rows == 0) return STRATA_OK;
@@ -629,7 +633,8 @@ int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int C
   p.out = static_cast<__nv_bfloat16*>(out);
   p.row0 = row0; p.n_rows = n_rows;
   p.D = D; p.h = h; p.w = w; p.Cb = Cb; p.factor = factor; p.ks = ks;
-  int r = launch_adaln_cond(p, sms, as_stream(stream));
+  if (table_ws && !aligned16(table_ws)) return STRATA_ERR_ARG;
+  int r = launch_adaln_cond(p, table_ws, sms, as_stream(stream));
   return r == -2 ? STRATA_ERR_ARG : r;
 }
 

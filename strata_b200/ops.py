@@ -414,10 +414,12 @@ def qk_norm_rows_(qkv: torch.Tensor, C: int, eps: float = 1e-6) -> torch.Tensor:
 
 
 def adaln_cond(tokens: torch.Tensor, w_dw: torch.Tensor, b_dw: torch.Tensor | None, factor: int,
-               row0: int = 0, n_rows: int | None = None, out: torch.Tensor | None = None):
+               row0: int = 0, n_rows: int | None = None, out: torch.Tensor | None = None,
+               direct: bool = False):
     """GELU(depthwise conv(bilinear upsample(tokens)) + bias) as bf16 rows. tokens: bf16
     [B, D, h, w, Cb] contiguous; w_dw fp32 [Cb, ks, ks]; rows row0 .. row0+n_rows of the
-    flattened (b, d, y, x) pixels at resolution (h*factor, w*factor)."""
+    flattened (b, d, y, x) pixels at resolution (h*factor, w*factor). direct=True evaluates
+    every pixel tap by tap instead of through the folded 3x3 stencil table."""
     _require_cuda_bf16(tokens, "tokens")
     if tokens.dim() != 5 or not tokens.is_contiguous():
         raise ValueError("tokens must be contiguous [B, D, h, w, Cb]")
@@ -434,9 +436,13 @@ def adaln_cond(tokens: torch.Tensor, w_dw: torch.Tensor, b_dw: torch.Tensor | No
         out = torch.empty((n_rows, Cb), dtype=torch.bfloat16, device=tokens.device)
     elif out.shape != (n_rows, Cb) or not out.is_contiguous() or out.dtype != torch.bfloat16:
         raise ValueError("out must be contiguous bf16 [n_rows, Cb]")
+    lib = _lib.load()
+    n_table = 0 if direct else int(lib.strata_adaln_cond_table_floats(Cb, int(factor), ks))
+    table = torch.empty(n_table, dtype=torch.float32, device=tokens.device) if n_table else None
     with torch.cuda.device(tokens.device):
-        _lib.check(_lib.load().strata_adaln_cond_bf16(
+        _lib.check(lib.strata_adaln_cond_bf16(
             tokens.data_ptr(), B, D, h, w, Cb, int(factor), w_dw.data_ptr(),
             None if b_dw is None else b_dw.data_ptr(), ks, int(row0), int(n_rows), out.data_ptr(),
-            _stream_ptr(tokens)), "strata_adaln_cond_bf16")
+            None if table is None else table.data_ptr(), _stream_ptr(tokens)),
+            "strata_adaln_cond_bf16")
     return out

@@ -60,7 +60,9 @@ def test_qk_norm_rows():
 
 
 @pytest.mark.parametrize("shape,factor,ks", [((1, 2, 5, 6, 64), 4, 5), ((2, 1, 4, 4, 128), 2, 5),
-                                             ((1, 3, 3, 7, 64), 4, 3), ((1, 2, 6, 5, 64), 1, 5)])
+                                             ((1, 3, 3, 7, 64), 4, 3), ((1, 2, 6, 5, 64), 1, 5),
+                                             ((2, 2, 9, 11, 1024), 4, 5), ((1, 1, 5, 4, 96), 8, 5),
+                                             ((1, 2, 4, 6, 72), 4, 5)])
 def test_adaln_cond_matches_oracle(shape, factor, ks):
     from strata_b200 import ops
     g = torch.Generator().manual_seed(sum(shape) + factor)
@@ -72,6 +74,9 @@ def test_adaln_cond_matches_oracle(shape, factor, ks):
     got = ops.adaln_cond(tok, w.cuda(), b.cuda(), factor)
     assert got.shape == want.shape
     assert rel_max_err(got, want) < 1e-2
+    # the tap-by-tap evaluation (the only one for small factors) agrees as well
+    direct = ops.adaln_cond(tok, w.cuda(), b.cuda(), factor, direct=True)
+    assert rel_max_err(direct, want) < 1e-2
     # a row range gives the same rows
     part = ops.adaln_cond(tok, w.cuda(), b.cuda(), factor, row0=17, n_rows=40)
     assert torch.equal(part, got[17:57])
