@@ -270,30 +270,48 @@ __global__ void __launch_bounds__(256) adaln_cond_kernel(const AdalnCondParams p
   }
 }
 
-// Upsample followed by the depthwise conv is linear in the tokens: away from the image border
-// a pixel of the factor x factor cell of token (R, Cc) reads the 3 x 3 tokens around (R, Cc)
-// with weights that depend only on its position inside the cell (the phase) and the channel.
-// This kernel folds the ks x ks taps into that table, [factor^2][9][Cb] fp32. Valid for
-// factor >= 4 and ks <= 5 (then every tap of every phase falls on rows R-1 .. R+1).
+// Upsample followed by the depthwise conv is linear in the tokens: a pixel of the
+// factor x factor cell of token (R, Cc) reads a 3 x 3 block of tokens with weights that depend
+// only on the channel and on the pixel's position class along each axis - 3 * factor classes:
+// the `factor` pixels of the first cell (clamped upsample source, conv taps cut by the zero
+// padding), the `factor` phases of an interior cell, the `factor` pixels of the last cell.
+// The token block starts at row R-1 (0 for the first cell, h-3 for the last), same for columns.
+// This kernel folds the ks x ks taps into that table, [3f][3f][9][Cb] fp32. Valid for
+// factor >= 4, ks <= 5 and at least 3 cells per axis (then every tap falls inside the block).
+__device__ __forceinline__ void cond_class_ref(int cls, int f, int& pos, int& base) {
+  // representative pixel position and token-block base on a reference axis of 4 cells
+  if (cls < f) { pos = cls; base = 0; }
+  else if (cls < 2 * f) { pos = cls; base = 0; }             // cell 1, phase cls - f
+  else { pos = 3 * f + (cls - 2 * f); base = 1; }            // cell 3 (last)
+}
+
 __global__ void adaln_cond_table_kernel(const float* __restrict__ wdw, int Cb, int factor, int ks,
                                         float* __restrict__ table) {
-  const int n = factor * factor * Cb;
+  const int ncls = 3 * factor;
+  const int n = ncls * ncls * Cb;
   const int r = ks >> 1;
+  const int n_ref = 4 * factor;
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
     const int ch = t % Cb;
-    const int phase = t / Cb;
-    const int phy = phase / factor, phx = phase % factor;
+    const int cls = t / Cb;
+    int y, rb, x, cb;
+    cond_class_ref(cls / ncls, factor, y, rb);
+    cond_class_ref(cls % ncls, factor, x, cb);
     float acc[9];
 #pragma unroll
     for (int k = 0; k < 9; ++k) acc[k] = 0.f;
     for (int dy = -r; dy <= r; ++dy) {
+      if (y + dy < 0 || y + dy >= n_ref) continue;
       int r0, r1;
       float ly0, ly1;
-      bilinear_tap(factor + phy + dy, factor, 4, r0, r1, ly0, ly1);   // cell R = 1 of a 4-row grid
+      bilinear_tap(y + dy, factor, 4, r0, r1, ly0, ly1);
+      r0 -= rb; r1 -= rb;
       for (int dx = -r; dx <= r; ++dx) {
+        if (x + dx < 0 || x + dx >= n_ref) continue;
         int c0, c1;
         float lx0, lx1;
-        bilinear_tap(factor + phx + dx, factor, 4, c0, c1, lx0, lx1);
+        bilinear_tap(x + dx, factor, 4, c0, c1, lx0, lx1);
+        c0 -= cb; c1 -= cb;
         const float wt = wdw[ch * ks * ks + (dy + r) * ks + (dx + r)];
 #pragma unroll
         for (int k = 0; k < 9; ++k) {
@@ -305,127 +323,139 @@ __global__ void adaln_cond_table_kernel(const float* __restrict__ wdw, int Cb, i
       }
     }
 #pragma unroll
-    for (int k = 0; k < 9; ++k) table[(phase * 9 + k) * Cb + ch] = acc[k];
+    for (int k = 0; k < 9; ++k) table[(static_cast<long long>(cls) * 9 + k) * Cb + ch] = acc[k];
+  }
+}
+
+// acc = bias + sum_k w[k] * t[k] over the 3 x 3 token block; tb points at this thread's 8
+// channels of table entry k = 0, entries `stride` float4 apart.
+__device__ __forceinline__ void cond_stencil(const float4* tb, int stride, const uint4 (&tk)[9],
+                                             const float* bdw, int cv, float (&acc)[8]) {
+  if (bdw != nullptr) {
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bdw) + cv * 2);
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(bdw) + cv * 2 + 1);
+    acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w;
+    acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  }
+#pragma unroll
+  for (int k = 0; k < 9; ++k) {
+    const float4 w0 = tb[k * stride];
+    const float4 w1 = tb[k * stride + 1];
+    float t[8];
+    unpack8(tk[k], t);
+    acc[0] = fmaf(w0.x, t[0], acc[0]); acc[1] = fmaf(w0.y, t[1], acc[1]);
+    acc[2] = fmaf(w0.z, t[2], acc[2]); acc[3] = fmaf(w0.w, t[3], acc[3]);
+    acc[4] = fmaf(w1.x, t[4], acc[4]); acc[5] = fmaf(w1.y, t[5], acc[5]);
+    acc[6] = fmaf(w1.z, t[6], acc[6]); acc[7] = fmaf(w1.w, t[7], acc[7]);
   }
 }
 
 // One thread: one cell (factor x factor pixels of one backbone token) x 8 channels. A warp
-// holds 8 consecutive cells x 4 consecutive channel vectors, so a table read is one 128-byte
-// line shared by the 8 cells and a token read / row write is 64 contiguous bytes per cell.
-// Interior cells only; the frame of border cells is adaln_cond_frame_kernel's.
-__global__ void __launch_bounds__(256)
+// holds 8 consecutive cells x 4 consecutive channel vectors (32 channels), so a token read and
+// a row write are 64 contiguous bytes per cell. A block works on 256 consecutive cells of one
+// 32-channel group at a time and keeps the interior-phase slab of that group's table
+// ([factor^2][9][32] fp32) in shared memory; the cells on the image border (a launch of their
+// own) read their classes' entries from global memory.
+constexpr int COND_CELLS_PER_ITEM = 256;
+
+#ifndef COND_CELLS_MIN_BLOCKS
+#define COND_CELLS_MIN_BLOCKS 2
+#endif
+// BORDER = false: interior cells (the others are skipped); BORDER = true: the cells of the
+// outermost ring of every plane, enumerated densely so that a warp does not mix the two paths.
+template <bool BORDER>
+__global__ void __launch_bounds__(256, COND_CELLS_MIN_BLOCKS)
 adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table) {
+  extern __shared__ __align__(16) float slab[];
   const int nvec = p.Cb >> 3;
   const int ncvg = nvec >> 2;
   const int f = p.factor;
+  const int ncls = 3 * f;
   const int H = p.h * f, W = p.w * f;
   const long long gR0 = p.row0 / W / f;
   const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
-  const long long n_cells = (gR1 - gR0 + 1) * p.w;
-  const long long n_cell_groups = (n_cells + 7) >> 3;
-  const long long total_warps = n_cell_groups * ncvg;
+  const long long ring = 2LL * p.w + 2LL * (p.h - 2);        // border cells of one plane
+  const long long plane0 = gR0 / p.h;
+  const long long n_cells = BORDER ? (gR1 / p.h - plane0 + 1) * ring : (gR1 - gR0 + 1) * p.w;
+  const long long n_chunks = (n_cells + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM;
+  const long long n_items = n_chunks * ncvg;
   const int lane = threadIdx.x & 31;
-  const long long warps_in_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  for (long long wg = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-       wg < total_warps; wg += warps_in_grid) {
-    const int cvg = static_cast<int>(wg / n_cell_groups);
-    const long long cell = (wg % n_cell_groups) * 8 + (lane >> 2);
-    if (cell >= n_cells) continue;
+  const int warp = threadIdx.x >> 5;
+  const int slab_vec = f * f * 9 * 8;                      // float4 count of a slab
+  for (long long item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int cvg = static_cast<int>(item / n_chunks);
+    const long long cell0 = (item % n_chunks) * COND_CELLS_PER_ITEM;
+    if constexpr (!BORDER) {
+      __syncthreads();                                     // previous item's readers are done
+      for (int v = threadIdx.x; v < slab_vec; v += blockDim.x) {
+        const int e = v >> 3;                              // (phase, k)
+        const int phase = e / 9, k = e - phase * 9;
+        const int cls = (f + phase / f) * ncls + (f + phase % f);
+        reinterpret_cast<float4*>(slab)[v] = __ldg(
+            reinterpret_cast<const float4*>(table + (static_cast<long long>(cls) * 9 + k) * p.Cb +
+                                            cvg * 32) + (v & 7));
+      }
+      __syncthreads();
+    }
     const int cv = cvg * 4 + (lane & 3);
-    const long long gR = gR0 + cell / p.w;
-    const int Cc = static_cast<int>(cell % p.w);
-    const long long plane = gR / p.h;
-    const int R = static_cast<int>(gR % p.h);
-    const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
-    // cells on the image border belong to adaln_cond_frame_kernel
-    if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
-    float t[9][8];
-    float bias[8];
+    for (int pass = 0; pass < COND_CELLS_PER_ITEM / 64; ++pass) {
+      const long long cell = cell0 + pass * 64 + warp * 8 + (lane >> 2);
+      if (cell >= n_cells) continue;
+      long long plane;
+      int R, Cc;
+      if constexpr (BORDER) {
+        plane = plane0 + cell / ring;
+        long long k = cell % ring;
+        if (k < p.w) { R = 0; Cc = static_cast<int>(k); }
+        else if (k < 2LL * p.w) { R = p.h - 1; Cc = static_cast<int>(k - p.w); }
+        else { k -= 2LL * p.w; R = 1 + static_cast<int>(k >> 1); Cc = (k & 1) ? p.w - 1 : 0; }
+      } else {
+        const long long gR = gR0 + cell / p.w;
+        Cc = static_cast<int>(cell % p.w);
+        plane = gR / p.h;
+        R = static_cast<int>(gR % p.h);
+        if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
+      }
+      const int rb = R == 0 ? 0 : (R == p.h - 1 ? p.h - 3 : R - 1);
+      const int cb = Cc == 0 ? 0 : (Cc == p.w - 1 ? p.w - 3 : Cc - 1);
+      const int ycls0 = R == 0 ? 0 : (R == p.h - 1 ? 2 * f : f);
+      const int xcls0 = Cc == 0 ? 0 : (Cc == p.w - 1 ? 2 * f : f);
+      const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
+      uint4 tk[9];
 #pragma unroll
-    for (int k = 0; k < 9; ++k)
-      unpack8(__ldg(base + (static_cast<long long>(R - 1 + k / 3) * p.w + (Cc - 1 + k % 3)) * nvec),
-              t[k]);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) bias[c] = p.bdw ? __ldg(p.bdw + cv * 8 + c) : 0.f;
-    for (int phy = 0; phy < f; ++phy) {
-      const int y = R * f + phy;
-      for (int phx = 0; phx < f; ++phx) {
-        const int x = Cc * f + phx;
-        const long long pix = (plane * H + y) * W + x;
-        if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
-        float acc[8];
-        const float4* tb =
-            reinterpret_cast<const float4*>(table + static_cast<long long>(phy * f + phx) * 9 * p.Cb) +
-            cv * 2;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) acc[c] = bias[c];
-#pragma unroll
-        for (int k = 0; k < 9; ++k) {
-          const float4 w0 = __ldg(tb + k * (p.Cb >> 2));
-          const float4 w1 = __ldg(tb + k * (p.Cb >> 2) + 1);
-          acc[0] = fmaf(w0.x, t[k][0], acc[0]); acc[1] = fmaf(w0.y, t[k][1], acc[1]);
-          acc[2] = fmaf(w0.z, t[k][2], acc[2]); acc[3] = fmaf(w0.w, t[k][3], acc[3]);
-          acc[4] = fmaf(w1.x, t[k][4], acc[4]); acc[5] = fmaf(w1.y, t[k][5], acc[5]);
-          acc[6] = fmaf(w1.z, t[k][6], acc[6]); acc[7] = fmaf(w1.w, t[k][7], acc[7]);
+      for (int k = 0; k < 9; ++k)
+        tk[k] = __ldg(base + (static_cast<long long>(rb + k / 3) * p.w + (cb + k % 3)) * nvec);
+      for (int phy = 0; phy < f; ++phy) {
+        const int y = R * f + phy;
+        for (int phx = 0; phx < f; ++phx) {
+          const int x = Cc * f + phx;
+          const long long pix = (plane * H + y) * W + x;
+          if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
+          float acc[8];
+          if constexpr (!BORDER) {
+            cond_stencil(reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + (lane & 3) * 2,
+                         8, tk, p.bdw, cv, acc);
+          } else {
+            const long long cls = static_cast<long long>(ycls0 + phy) * ncls + (xcls0 + phx);
+            cond_stencil(reinterpret_cast<const float4*>(table + cls * 9 * p.Cb) + cv * 2, p.Cb >> 2,
+                         tk, p.bdw, cv, acc);
+          }
+          gelu8(acc);
+          reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
         }
-        gelu8(acc);
-        reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
       }
     }
-  }
-}
-
-// The frame of border cells (the outermost `factor` pixels on every side of each H x W plane),
-// tap by tap: one thread per (frame pixel, 8 channels), frame pixels enumerated densely - top
-// band, bottom band, then the left and right strips of the rows in between.
-__global__ void __launch_bounds__(256) adaln_cond_frame_kernel(const AdalnCondParams p) {
-  const int nvec = p.Cb >> 3;
-  const int f = p.factor;
-  const int H = p.h * f, W = p.w * f;
-  const long long HW = static_cast<long long>(H) * W;
-  const long long plane0 = p.row0 / HW;
-  const long long plane1 = (p.row0 + p.n_rows - 1) / HW;
-  const int band = f * W;                                   // pixels of the top (or bottom) band
-  const int mid_rows = H > 2 * f ? H - 2 * f : 0;
-  const int strip_w = W >= 2 * f ? 2 * f : W;               // left + right strip of a middle row
-  const long long per_plane =
-      (H >= 2 * f ? 2LL * band : HW) + static_cast<long long>(mid_rows) * strip_w;
-  const long long total = (plane1 - plane0 + 1) * per_plane * nvec;
-  for (long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
-       t += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int cv = static_cast<int>(t % nvec);
-    const long long fp = t / nvec;
-    const long long plane = plane0 + fp / per_plane;
-    long long k = fp % per_plane;
-    int y, x;
-    if (H < 2 * f) {
-      y = static_cast<int>(k / W); x = static_cast<int>(k % W);
-    } else if (k < band) {
-      y = static_cast<int>(k / W); x = static_cast<int>(k % W);
-    } else if (k < 2LL * band) {
-      k -= band;
-      y = H - f + static_cast<int>(k / W); x = static_cast<int>(k % W);
-    } else {
-      k -= 2LL * band;
-      y = f + static_cast<int>(k / strip_w);
-      const int sx = static_cast<int>(k % strip_w);
-      x = (W >= 2 * f && sx >= f) ? W - 2 * f + sx : sx;
-    }
-    const long long pix = plane * HW + static_cast<long long>(y) * W + x;
-    if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
-    const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
-    float acc[8];
-    cond_direct_pixel(p, base, nvec, H, W, y, x, cv, acc);
-    gelu8(acc);
-    reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
   }
 }
 
 // Number of floats of the table the cell kernel needs, or 0 when the geometry takes the
 // direct kernel (small factor, wide conv kernel, channel count not a multiple of 32).
 inline long long adaln_cond_table_floats(int Cb, int factor, int ks) {
-  if (factor < 4 || ks > 5 || Cb % 32 != 0) return 0;
-  return static_cast<long long>(factor) * factor * 9 * Cb;
+  if (factor < 4 || factor > 8 || ks > 5 || Cb % 32 != 0) return 0;   // slab <= 72 KB of smem
+  return 9LL * factor * factor * 9 * Cb;
 }
 
 // table: device scratch of adaln_cond_table_floats() floats, or null for the direct kernel.
@@ -435,25 +465,31 @@ inline int launch_adaln_cond(const AdalnCondParams& p, float* table, int sm_coun
       p.D <= 0 || p.h <= 0 || p.w <= 0 || p.row0 < 0)
     return -2;
   if (p.n_rows <= 0) return 0;
-  if (table != nullptr && adaln_cond_table_floats(p.Cb, p.factor, p.ks) > 0) {
-    const int n = p.factor * p.factor * p.Cb;
+  if (table != nullptr && p.h >= 3 && p.w >= 3 &&
+      adaln_cond_table_floats(p.Cb, p.factor, p.ks) > 0) {
+    const int n = 9 * p.factor * p.factor * p.Cb;
     adaln_cond_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(p.wdw, p.Cb, p.factor, p.ks, table);
     const long long W = static_cast<long long>(p.w) * p.factor;
     const long long cell_rows = (p.row0 + p.n_rows - 1) / W / p.factor - p.row0 / W / p.factor + 1;
-    const long long warps = (cell_rows * p.w + 7) / 8 * (p.Cb / 32);
-    long long blocks = (warps + 7) / 8;
-    const long long cap = static_cast<long long>(sm_count) * 16;
+    const long long items =
+        (cell_rows * p.w + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM * (p.Cb / 32);
+    long long blocks = items;
+    const long long cap = static_cast<long long>(sm_count) * 24;
     if (blocks > cap) blocks = cap;
-    if (p.h > 2 && p.w > 2)
-      adaln_cond_cells_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, table);
+    const int slab_bytes = p.factor * p.factor * 9 * 32 * 4;
+    if (slab_bytes > 48 * 1024) {
+      cudaError_t ea = cudaFuncSetAttribute(adaln_cond_cells_kernel<false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, slab_bytes);
+      if (ea != cudaSuccess) return -static_cast<int>(ea) - 1000;
+    }
+    adaln_cond_cells_kernel<false><<<static_cast<int>(blocks), 256, slab_bytes, stream>>>(p, table);
     {
       const long long H = static_cast<long long>(p.h) * p.factor;
       const long long planes = (p.row0 + p.n_rows - 1) / (H * W) - p.row0 / (H * W) + 1;
-      const long long frame = H * W - (p.h > 2 && p.w > 2 ? (H - 2 * p.factor) * (W - 2 * p.factor) : 0);
-      long long fb = (planes * frame * (p.Cb / 8) + 255) / 256;
-      const long long fcap = static_cast<long long>(sm_count) * 32;
-      if (fb > fcap) fb = fcap;
-      adaln_cond_frame_kernel<<<static_cast<int>(fb), 256, 0, stream>>>(p);
+      const long long ring = 2LL * p.w + 2LL * (p.h - 2);
+      long long bb = (planes * ring + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM * (p.Cb / 32);
+      if (bb > cap) bb = cap;
+      adaln_cond_cells_kernel<true><<<static_cast<int>(bb), 256, 0, stream>>>(p, table);
     }
   } else {
     const long long total = p.n_rows * (p.Cb / 8);

@@ -625,6 +625,7 @@ int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int C
   if (!tokens || !w_dw || !out || !aligned16(tokens) || !aligned16(out) || B <= 0 || n_rows < 0)
     return STRATA_ERR_ARG;
   if (D <= 0 || h <= 0 || w <= 0 || factor <= 0) return STRATA_ERR_ARG;
+  if (!aligned16(w_dw) || (b_dw && !aligned16(b_dw))) return STRATA_ERR_ARG;
   const int64_t pixels = static_cast<int64_t>(B) * D * h * factor * w * factor;
   if (row0 < 0 || row0 + n_rows > pixels) return STRATA_ERR_ARG;
   AdalnCondParams p;
