@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from . import ops
+from . import ops, rope
 from .ops import EPI_BIAS, EPI_GATE, EPI_GELU
 from .strata import FinalLayer, Mlp, NeighborhoodAttention3D, PatchEmbed3D, StrataTransformer3D, _triple
 
@@ -29,16 +29,27 @@ _COND_CHUNK_ROWS = 1 << 18
 class StrataPixel3DBlock(nn.Module):
     """x += g1 * proj(NA3D(qkv(LN(x) * (1 + s1) + b1)));  x += g2 * fc2(gelu(fc1(LN(x) * (1 + s2) + b2)))
     with (b1, s1, g1, b2, s2, g2) = chunks of proj6(GELU(dwconv(bilinear_up(backbone tokens)))).
-    A block built without AdaLN parameters (first_block_only_adaln) runs unmodulated."""
+    In the "pixel_proj" mode the chunks come from Linear(SiLU(backbone token)) instead, one set per
+    pixel of the token's patch. A block built without AdaLN parameters (first_block_only_adaln)
+    runs unmodulated."""
 
     def __init__(self, dim: int, num_heads: int, mlp_ratio: float, qk_norm: bool, gated: bool,
-                 kernel, cond_dim: int, adaln: bool, dw_kernel: int = 5):
+                 kernel, cond_dim: int, adaln: bool, dw_kernel: int = 5,
+                 adaln_mode: str = "bilinear_dw", patch=(1, 1, 1)):
         super().__init__()
         self.dim, self.num_heads, self.qk_norm = dim, num_heads, qk_norm
         self.kernel = _triple(kernel)
+        self.patch = _triple(patch)
         self.attn = NeighborhoodAttention3D(dim, num_heads, True, gated)
         self.mlp = Mlp(dim, int(dim * mlp_ratio))
-        if adaln:
+        if adaln and adaln_mode == "pixel_proj":
+            # every backbone token emits the modulation of the pv x ph x pw pixels it covers
+            pv, ph, pw = self.patch
+            self.adaln_pixel_proj = nn.Sequential(nn.SiLU(),
+                                                  nn.Linear(cond_dim, pv * ph * pw * 6 * dim))
+            nn.init.zeros_(self.adaln_pixel_proj[-1].weight)
+            nn.init.zeros_(self.adaln_pixel_proj[-1].bias)
+        elif adaln:
             self.adaln_bilinear_dw_conv = nn.Conv3d(cond_dim, cond_dim, (1, dw_kernel, dw_kernel),
                                                     padding=(0, dw_kernel // 2, dw_kernel // 2),
                                                     groups=cond_dim)
@@ -50,7 +61,7 @@ class StrataPixel3DBlock(nn.Module):
 
     @property
     def has_adaln(self) -> bool:
-        return hasattr(self, "adaln_bilinear_dw_proj")
+        return hasattr(self, "adaln_bilinear_dw_proj") or hasattr(self, "adaln_pixel_proj")
 
     def device_weights(self) -> dict:
         key = tuple((p.data_ptr(), p._version, p.device) for p in self.parameters())
@@ -64,7 +75,9 @@ class StrataPixel3DBlock(nn.Module):
              "w_fc2": w(self.mlp.layers[2]), "b_fc2": b(self.mlp.layers[2])}
         if hasattr(self.attn, "gate_proj"):
             c["w_gate"], c["b_gate"] = w(self.attn.gate_proj), b(self.attn.gate_proj)
-        if self.has_adaln:
+        if hasattr(self, "adaln_pixel_proj"):
+            c["w_pp"], c["b_pp"] = w(self.adaln_pixel_proj[-1]), b(self.adaln_pixel_proj[-1])
+        elif self.has_adaln:
             conv = self.adaln_bilinear_dw_conv
             ks = conv.kernel_size[-1]
             c["w_dw"] = conv.weight.detach().float().reshape(conv.out_channels, ks, ks).contiguous()
@@ -79,6 +92,12 @@ class StrataPixel3DBlock(nn.Module):
             return None
         c = self.device_weights()
         B, D, h, w, Cb = backbone_tokens.shape
+        if "w_pp" in c:
+            pv, ph, pw = self.patch
+            a = torch.nn.functional.silu(backbone_tokens).view(-1, Cb)
+            m = ops.linear(a, c["w_pp"], c["b_pp"], EPI_BIAS)
+            m = m.view(B, D, h, w, pv, ph, pw, 6 * self.dim).permute(0, 1, 4, 2, 5, 3, 6, 7)
+            return m.reshape(B * D * pv * h * ph * w * pw, 6 * self.dim)   # one strided copy
         pixels = B * D * h * factor * w * factor
         mod = torch.empty((pixels, 6 * self.dim), dtype=torch.bfloat16, device=backbone_tokens.device)
         chunk = min(pixels, _COND_CHUNK_ROWS)
@@ -89,8 +108,10 @@ class StrataPixel3DBlock(nn.Module):
             ops.linear(buf[:n], c["w_mod"], c["b_mod"], EPI_BIAS, out=mod[r0:r0 + n])
         return mod
 
-    def forward(self, x: torch.Tensor, grid, mod: torch.Tensor | None, n_tiles: int) -> torch.Tensor:
-        """x: bf16 rows [n_tiles * D*H*W, dim], updated in place and returned."""
+    def forward(self, x: torch.Tensor, grid, mod: torch.Tensor | None, n_tiles: int,
+                rope_cs: torch.Tensor | None = None) -> torch.Tensor:
+        """x: bf16 rows [n_tiles * D*H*W, dim], updated in place and returned. rope_cs: packed
+        half (cos, sin) table [n_tiles, H*W, 32, 2] or None."""
         if not (isinstance(self.mlp.layers[1], nn.GELU) and self.mlp.layers[1].approximate == "tanh"):
             raise RuntimeError("the fused MLP kernel implements the tanh GELU; this block's Mlp "
                                "still holds an exact GELU (the wrapper's tanh swap did not run)")
@@ -99,9 +120,14 @@ class StrataPixel3DBlock(nn.Module):
         D, H, W = grid
         sl = (lambda i: mod[:, i * C:(i + 1) * C]) if mod is not None else (lambda i: None)
         xn = ops.adaln_rows(x, shift=sl(0), scale=sl(1))
-        qkv = ops.linear(xn, c["w_qkv"], c["b_qkv"])
-        if self.qk_norm:
-            ops.qk_norm_rows_(qkv, C)
+        if rope_cs is not None:
+            # rotation (and the q/k norm) in the GEMM epilogue, as in the backbone blocks
+            qkv = ops.qkv_rope(xn, c["w_qkv"], c["b_qkv"], C // self.num_heads, None, None,
+                               D * H * W, H * W, qk_norm=self.qk_norm, rope_cs=rope_cs)
+        else:
+            qkv = ops.linear(xn, c["w_qkv"], c["b_qkv"])
+            if self.qk_norm:
+                ops.qk_norm_rows_(qkv, C)
         q6 = qkv.view(n_tiles, D, H, W, 3, self.num_heads, C // self.num_heads)
         attn = ops.na3d(q6[:, :, :, :, 0], q6[:, :, :, :, 1], q6[:, :, :, :, 2], self.kernel)
         attn = attn.view(-1, C)
@@ -130,18 +156,16 @@ class Strata(nn.Module):
                  bf16_mixed_pixel: bool = False, activation_checkpointing_pixel: bool | float = False,
                  adaln_dw_kernel: int = 5):
         super().__init__()
-        if adaln_mode != "bilinear_dw":
-            raise ValueError("only adaln_mode='bilinear_dw' (the production pixel configuration, "
-                             "use_bilinear_dw_gelu_project_adaln_pixel=True) is built")
-        if rope_mode_pixel != "none":
-            raise ValueError("pixel-stage RoPE is not built (the production pixel configuration "
-                             "runs without it)")
+        if adaln_mode not in ("bilinear_dw", "pixel_proj"):
+            raise ValueError(f"unknown adaln_mode {adaln_mode!r}")
+        if rope_mode_pixel not in ("none", "axial", "stereographic"):
+            raise ValueError(f"unknown rope_mode_pixel {rope_mode_pixel!r}")
         if qk_norm_affine_pixel:
             raise ValueError("qk_norm_affine_pixel=True is not supported")
         self.backbone = StrataTransformer3D(**backbone_config)
         self.backbone.final_layer = None     # the two-stage model has no backbone output head
         pv, ph, pw = self.backbone.patch_size
-        if pv != 1 or ph != pw:
+        if adaln_mode == "bilinear_dw" and (pv != 1 or ph != pw):
             raise ValueError("the bilinear_dw AdaLN needs patch_size_vert == 1 and square patches")
         heads = num_heads_pixel if num_heads_pixel is not None else max(embed_dim_pixel // 64, 1)
         if embed_dim_pixel % heads or embed_dim_pixel // heads != 64:
@@ -160,11 +184,44 @@ class Strata(nn.Module):
         self.pixel_blocks = nn.ModuleList([
             StrataPixel3DBlock(embed_dim_pixel, heads, mlp_ratio_pixel, qk_norm_pixel,
                                gated_attention_pixel, attn_kernel_pixel, self.backbone.embed_dim,
-                               adaln=(i == 0 or not first_block_only_adaln), dw_kernel=adaln_dw_kernel)
+                               adaln=(i == 0 or not first_block_only_adaln), dw_kernel=adaln_dw_kernel,
+                               adaln_mode=adaln_mode, patch=self.backbone.patch_size)
             for i in range(num_layers_pixel)])
         self.pixel_final_layer = FinalLayer(embed_dim_pixel, self.out_channels)
+        if rope_mode_pixel == "axial":
+            self._build_axial_rope_pixel()
 
-    def pixel_stage(self, pixel_tokens: torch.Tensor, backbone_tokens: torch.Tensor, grid_px):
+    def _build_axial_rope_pixel(self, device=None) -> None:
+        """Non-persistent buffers `_rope_cos_pixel` / `_rope_sin_pixel` [D*H*W, head_dim/2] for the
+        axial mode (one row per pixel token; the reference's wrapper rebuilds them in
+        set_tile_size, screamcast/strata_wrappers.py:634-645)."""
+        cos, sin = rope.axial_rope_tables(self.height, self.width, self.head_dim_pixel,
+                                          self.rope_base_pixel, device=device)
+        self.register_buffer("_rope_cos_pixel", cos[0].repeat(self.depth, 1), persistent=False)
+        self.register_buffer("_rope_sin_pixel", sin[0].repeat(self.depth, 1), persistent=False)
+
+    def rope_tables_pixel(self, pos: torch.Tensor | None, n_tiles: int, grid_px):
+        """Packed half (cos, sin) table [n_tiles, H*W, head_dim/2, 2] of the pixel tokens, or None."""
+        D, H, W = grid_px
+        if self.rope_mode_pixel == "none":
+            return None
+        if self.rope_mode_pixel == "axial":
+            hw = H * W
+            if self._rope_cos_pixel.shape[0] != D * hw:
+                raise ValueError(f"axial pixel RoPE tables were built for {self._rope_cos_pixel.shape[0]} "
+                                 f"tokens, the input has {D * hw}; call set_tile_size first")
+            cos = self._rope_cos_pixel[:hw].expand(n_tiles, -1, -1).contiguous()
+            sin = self._rope_sin_pixel[:hw].expand(n_tiles, -1, -1).contiguous()
+        else:
+            if pos is None:
+                raise ValueError("stereographic RoPE needs pos=[B, 2, H, W] (lat, lon)")
+            cos, sin = rope.stereographic_rope_tables(pos, self.head_dim_pixel, 1,
+                                                      self.rope_length_scale_pixel,
+                                                      self.rope_base_pixel)
+        return rope.pack_rope_tables(cos, sin)
+
+    def pixel_stage(self, pixel_tokens: torch.Tensor, backbone_tokens: torch.Tensor, grid_px,
+                    rope_cs: torch.Tensor | None = None):
         """pixel_tokens bf16 [B, D*H*W, C] (modified in place), backbone_tokens bf16
         [B, D, h, w, Cb] -> pixel tokens after the blocks."""
         B = pixel_tokens.shape[0]
@@ -172,7 +229,7 @@ class Strata(nn.Module):
         x = pixel_tokens.view(-1, self.embed_dim_pixel)
         for blk in self.pixel_blocks:
             mod = blk.modulation(backbone_tokens, factor)
-            blk(x, grid_px, mod, B)
+            blk(x, grid_px, mod, B, rope_cs)
             del mod
         return pixel_tokens
 
@@ -195,7 +252,8 @@ class Strata(nn.Module):
                                     patch=(1, 1, 1), k_pad=Kpp)
         px = self.pixel_patch_embed.tokens_from_patches(ap, B)
         del a, ap
-        px = self.pixel_stage(px, tokens.view(B, *grid, bb.embed_dim), (D, H, W))
+        px = self.pixel_stage(px, tokens.view(B, *grid, bb.embed_dim), (D, H, W),
+                              self.rope_tables_pixel(pos, B, (D, H, W)))
         y, _ = self.pixel_final_layer.matrix_bf16(px)
         return ops.postprocess_fields(y, (B, self.out_channels, D, H, W), lat, lon, lat0, lon0,
                                       wind=wind, patch=(1, 1, 1))

@@ -426,14 +426,21 @@ class StrataModel(_StrataModelBase):
     def set_tile_size(self, height: int, width: int) -> None:
         self.strata.backbone.set_tile_size(height, width)
         self.strata.height, self.strata.width = int(height), int(width)
+        if self.strata.rope_mode_pixel == "axial":
+            self.strata._build_axial_rope_pixel(device=self.strata._rope_cos_pixel.device)
 
     def set_rope_length_scale(self, base: float) -> None:
         if base <= 0:
             raise ValueError(f"rope length scale base must be positive, got {base}")
-        if self.strata.backbone.rope_mode != "stereographic":
+        backbone_stereo = self.strata.backbone.rope_mode == "stereographic"
+        pixel_stereo = self.strata.rope_mode_pixel == "stereographic"
+        if not (backbone_stereo or pixel_stereo):
             raise ValueError("set_rope_length_scale is only meaningful for stereographic RoPE")
         self._rope_length_scale_base = base
-        self.strata.backbone.rope_length_scale = base * self.strata.backbone.patch_size[1]
+        if backbone_stereo:
+            self.strata.backbone.rope_length_scale = base * self.strata.backbone.patch_size[1]
+        if pixel_stereo:
+            self.strata.rope_length_scale_pixel = base
 
     def forward(self, x: torch.Tensor, index) -> torch.Tensor:
         if not (x.is_cuda and x.dtype == torch.float32):

@@ -50,6 +50,12 @@ def test_structure_contract():
     # adaLN-zero initialisation
     assert not blocks[0].adaln_bilinear_dw_proj.weight.any()
     assert not blocks[0].adaln_bilinear_dw_proj.bias.any()
+    # default AdaLN mode: one projection per block, Sequential ending in the zero-initialised Linear
+    d = _two_stage(n_layers=2, n_layers_pixel=2, use_bilinear_dw_gelu_project_adaln_pixel=False)
+    assert d.strata.adaln_mode == "pixel_proj"
+    last = d.strata.pixel_blocks[1].adaln_pixel_proj[-1]
+    assert last.out_features == 16 * 6 * 128 and not last.weight.any() and not last.bias.any()
+    assert not hasattr(d.strata.pixel_blocks[0], "adaln_bilinear_dw_proj")
     with pytest.raises(RuntimeError, match="CUDA"):
         m(torch.zeros(1, 5, 4, 32, 32), {"lat": torch.zeros(1, 32, 32), "lon": torch.zeros(1, 32, 32)})
 

@@ -106,7 +106,7 @@ def _randomise(m, seed=5):
         for n, p in m.named_parameters():
             if n.endswith(".bias"):
                 p.copy_(torch.randn(p.shape, generator=g) * 0.05)
-            if n.endswith("adaln_bilinear_dw_proj.weight"):
+            if n.endswith("adaln_bilinear_dw_proj.weight") or n.endswith("adaln_pixel_proj.1.weight"):
                 p.copy_(torch.randn(p.shape, generator=g) * (0.5 / p.shape[1] ** 0.5))
     return m
 
@@ -145,14 +145,22 @@ def test_fresh_pixel_blocks_are_identity():
     assert torch.equal(y, x)
 
 
-@pytest.mark.parametrize("wind,first_only", [(False, False), (True, True)])
-def test_two_stage_model_matches_oracle(wind, first_only):
-    over = dict(first_block_only_adaln_pixel=first_only)
+@pytest.mark.parametrize("wind,first_only,extra", [
+    (False, False, {}),
+    (True, True, {}),
+    (False, False, dict(do_rope_2d_stereographic_pixel=True)),
+    (True, False, dict(do_rope_2d_pixel=True, qk_norm_pixel=False)),
+    (False, False, dict(use_bilinear_dw_gelu_project_adaln_pixel=False)),
+    (False, True, dict(use_bilinear_dw_gelu_project_adaln_pixel=False, patch_size_vert=2,
+                       attn_kernel=(1, 3, 3))),
+])
+def test_two_stage_model_matches_oracle(wind, first_only, extra):
+    over = dict(first_block_only_adaln_pixel=first_only, **extra)
     if wind:
         over.update(do_rotate_wind=True, wind_channel_indices=(0, 1))
     m = _randomise(_two_stage(**over))
     names = [n for n, _ in m.named_parameters()]
-    assert ("strata.pixel_blocks.1.adaln_bilinear_dw_proj.weight" in names) == (not first_only)
+    assert any(n.startswith("strata.pixel_blocks.1.adaln_") for n in names) == (not first_only)
     assert not any(n.startswith("strata.backbone.final_layer") for n in names)
     B, H, W = 2, 32, 32
     x = torch.randn(B, 5, 4, H, W, generator=torch.Generator().manual_seed(0))
@@ -161,13 +169,17 @@ def test_two_stage_model_matches_oracle(wind, first_only):
         y = m(x.cuda(), {"lat": lat.cuda(), "lon": lon.cuda()})
     assert y.shape == x.shape and torch.isfinite(y).all()
     state = {k: v.detach().cpu() for k, v in m.state_dict().items()}
-    kw = dict(patch=(1, 4, 4), num_heads=2, kernel=3, num_layers=2, num_heads_pixel=2,
-              kernel_pixel=(3, 5, 5), num_layers_pixel=2, lat=lat, lon=lon, qk_norm=True, gated=True,
-              qk_norm_pixel=True, wind_channels=(0, 1) if wind else None)
+    rope_px = ("stereographic" if extra.get("do_rope_2d_stereographic_pixel")
+               else "axial" if extra.get("do_rope_2d_pixel") else "none")
+    kw = dict(patch=(extra.get("patch_size_vert", 1), 4, 4), num_heads=2,
+              kernel=extra.get("attn_kernel", 3), num_layers=2,
+              num_heads_pixel=2, kernel_pixel=(3, 5, 5), num_layers_pixel=2, lat=lat, lon=lon,
+              qk_norm=True, gated=True, qk_norm_pixel=extra.get("qk_norm_pixel", True),
+              wind_channels=(0, 1) if wind else None, rope_mode_pixel=rope_px)
     for emulate in (False, True):
         ref = po.two_stage_forward(x, state, emulate_bf16=emulate, **kw)
         err = rel_max_err(y, ref)
-        print(f"two-stage model vs oracle (emulate_bf16={emulate}): {err:.4f}")
+        print(f"two-stage model vs oracle (emulate_bf16={emulate}, {extra}): {err:.4f}")
         assert err < TOL_BF16
 
 
@@ -180,6 +192,13 @@ def test_two_stage_wrapper_contract():
     m.set_rope_length_scale(1e-2)
     assert m.strata.backbone.rope_length_scale == 4e-2
     m.disable_activation_checkpointing()
+    ax = _two_stage(do_rope_2d_pixel=True)
+    assert ax.strata._rope_cos_pixel.shape[-2] == 4 * 32 * 32     # tests/test_dit_3d_pixel.py:200
+    ax.set_tile_size(16, 48)
+    assert ax.strata._rope_cos_pixel.shape[-2] == 4 * 16 * 48 and ax.strata._rope_cos_pixel.is_cuda
+    st = _two_stage(do_rope_2d_stereographic_pixel=True)
+    st.set_rope_length_scale(1e-2)
+    assert st.strata.rope_length_scale_pixel == 1e-2 and st.strata.backbone.rope_length_scale == 4e-2
     with pytest.raises(ValueError, match="patch_size_vert=1"):
         _two_stage(patch_size_vert=2, depth=4)
     with pytest.raises(TypeError, match="Unsupported legacy DiT kwargs"):
