@@ -262,6 +262,16 @@ int strata_adaln_cond_bf16(const void* tokens, int B, int D, int h, int w, int C
  * 0 when the geometry has no such form. With table_ws NULL every pixel is evaluated tap by tap. */
 int64_t strata_adaln_cond_table_floats(int Cb, int factor, int ks);
 
+/* Operand rows of the de-aliased patch embedding (screamcast/dealias.py:28-143,
+ * DealiasedPatchEmbed3D): x_rows = pixel rows [B, D, H, W, ldx] bf16, channels last (what
+ * strata_preprocess_patches_bf16 writes at patch 1x1x1); a[token, (c, v, y, x)] = the low-pass
+ * filtered patch, so that strata_linear_bf16 with the proj weight gives the module's tokens.
+ * taps: HOST array of the 1-D resample filter (n_taps <= 8, e.g. 1 4 6 4 1), applied on the
+ * axes whose patch size exceeds 1, normalised by its sum; edges replicate as in the reference. */
+int strata_dealias_patches_bf16(const void* x_rows, int64_t ldx, int B, int C, int D, int H, int W,
+                                int pv, int ph, int pw, const float* taps, int n_taps, void* a,
+                                int64_t lda, void* stream);
+
 /* Cross-GPU barrier on the stream: publishes `epoch` (monotonically increasing per use) in slot
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
  * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work

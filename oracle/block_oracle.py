@@ -285,7 +285,8 @@ def backbone_forward(x: torch.Tensor, state: dict, *, patch, num_heads: int, ker
                      lat: torch.Tensor, lon: torch.Tensor, rope_mode: str = "stereographic",
                      rope_length_scale: float | None = None, rope_base: float = 100.0,
                      qk_norm: bool = False, gated: bool = False, concat_latitude: bool = True,
-                     wind_channels=None, alt_depthwise: bool = False, emulate_bf16: bool = False):
+                     wind_channels=None, alt_depthwise: bool = False, emulate_bf16: bool = False,
+                     dealias_filter=None):
     """Single-stage model: the wrapper's pre/post-processing (wind rotation, cos/sin(lat)
     concat: screamcast/strata_wrappers.py:206-249) around patch embed -> blocks -> final layer.
 
@@ -310,8 +311,12 @@ def backbone_forward(x: torch.Tensor, state: dict, *, patch, num_heads: int, ker
         x = torch.cat([x, torch.cos(le), torch.sin(le)], dim=1)
     r = lambda t: _round(t, emulate_bf16)
     w = state["strata.patch_embed.proj.weight"].float()
-    t = F.conv3d(r(x), _weight(w, emulate_bf16), state["strata.patch_embed.proj.bias"].float(),
-                 stride=patch)
+    if dealias_filter is not None:
+        t = dealiased_patch_embed(r(x), _weight(w, emulate_bf16),
+                                  state["strata.patch_embed.proj.bias"], patch, dealias_filter)
+    else:
+        t = F.conv3d(r(x), _weight(w, emulate_bf16), state["strata.patch_embed.proj.bias"].float(),
+                     stride=patch)
     C = t.shape[1]
     grid = (D // pv, H // ph, W // pw)
     t = r(t.flatten(2).transpose(1, 2))
@@ -344,6 +349,27 @@ def backbone_forward(x: torch.Tensor, state: dict, *, patch, num_heads: int, ker
         y = y.clone()
         y[:, u], y[:, v] = torch.from_numpy(ug), torch.from_numpy(vg)
     return y
+
+
+def dealiased_patch_embed(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, patch,
+                          resample_filter) -> torch.Tensor:
+    """De-aliased patch embedding (screamcast/dealias.py:116-143): the patch convolution at
+    stride 1 on the unpadded input, replicate padding of ITS OUTPUT by (k-1)//2 before and the
+    rest after on every decimated axis, then a normalised separable low-pass applied per channel
+    at stride = patch. Axes with patch 1 are not filtered. x [B, C, D, H, W] -> [B, E, D', H', W']."""
+    pd, ph, pw = patch
+    s1 = F.conv3d(x.float(), weight.float(), bias.float())
+    f = torch.as_tensor(resample_filter, dtype=torch.float32)
+    taps = [f / f.sum() if p > 1 else torch.ones(1) for p in (pd, ph, pw)]
+    kd, kh, kw = (len(t) for t in taps)
+    pads = []
+    for k in (kw, kh, kd):                      # F.pad lists the last axis first
+        pads += [(k - 1) // 2, (k - 1) - (k - 1) // 2]
+    if max(kd, kh, kw) > 1:
+        s1 = F.pad(s1, pads, mode="replicate")
+    f3 = taps[0][:, None, None] * taps[1][None, :, None] * taps[2][None, None, :]
+    E = s1.shape[1]
+    return F.conv3d(s1, f3[None, None].repeat(E, 1, 1, 1, 1), groups=E, stride=(pd, ph, pw))
 
 
 # --------------------------------------------------------------------------- per-block halo

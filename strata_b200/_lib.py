@@ -77,6 +77,9 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                        c_void_p, c_void_p]),
     "strata_adaln_cond_table_floats": (c_int64, [c_int, c_int, c_int]),
+    "strata_dealias_patches_bf16": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int64,
+                                            c_void_p]),
     "strata_halo_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p]),
     "strata_ipc_alloc": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
     "strata_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),

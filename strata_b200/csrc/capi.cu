@@ -612,6 +612,39 @@ int strata_qk_norm_rows_bf16(void* qkv, int64_t ld, int64_t M, int C, float eps,
   return r == -2 ? STRATA_ERR_ARG : r;
 }
 
+int strata_dealias_patches_bf16(const void* x_rows, int64_t ldx, int B, int C, int D, int H, int W,
+                                int pv, int ph, int pw, const float* taps, int n_taps, void* a,
+                                int64_t lda, void* stream) {
+  const int sms = current_sm_count();
+  if (sms <= 0) return STRATA_ERR_NO_DEVICE;
+  if (B < 0 || C <= 0 || D <= 0 || H <= 0 || W <= 0 || pv <= 0 || ph <= 0 || pw <= 0)
+    return STRATA_ERR_ARG;
+  if (D % pv || H % ph || W % pw || !x_rows || !a || !taps || n_taps < 1 || n_taps > 8)
+    return STRATA_ERR_ARG;
+  if (ldx < C || lda < static_cast<int64_t>(C) * pv * ph * pw) return STRATA_ERR_ARG;
+  if (B == 0) return STRATA_OK;
+  DealiasParams p{};
+  p.B = B; p.C = C; p.D = D; p.H = H; p.W = W; p.pv = pv; p.ph = ph; p.pw = pw;
+  p.ldx = ldx; p.lda = lda;
+  // host taps: the filter acts on decimated axes only (a stride-1 axis keeps a single unit tap)
+  float sum = 0.f;
+  for (int i = 0; i < n_taps; ++i) sum += taps[i];
+  if (sum == 0.f) return STRATA_ERR_ARG;
+  auto fill = [&](int patch, int& k, float* f) {
+    if (patch == 1) { k = 1; f[0] = 1.f; return; }
+    k = n_taps;
+    for (int i = 0; i < n_taps; ++i) f[i] = taps[i] / sum;
+  };
+  fill(pv, p.kd, p.fd); fill(ph, p.kh, p.fh); fill(pw, p.kw, p.fw);
+  const long long total = static_cast<long long>(B) * (D / pv) * (H / ph) * (W / pw) * lda;
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 32) blocks = static_cast<long long>(sms) * 32;
+  dealias_patches_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_rows), static_cast<__nv_bfloat16*>(a), p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
 int64_t strata_adaln_cond_table_floats(int Cb, int factor, int ks) {
   return adaln_cond_table_floats(Cb, factor, ks);
 }

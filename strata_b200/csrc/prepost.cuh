@@ -188,4 +188,64 @@ postprocess_fields_kernel(const __nv_bfloat16* __restrict__ y, float* __restrict
   }
 }
 
+// De-aliased patch gathering (reference: screamcast/dealias.py:28-143). The reference runs the
+// patch convolution at stride 1 without padding, pads its output by replication, low-pass
+// filters it per decimated axis and decimates by the patch size. Filtering commutes with the
+// convolution, so the same tokens come from ONE strided GEMM whose operand rows are filtered
+// patches:  A[token, (c, v, y, x)] = sum_k f[k] * X[c, s_d(k) + v, s_h(k) + y, s_w(k) + x]  with
+// s_axis(k) = clamp(token_axis * patch + k_axis - (K_axis - 1) / 2, 0, size - patch) - the clamp
+// is the replicate padding of the stride-1 output. X: pixel rows [B, D, H, W, ldx] bf16
+// (channels last, the output of preprocess_patches at patch 1); A: [tokens, lda] bf16, zero
+// beyond the C * pv * ph * pw valid columns.
+struct DealiasParams {
+  int B, C, D, H, W, pv, ph, pw;
+  int kd, kh, kw;
+  float fd[8], fh[8], fw[8];     // per-axis taps, each already divided by its sum
+  long long ldx, lda;
+};
+
+__global__ void __launch_bounds__(256)
+dealias_patches_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ a,
+                       const DealiasParams p) {
+  const int d_tok = p.D / p.pv, h_tok = p.H / p.ph, w_tok = p.W / p.pw;
+  const int pvol = p.pv * p.ph * p.pw;
+  const int K = p.C * pvol;
+  const long long total = static_cast<long long>(p.B) * d_tok * h_tok * w_tok * p.lda;
+  for (long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int col = static_cast<int>(t % p.lda);
+    const long long tok = t / p.lda;
+    if (col >= K) {
+      a[t] = __float2bfloat16(0.f);
+      continue;
+    }
+    const int c = col / pvol;
+    int rem = col - c * pvol;
+    const int v = rem / (p.ph * p.pw);
+    rem -= v * p.ph * p.pw;
+    const int yy = rem / p.pw, xx = rem - yy * p.pw;
+    const int tw = static_cast<int>(tok % w_tok);
+    const int th = static_cast<int>((tok / w_tok) % h_tok);
+    const int td = static_cast<int>((tok / (static_cast<long long>(w_tok) * h_tok)) % d_tok);
+    const long long b = tok / (static_cast<long long>(w_tok) * h_tok * d_tok);
+    float acc = 0.f;
+    for (int id = 0; id < p.kd; ++id) {
+      int sd = td * p.pv + id - (p.kd - 1) / 2;
+      sd = sd < 0 ? 0 : (sd > p.D - p.pv ? p.D - p.pv : sd);
+      for (int ih = 0; ih < p.kh; ++ih) {
+        int sh = th * p.ph + ih - (p.kh - 1) / 2;
+        sh = sh < 0 ? 0 : (sh > p.H - p.ph ? p.H - p.ph : sh);
+        const float fdh = p.fd[id] * p.fh[ih];
+        const long long row = ((b * p.D + sd + v) * p.H + sh + yy) * p.W;
+        for (int iw = 0; iw < p.kw; ++iw) {
+          int sw = tw * p.pw + iw - (p.kw - 1) / 2;
+          sw = sw < 0 ? 0 : (sw > p.W - p.pw ? p.W - p.pw : sw);
+          acc = fmaf(fdh * p.fw[iw], __bfloat162float(x[(row + sw + xx) * p.ldx + c]), acc);
+        }
+      }
+    }
+    a[t] = __float2bfloat16(acc);
+  }
+}
+
 }  // namespace strata

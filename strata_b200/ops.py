@@ -446,3 +446,26 @@ def adaln_cond(tokens: torch.Tensor, w_dw: torch.Tensor, b_dw: torch.Tensor | No
             None if table is None else table.data_ptr(), _stream_ptr(tokens)),
             "strata_adaln_cond_bf16")
     return out
+
+
+def dealias_patches(x_rows: torch.Tensor, shape, channels: int, patch, taps, k_pad: int | None = None):
+    """Filtered patch rows of the de-aliased patch embedding. x_rows: bf16 pixel rows
+    [B*D*H*W, ld] (channels last, `preprocess_patches` at patch 1); shape = (B, D, H, W);
+    taps: the 1-D resample filter (python floats). Returns bf16 [tokens, k_pad]."""
+    import ctypes
+    _require_cuda_bf16(x_rows, "x_rows")
+    B, D, H, W = (int(v) for v in shape)
+    pv, ph, pw = (int(v) for v in patch)
+    if x_rows.dim() != 2 or x_rows.shape[0] != B * D * H * W or x_rows.stride(1) != 1:
+        raise ValueError("x_rows must be [B*D*H*W, ld] pixel rows")
+    K = channels * pv * ph * pw
+    k_pad = K if k_pad is None else int(k_pad)
+    tokens = B * (D // pv) * (H // ph) * (W // pw)
+    a = torch.empty((tokens, k_pad), dtype=torch.bfloat16, device=x_rows.device)
+    t = (ctypes.c_float * len(taps))(*[float(v) for v in taps])
+    with torch.cuda.device(x_rows.device):
+        _lib.check(_lib.load().strata_dealias_patches_bf16(
+            x_rows.data_ptr(), x_rows.stride(0), B, int(channels), D, H, W, pv, ph, pw,
+            ctypes.cast(t, ctypes.c_void_p), len(taps), a.data_ptr(), k_pad, _stream_ptr(x_rows)),
+            "strata_dealias_patches_bf16")
+    return a

@@ -241,17 +241,14 @@ class Strata(nn.Module):
         bb = self.backbone
         B, _, D, H, W = x.shape
         grid = bb.token_grid(D, H, W)
-        _, _, _, Kp = bb.patch_embed._gemm_weights()
-        a = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
-                                   patch=bb.patch_size, k_pad=Kp)
-        tokens = bb.patch_embed.tokens_from_patches(a, B)
+        tokens = bb.embed_fused(x, lat, lon, lat0, lon0, wind, concat_lat)
         cos, sin = bb.rope_tables(pos, B, grid)
         tokens = bb.forward_tokens(tokens, grid, cos, sin)
         _, _, _, Kpp = self.pixel_patch_embed._gemm_weights()
         ap = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
                                     patch=(1, 1, 1), k_pad=Kpp)
         px = self.pixel_patch_embed.tokens_from_patches(ap, B)
-        del a, ap
+        del ap
         px = self.pixel_stage(px, tokens.view(B, *grid, bb.embed_dim), (D, H, W),
                               self.rope_tables_pixel(pos, B, (D, H, W)))
         y, _ = self.pixel_final_layer.matrix_bf16(px)

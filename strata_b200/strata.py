@@ -87,6 +87,62 @@ class PatchEmbed3D(nn.Module):
         return ops.linear(a, wm, bias).view(n_tiles, -1, wm.shape[0])
 
 
+class DealiasedPatchEmbed3D(nn.Module):
+    """Patch embedding with a fixed low-pass before the decimation (reference:
+    screamcast/dealias.py:28-143; same constructor, same `proj` shape and state-dict keys as the
+    plain embedding, the filter a non-persistent buffer). The reference convolves at stride 1,
+    replicate-pads, filters and decimates; here the filter is applied to the patches while they
+    are gathered (`ops.dealias_patches`) and one tcgen05 GEMM with the `proj` weight follows -
+    the same linear map, 1/patch-volume of the multiply-adds."""
+
+    def __init__(self, depth, height, width, patch_size=16, in_chans=3, embed_dim=768,
+                 resample_filter=(1, 1)):
+        super().__init__()
+        self.patch_size = _triple(patch_size)
+        pd, ph, pw = self.patch_size
+        for size, p_, what in ((depth, pd, "Depth"), (height, ph, "Height"), (width, pw, "Width")):
+            if size % p_ != 0:
+                kind = "vertical" if what == "Depth" else "horizontal"
+                raise ValueError(f"{what} ({size}) must be divisible by {kind} patch size ({p_})")
+        self.depth, self.height, self.width = depth, height, width
+        self.num_patches = (depth // pd) * (height // ph) * (width // pw)
+        self.proj = nn.Conv3d(in_chans, embed_dim, kernel_size=self.patch_size, stride=1, padding=0,
+                              bias=True)
+        self.resample_filter = tuple(float(v) for v in resample_filter)
+        f = torch.tensor(self.resample_filter, dtype=torch.float32)
+        one = torch.ones(1)
+        fd, fh, fw = (one if pd == 1 else f), (one if ph == 1 else f), (one if pw == 1 else f)
+        f3d = fd[:, None, None] * fh[None, :, None] * fw[None, None, :]
+        self.register_buffer("dealias_filter", (f3d / f3d.sum())[None, None], persistent=False)
+        self._embed_dim = embed_dim
+        self._gemm_cache = None
+        self._gemm_key = None
+
+    _gemm_weights = PatchEmbed3D._gemm_weights
+
+    def tokens_from_pixel_rows(self, rows: torch.Tensor, shape) -> torch.Tensor:
+        """rows: bf16 pixel rows [B*D*H*W, ld] of the pre-processed fields (channels last);
+        shape = (B, D, H, W). Returns bf16 tokens [B, tokens, embed_dim]."""
+        wm, bias, _, Kp = self._gemm_weights()
+        a = ops.dealias_patches(rows, shape, self.proj.in_channels, self.patch_size,
+                                self.resample_filter, k_pad=Kp)
+        return ops.linear(a, wm, bias).view(shape[0], -1, wm.shape[0])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """[B, C, D, H, W] -> [B, embed_dim, D', H', W'] (the reference module's output layout)."""
+        if not x.is_cuda:
+            raise RuntimeError("DealiasedPatchEmbed3D runs on CUDA only (its kernels have no CPU "
+                               "fallback)")
+        B, C, D, H, W = x.shape
+        rows = x.permute(0, 2, 3, 4, 1).to(torch.bfloat16).reshape(B * D * H * W, C)
+        Cp = (C + 7) // 8 * 8
+        if Cp != C:
+            rows = torch.nn.functional.pad(rows, (0, Cp - C))
+        t = self.tokens_from_pixel_rows(rows.contiguous(), (B, D, H, W))
+        pd, ph, pw = self.patch_size
+        return t.view(B, D // pd, H // ph, W // pw, -1).permute(0, 4, 1, 2, 3)
+
+
 class Mlp(nn.Module):
     """layers = Sequential(fc1, GELU, fc2); the reference's wrapper swaps the GELU to the tanh
     approximation (screamcast/strata_wrappers.py:76-100)."""
@@ -294,7 +350,9 @@ class StrataTransformer3D(nn.Module):
         grid = self.token_grid(D, H, W)
         if isinstance(self.patch_embed, PatchEmbed3D):
             tokens = self.patch_embed.tokens_bf16(x.contiguous())
-        else:   # a caller-assigned embed module (e.g. the de-aliased variant): run it as it is
+        elif isinstance(self.patch_embed, DealiasedPatchEmbed3D):
+            tokens = self.patch_embed(x).flatten(2).transpose(1, 2).contiguous()
+        else:   # a caller-assigned embed module: run it as it is
             with torch.autocast("cuda", dtype=torch.bfloat16, enabled=x.is_cuda):
                 tokens = self.patch_embed(x)
             tokens = tokens.to(torch.bfloat16).contiguous()
@@ -305,7 +363,23 @@ class StrataTransformer3D(nn.Module):
     def fused_path_available(self, x: torch.Tensor) -> bool:
         """The fused pre/post-processing kernels serve the plain patch embedding on CUDA fp32
         inputs; anything else (a caller-assigned embed module) goes through `forward`."""
-        return isinstance(self.patch_embed, PatchEmbed3D) and x.is_cuda and x.dtype == torch.float32
+        return (isinstance(self.patch_embed, (PatchEmbed3D, DealiasedPatchEmbed3D)) and x.is_cuda
+                and x.dtype == torch.float32)
+
+    def embed_fused(self, x, lat, lon, lat0, lon0, wind, concat_lat):
+        """Raw fields -> bf16 backbone tokens [B, tokens, C]: pre-processing kernel (wind rotation,
+        latitude channels, patch gathering) + the patch-embedding GEMM; the de-aliased embedding
+        gathers pixel rows first and filters them while forming the patches."""
+        B, _, D, H, W = x.shape
+        _, _, _, Kp = self.patch_embed._gemm_weights()
+        if isinstance(self.patch_embed, DealiasedPatchEmbed3D):
+            cin = self.patch_embed.proj.in_channels
+            rows = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
+                                          patch=(1, 1, 1), k_pad=(cin + 7) // 8 * 8)
+            return self.patch_embed.tokens_from_pixel_rows(rows, (B, D, H, W))
+        a = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
+                                   patch=self.patch_size, k_pad=Kp)
+        return self.patch_embed.tokens_from_patches(a, B)
 
     def forward_fused(self, x: torch.Tensor, pos: torch.Tensor | None, *, lat=None, lon=None,
                       lat0=None, lon0=None, wind=None, concat_lat: bool = False) -> torch.Tensor:
@@ -315,10 +389,7 @@ class StrataTransformer3D(nn.Module):
         appends and casts the patch rows, one un-patchifies and rotates back."""
         B, _, D, H, W = x.shape
         grid = self.token_grid(D, H, W)
-        _, _, _, Kp = self.patch_embed._gemm_weights()
-        a = ops.preprocess_patches(x, lat, lon, lat0, lon0, wind=wind, concat_lat=concat_lat,
-                                   patch=self.patch_size, k_pad=Kp)
-        tokens = self.patch_embed.tokens_from_patches(a, B)
+        tokens = self.embed_fused(x, lat, lon, lat0, lon0, wind, concat_lat)
         cos, sin = self.rope_tables(pos, B, grid)
         tokens = self.forward_tokens(tokens, grid, cos, sin)
         y, _ = self.final_layer.matrix_bf16(tokens)

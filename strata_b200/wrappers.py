@@ -196,6 +196,19 @@ class _StrataModelBase(nn.Module):
         return x
 
 
+def _dealiased_embed(depth, height, width, patch, in_chans, embed_dim, resample_filter):
+    """The swapped-in de-aliased patch embedding with the reference's initialisation of it
+    (xavier-uniform on the flattened conv weight, zero bias: strata_wrappers.py:103-107)."""
+    from .strata import DealiasedPatchEmbed3D
+    pe = DealiasedPatchEmbed3D(depth=depth, height=height, width=width, patch_size=patch,
+                               in_chans=in_chans, embed_dim=embed_dim,
+                               resample_filter=resample_filter)
+    w = pe.proj.weight.data
+    nn.init.xavier_uniform_(w.view([w.shape[0], -1]))
+    nn.init.constant_(pe.proj.bias, 0.0)
+    return pe
+
+
 class StrataBackboneModel(_StrataModelBase):
     """Single-stage model (reference: strata_wrappers.py:252-415). Constructor argument
     names and defaults are the reference's."""
@@ -221,8 +234,6 @@ class StrataBackboneModel(_StrataModelBase):
                          wind_channel_indices=wind_channel_indices, grid_type=grid_type,
                          nside=nside, cubesphere_latlon_path=cubesphere_latlon_path,
                          index_is_latlon=index_is_latlon)
-        if use_dealiased_patch_embed:
-            raise ValueError("use_dealiased_patch_embed is not supported by this package yet")
         pv = patch_size_vert if patch_size_vert is not None else patch_size
         ph = patch_size_horiz if patch_size_horiz is not None else patch_size
         rope_mode = _rope_mode(do_rope_2d, do_rope_2d_stereographic)
@@ -240,6 +251,10 @@ class StrataBackboneModel(_StrataModelBase):
                                if rope_mode == "stereographic" else 1.0),
             activation_checkpointing=do_activation_checkpointing, bf16_mixed=do_bf16_mixed)
         _use_tanh_gelu(self.strata)
+        if use_dealiased_patch_embed:
+            self.strata.patch_embed = _dealiased_embed(depth, height, width, (pv, ph, ph),
+                                                       self.strata.in_channels, embed_dim,
+                                                       dealias_resample_filter)
 
     @property
     def _out_chans(self) -> int:
@@ -336,8 +351,6 @@ class StrataModel(_StrataModelBase):
                          cubesphere_latlon_path=sk.get("cubesphere_latlon_path",
                                                        "data/latlon_ne1024pg2.nc"),
                          index_is_latlon=sk.get("index_is_latlon", False))
-        if sk.get("use_dealiased_patch_embed", False):
-            raise ValueError("use_dealiased_patch_embed is not supported by this package yet")
         self._rope_length_scale_base = _resolve_rope_base(sk.get("rope_length_scale"))
         backbone_config = self._backbone_config(sk)
         if use_bilinear_dw_gelu_project_adaln_pixel and backbone_config["patch_size"][0] != 1:
@@ -361,6 +374,11 @@ class StrataModel(_StrataModelBase):
             bf16_mixed_pixel=do_bf16_mixed_pixel,
             activation_checkpointing_pixel=do_activation_checkpointing_pixel)
         _use_tanh_gelu(self.strata)
+        if sk.get("use_dealiased_patch_embed", False):
+            self.strata.backbone.patch_embed = _dealiased_embed(
+                *backbone_config["input_shape"], backbone_config["patch_size"],
+                backbone_config["in_channels"], backbone_config["embed_dim"],
+                sk.get("dealias_resample_filter", (1, 4, 6, 4, 1)))
         if freeze_semantic:
             for p in self.strata.backbone.parameters():
                 p.requires_grad_(False)

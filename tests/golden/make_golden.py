@@ -122,6 +122,28 @@ def main(ref_root):
         V_rec=Vr.numpy(),
         mean_lon_pm=tg.mean_longitude(lon, return_0_2pi=False).numpy(),
         rope_scale=np.array([tg.TileGeometry.default_rope_length_scale(s) for s in (1, 2, 4)]))
+    # ---- de-aliased patch embedding (reference module run in fp32 on seeded inputs)
+    import screamcast.dealias as dl
+    cases = {}
+    for name, (shape, patch, cin, cout, filt, seed) in {
+            "p144": ((2, 3, 8, 12), (1, 4, 4), 3, 8, (1, 4, 6, 4, 1), 11),
+            "p222": ((1, 4, 6, 4), (2, 2, 2), 2, 16, (1, 1), 12),
+            "p133": ((1, 2, 6, 9), (1, 3, 3), 4, 8, (1, 2, 1), 13)}.items():
+        torch.manual_seed(seed)
+        B, D, H, W = shape
+        mod = dl.DealiasedPatchEmbed3D(D, H, W, patch_size=patch, in_chans=cin, embed_dim=cout,
+                                       resample_filter=filt)
+        x = torch.randn(B, cin, D, H, W)
+        with torch.no_grad():
+            y = mod(x)
+        cases[name + "_x"] = x.numpy()
+        cases[name + "_w"] = mod.proj.weight.detach().numpy()
+        cases[name + "_b"] = mod.proj.bias.detach().numpy()
+        cases[name + "_y"] = y.numpy()
+        cases[name + "_patch"] = np.array(patch)
+        cases[name + "_filter"] = np.array(filt, dtype=np.float32)
+    np.savez_compressed(OUT / "dealias_patch_embed.npz", **cases)
+
     # parameter names of the two-stage model, in order (names only; the manifest holds no values)
     manifest = next(Path(ref_root, "tests", "regression_data").glob("pixeldit_*param_order.txt"))
     names = [ln.strip() for ln in manifest.read_text().splitlines() if ln.strip()]
