@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 
 from . import rope
+from .checkpoint_compat import remap_legacy_pre_hook
 from .strata import Mlp, StrataTransformer3D
 
 
@@ -163,6 +164,10 @@ class _StrataModelBase(nn.Module):
         self.geometry = TileGeometry(grid_type=grid_type, nside=nside,
                                      cubesphere_latlon_path=cubesphere_latlon_path,
                                      index_is_latlon=index_is_latlon)
+        # legacy checkpoint keys are translated inside the load machinery itself, so the
+        # translation also happens when this wrapper is a submodule of the module being loaded
+        # (reference: strata_wrappers.py:193-199)
+        self.register_load_state_dict_pre_hook(remap_legacy_pre_hook)
 
     @property
     def _index_is_latlon(self) -> bool:

@@ -148,7 +148,51 @@ def main(ref_root):
     manifest = next(Path(ref_root, "tests", "regression_data").glob("pixeldit_*param_order.txt"))
     names = [ln.strip() for ln in manifest.read_text().splitlines() if ln.strip()]
     (OUT / "two_stage_param_names.txt").write_text("\n".join(names) + "\n")
-    print("wrote", sorted(p.name for p in OUT.glob("*.npz")), "two_stage_param_names.txt")
+    # ---- legacy checkpoint key translation: the reference's remap run on legacy spellings of
+    # the manifest's names (built here by the inverse renames), on wrapper-prefixed variants, on
+    # keys it drops and on inputs it rejects
+    import json
+    import screamcast.checkpoint_compat as cc
+
+    def legacy_of(n, two_stage):
+        n = n[len("strata."):]
+        n = n.replace(".attn.gate_proj.", ".attn.gated_attention_map.")
+        n = n.replace(".mlp.layers.0.", ".mlp.fwd.0.").replace(".mlp.layers.2.", ".mlp.fwd.3.")
+        for new, old in (("backbone.patch_embed.", "semantic._patch_emb."),
+                         ("backbone.blocks.", "semantic._blocks."),
+                         ("pixel_patch_embed.", "_pixel_patch_emb."), ("pixel_blocks.", "_pixel_blocks."),
+                         ("pixel_final_layer.", "_pixel_final_layer."), ("patch_embed.", "_patch_emb."),
+                         ("blocks.", "_blocks."), ("final_layer.", "_final_layer.")):
+            if n.startswith(new):
+                return old + n[len(new):]
+        return n
+
+    single = next(Path(ref_root, "tests", "regression_data").glob("sweep1_*param_order.txt"))
+    single_names = [ln.strip() for ln in single.read_text().splitlines() if ln.strip()]
+    inputs = {
+        "two_stage": [legacy_of(n, True) for n in names],
+        "single_stage": [legacy_of(n, False) for n in single_names],
+        "compiled": ["_orig_mod." + legacy_of(n, True) for n in names[:40]],
+        "ddp_over_compiled": ["module._orig_mod." + legacy_of(n, False) for n in single_names[:20]],
+        "migrated_with_prefix": ["_orig_mod." + n for n in names[:30]],
+        "migrated": list(names[:30]),
+        "with_dropped": [legacy_of(n, True) for n in names[:12]]
+                        + ["semantic._final_layer.linear.weight", "_concat_skip_linear.weight"],
+        "mixed": [legacy_of(names[0], True), names[1]],
+        "duplicate_after_strip": ["_orig_mod." + names[0], names[0]],
+    }
+    cases = []
+    for cname, keys in inputs.items():
+        sd = {k: torch.zeros(1) for k in keys}
+        try:
+            new_sd, rep = cc.remap_legacy_state_dict(sd)
+            cases.append(dict(name=cname, input=keys, output=list(new_sd), was_legacy=rep.was_legacy,
+                              dropped=rep.dropped, passthrough=rep.passthrough))
+        except ValueError as exc:
+            cases.append(dict(name=cname, input=keys, raises=str(exc)[:40]))
+    (OUT / "checkpoint_remap.json").write_text(json.dumps(cases, indent=0))
+    print("wrote", sorted(p.name for p in OUT.glob("*.npz")), "two_stage_param_names.txt",
+          "checkpoint_remap.json")
 
 
 if __name__ == "__main__":
