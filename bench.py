@@ -322,6 +322,15 @@ def run_gpu_arm(args):
     # per-kernel breakdown (same sequence as strata_block_forward_bf16, one event pair each)
     breakdown = kernel_breakdown(torch, ops, x, weights, cs, (D, H, W), heads, kernel, hidden)
     sweep = na3d_sweep(torch, ops) if world == 1 else None
+    # secondary metric: one AdaLN pixel block of the two-stage model (1 GPU; tiles are independent)
+    pixel = None
+    if world == 1:
+        torch.cuda.empty_cache()
+        try:
+            pixel = pixel_stage_bench(torch, dev)
+        except Exception as exc:
+            pixel = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
 
     if rank == 0:
         tf_peak, hbm_peak, peak_kind = measured_peaks()
@@ -350,7 +359,7 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world,
                     "cpus_per_rank": numa_cpus},
-            "sphere_step": sphere, "tiled_blocks": tiled, "na3d_sweep": sweep,
+            "sphere_step": sphere, "tiled_blocks": tiled, "na3d_sweep": sweep, "pixel_stage": pixel,
             "gpu_launches": 7 * args.steps, "device_status": status, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

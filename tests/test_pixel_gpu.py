@@ -211,3 +211,21 @@ def test_two_stage_wrapper_contract():
     with torch.inference_mode():
         y = m(x, {"lat": lat.cuda(), "lon": lon.cuda()})
     assert y.shape == x.shape
+
+
+def test_sphere_stepper_runs_the_two_stage_model():
+    from strata_b200.rollout import TiledSphereStepper
+    from strata_b200.topology import TileTopology
+    topo = TileTopology(1, 0, face_size=32, tile_size=16, halo_width=8)
+    net = _randomise(_two_stage(height=32, width=32, in_chans=3, base_out_chans=3, n_layers=1,
+                                n_layers_pixel=1))
+    step = TiledSphereStepper(net, topo)
+    x = torch.randn(3, 4, topo.tiles_per_rank, 16, 16, device="cuda",
+                    generator=torch.Generator("cuda").manual_seed(1))
+    y = step(x)
+    assert y.shape == x.shape and torch.isfinite(y).all()
+    padded = step.halo(x).permute(2, 0, 1, 3, 4).contiguous()
+    with torch.inference_mode():
+        want = topo.crop(net(padded, {"lat": step.lat_rad, "lon": step.lon_rad})).permute(1, 2, 0, 3, 4)
+    assert torch.equal(y, want)
+    step.halo.check_status()
