@@ -100,7 +100,9 @@ class StrataPixel3DBlock(nn.Module):
             return m.reshape(B * D * pv * h * ph * w * pw, 6 * self.dim)   # one strided copy
         pixels = B * D * h * factor * w * factor
         mod = torch.empty((pixels, 6 * self.dim), dtype=torch.bfloat16, device=backbone_tokens.device)
-        chunk = min(pixels, _COND_CHUNK_ROWS)
+        # whole groups of `factor` image rows per chunk, so that no cell straddles two chunks
+        band = factor * w * factor
+        chunk = min(pixels, max(band, _COND_CHUNK_ROWS // band * band))
         buf = torch.empty((chunk, Cb), dtype=torch.bfloat16, device=backbone_tokens.device)
         for r0 in range(0, pixels, chunk):
             n = min(chunk, pixels - r0)
