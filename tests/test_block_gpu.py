@@ -119,6 +119,8 @@ NA_CASES = [
     # the 128-row tile without queries
     (1, 1, 20, 24, 1, (1, 13, 13)), (1, 2, 17, 19, 2, (1, 15, 15)), (1, 9, 16, 18, 1, (5, 15, 15)),
     (1, 3, 33, 16, 1, (3, 5, 11)),
+    # cubic windows of the pixel stage (int attn_kernel_pixel: 9 in production, 7 by default)
+    (1, 12, 16, 16, 2, (9, 9, 9)), (1, 10, 12, 20, 1, (7, 7, 7)), (1, 9, 9, 9, 1, (9, 9, 9)),
 ]
 
 
