@@ -675,7 +675,18 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   // rest in depth - as far as the tensor is deep and the key box stays within 16 planes.
   p.QW = kw <= 9 ? 8 : (kw <= 13 ? 4 : 2);
   if (p.QW == 8) {
-    if (D >= 2) { p.QD = 2; p.QH = 8; } else { p.QD = 1; p.QH = 16; }
+    // 16 query rows as 1 x 16, 2 x 8 or 4 x 4 (depth x height): the shape whose key box has the
+    // fewest (plane, 4-row) units - deep windows (kd >= 7) favour 4 x 4; ties keep the taller tile
+    int best_units = 1 << 30;
+    for (int qd = 1; qd <= 4; qd <<= 1) {
+      const int qh = 16 / qd;
+      if (qd > D || qd + kd - 1 > 16 || qh + kh - 1 > 31) continue;
+      const int units = (qd + kd - 1) * ((qh + kh - 1 + 3) / 4);
+      if (units < best_units || (units == best_units && qd == 2)) {
+        best_units = units; p.QD = qd; p.QH = qh;
+      }
+    }
+    if (best_units == (1 << 30)) return -2;
   } else {
     p.QH = 16;
     p.QD = 128 / (16 * p.QW);
