@@ -688,9 +688,21 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
     }
     if (best_units == (1 << 30)) return -2;
   } else {
-    p.QH = 16;
-    p.QD = 128 / (16 * p.QW);
-    while (p.QD > 1 && (p.QD > D || p.QD + kd - 1 > 16)) p.QD >>= 1;
+    // narrower tiles hold 32 (QW = 4) or 64 (QW = 2) query rows: 16 or 8 rows high, the rest in
+    // depth as far as the tensor is deep and the key box stays within 16 planes and 128 units;
+    // among those the shape with the fewest key units (ties keep 16 rows)
+    const int rows = 128 / p.QW;
+    int best_units = 1 << 30;
+    for (int qh = 16; qh >= 8; qh >>= 1) {
+      int qd = rows / qh;
+      while (qd > 1 && (qd > D || qd + kd - 1 > 16)) qd >>= 1;
+      if (qh + kh - 1 > 31) continue;
+      const int units = (qd + kd - 1) * ((qh + kh - 1 + 3) / 4);
+      // compare per query row: a shrunk depth leaves part of the tile empty
+      const long long cost = static_cast<long long>(units) * rows / (qd * qh);
+      if (units <= 128 && cost < best_units) { best_units = static_cast<int>(cost); p.QD = qd; p.QH = qh; }
+    }
+    if (best_units == (1 << 30)) return -2;
   }
   p.q_rows = p.QD * p.QH * p.QW;
   if (p.QH + kh - 1 > 31) return -2;
