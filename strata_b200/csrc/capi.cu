@@ -162,7 +162,25 @@ static int qkv_rope_impl(const void* x, int64_t ldx, const void* w, int64_t ldw,
   const auto* A = static_cast<const __nv_bfloat16*>(x);
   const auto* W = static_cast<const __nv_bfloat16*>(w);
   if (!rope_cs && !qk_norm) return launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
-  if (!rope_cs) return STRATA_ERR_UNSUPPORTED;  // qk norm without rotation: not on the path
+  if (!rope_cs) {
+    // qk norm without rotation (rope_mode 'none' with qk_norm=True): plain projection, then the
+    // in-place row kernel normalises the q and k heads.
+    if (head_dim != 64) return STRATA_ERR_UNSUPPORTED;
+    int r = launch_gemm<EPI_BIAS>(A, ldx, W, ldw, p, sms, as_stream(stream));
+    if (r != 0) return r;
+    if (pad_T > 0) {
+      // padded layout: the interior rows are not contiguous - normalise every row of the padded
+      // buffer (halo rows are overwritten by the exchange that follows)
+      const int P = pad_T + 2 * pad_halo;
+      const long long rows = static_cast<long long>(M) / (pad_T * pad_T) * P * P;
+      r = launch_qk_norm_rows(static_cast<__nv_bfloat16*>(qkv), ldqkv, rows, C, qk_eps, sms,
+                              as_stream(stream));
+    } else {
+      r = launch_qk_norm_rows(static_cast<__nv_bfloat16*>(qkv), ldqkv, M, C, qk_eps, sms,
+                              as_stream(stream));
+    }
+    return r == -2 ? STRATA_ERR_ARG : r;
+  }
   return launch_gemm<EPI_QKV_ROPE>(A, ldx, W, ldw, p, sms, as_stream(stream));
 }
 

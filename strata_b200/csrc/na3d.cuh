@@ -187,6 +187,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
   constexpr int EWP = Cfg::EWP;
   constexpr int NKEYS = Cfg::NKEYS;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int PC = Cfg::PCOLS_ROW;          // P columns (bf16 pairs) per key row
+  constexpr int UNIT_PCOLS = 4 * PC;          // P columns of one unit (4 key rows)
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   if ((sbase & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
@@ -197,7 +199,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
   auto k_smem = [&](int st) { return sbase + Cfg::KV_OFF + st * 2 * Cfg::KV_BYTES; };
   auto v_smem = [&](int st) { return k_smem(st) + Cfg::KV_BYTES; };
   const uint32_t bar = sbase + Cfg::BAR_OFF;
-  const uint32_t q_full = bar, q_empty = bar + 8, s_full = bar + 16, p_ready = bar + 24;
+  const uint32_t q_full = bar, q_empty = bar + 8, s_full = bar + 16, p_ready = bar + 24,
+                 s_free = bar + 96;
   auto kv_full = [&](int st) { return bar + 32u + 8u * st; };
   auto pv_done = [&](int st) { return bar + 64u + 8u * st; };   // K/V stage free, O updated
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 128);
@@ -206,12 +209,16 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nblk = p.nblk;
+  // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... (the grid never exceeds n_items)
+  const int n_my = (p.n_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                   static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(p_ready, 4);   // one arrival per softmax warp
+    mbar_init(s_free, 4);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(pv_done(s), 1);
@@ -235,13 +242,10 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       bool ok = true;
-      int n = 0, st = 0;
+      int st = 0;
       uint32_t ph = 0;
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
-        const NaItem it = na_decode_item<KW, QW>(item, p);
-        if (!mbar_wait(q_empty, (n & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) break;
-        mbar_expect_tx(q_full, static_cast<uint32_t>(p.q_rows) * 128u);
-        tma_load_5d(q_smem, &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full);
+      for (int n = 0; n < n_my && ok; ++n) {
+        const NaItem it = na_decode_item<KW, QW>(static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x), p);
         for (int i = 0; i < nblk; ++i) {
           if (!mbar_wait(pv_done(st), ph ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -259,6 +263,16 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
                         it.b, kv_full(st));
           }
           if (++st == STAGES) { st = 0; ph ^= 1u; }
+          if (i == 0) {
+            // the item's Q tile follows its first K/V block: the wait for the previous item's last
+            // Q K^T then does not hold that block back
+            if (!mbar_wait(q_empty, (n & 1u) ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(q_full, static_cast<uint32_t>(p.q_rows) * 128u);
+            tma_load_5d(q_smem, &tmQ, it.head * 64, it.w0, it.h0, it.d0, it.b, q_full);
+          }
         }
       }
       if (!ok)
@@ -281,61 +295,49 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       const uint32_t s_tmem = tmem_base + Cfg::S_COL;
       const uint32_t p_tmem = tmem_base + Cfg::P_COL;
       const uint32_t o_tmem = tmem_base + Cfg::O_COL;
+      const int G = n_my * nblk;   // key blocks of this CTA, over all its items
 
-      int qk_st = 0;
+      // Q K^T of block g (blocks are numbered through the CTA's items): needs the item's Q tile,
+      // the block's K unit pair and - from the second block on - the softmax warps' word that
+      // they have copied the previous scores out of S.
+      int qk_st = 0, qk_i = 0, qk_n = 0;
       uint32_t qk_ph = 0;
-      auto issue_qk = [&]() -> bool {
+      auto issue_qk = [&](int g) -> bool {
+        if (qk_i == 0 && !mbar_wait(q_full, qk_n & 1u, abort_flag, ST_TIMEOUT_MMA)) return false;
         if (!mbar_wait(kv_full(qk_st), qk_ph, abort_flag, ST_TIMEOUT_MMA)) return false;
+        if (g > 0 && !mbar_wait(s_free, (g - 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) return false;
         tc_fence_after();
         const uint32_t klo = k_lo0 + qk_st * STAGE_UNITS;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_ss(s_tmem, desc(q_lo + 2u * k), desc(klo + 2u * k), idesc_qk, k != 0 ? 1u : 0u);
         umma_commit(s_full);
+        if (++qk_i == nblk) {   // last Q K^T of the item: its completion frees the Q tile
+          umma_commit(q_empty);
+          qk_i = 0;
+          ++qk_n;
+        }
         if (++qk_st == STAGES) { qk_st = 0; qk_ph ^= 1u; }
         return true;
       };
 
-      bool ok = true;
-      int n = 0, pv_st = 0;
-      uint32_t gb = 0;
-      bool pre_issued = false;   // S of this item's block 0 was issued during the previous item
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n) {
-        if (!pre_issued) {
-          if (!mbar_wait(q_full, n & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
-          if (!issue_qk()) break;
-          if (nblk == 1) umma_commit(q_empty);
-        }
-        pre_issued = false;
-        for (int i = 0; i < nblk; ++i, ++gb) {
-          if (!mbar_wait(p_ready, gb & 1u, abort_flag, ST_TIMEOUT_MMA)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          // O += P V of this block ...
-          const uint32_t vlo = v_lo0 + pv_st * STAGE_UNITS;
+      bool ok = G > 0 && issue_qk(0);
+      int pv_st = 0, pv_i = 0;
+      for (int g = 0; g < G && ok; ++g) {
+        // scores of the next block first: they are computed while the softmax warps work on
+        // this one ...
+        if (g + 1 < G && !issue_qk(g + 1)) break;
+        // ... then O += P V of this block, once its P is in tensor memory
+        if (!mbar_wait(p_ready, g & 1u, abort_flag, ST_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t vlo = v_lo0 + pv_st * STAGE_UNITS;
 #pragma unroll
-          for (int s = 0; s < PV_STEPS; ++s)
-            umma_ts(o_tmem, p_tmem + 8 * s, desc(vlo + 128u * s), idesc_pv,
-                    (s != 0 || i != 0) ? 1u : 0u);
-          umma_commit(pv_done(pv_st));
-          if (++pv_st == STAGES) pv_st = 0;
-          // ... then the scores of the next block (of this item, or block 0 of the next item);
-          // its S-full arrival also tells the softmax warps that P has been consumed
-          if (i + 1 < nblk) {
-            if (!issue_qk()) { ok = false; break; }
-            if (i + 2 == nblk) umma_commit(q_empty);   // last Q K^T of this item issued
-          } else if (item + static_cast<int>(gridDim.x) < p.n_items) {
-            if (!mbar_wait(q_full, (n + 1) & 1u, abort_flag, ST_TIMEOUT_MMA)) {
-              ok = false;
-              break;
-            }
-            if (!issue_qk()) { ok = false; break; }
-            if (nblk == 1) umma_commit(q_empty);
-            pre_issued = true;
-          }
-        }
+        for (int s = 0; s < PV_STEPS; ++s)
+          umma_ts(o_tmem, p_tmem + 8 * s, desc(vlo + 128u * s), idesc_pv,
+                  (s != 0 || pv_i != 0) ? 1u : 0u);
+        umma_commit(pv_done(pv_st));
+        if (++pv_st == STAGES) pv_st = 0;
+        if (++pv_i == nblk) pv_i = 0;
       }
     }
   } else {
@@ -357,8 +359,8 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
     uint32_t gb = 0;
     int st_prev = STAGES - 1;     // ring stage and phase of block gb-1 (for pv_done)
     uint32_t ph_prev = 1;
-    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-      const NaItem it = na_decode_item<KW, QW>(item, p);
+    for (int n = 0; n < n_my && ok; ++n) {
+      const NaItem it = na_decode_item<KW, QW>(static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x), p);
       const bool q_ok = has_query && (it.d0 + zd < p.D) && (it.h0 + zh < p.q_h0 + p.q_H) &&
                         (it.w0 + zw < p.q_w0 + p.q_W);
       const int id = min(it.d0 + zd, p.D - 1), ih = min(it.h0 + zh, p.H - 1),
@@ -406,112 +408,160 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         tc_fence_after();
 
-        // The row loops below are deliberately not unrolled over rows: the whole per-block body
-        // stays a few kilobytes of code, which two resident CTAs can keep in the instruction
-        // caches; rows no query of the warp can see are skipped warp-uniformly.
-        bool take_max = warp_rows != 0u && __any_sync(0xffffffffu, has_query && l_run == 0.f);
-        bool settled = false;
-        float rs_blk;
-#pragma unroll 1
-        while (true) {
-          if (take_max) {
-            // masked maximum of this thread's visible scores (scaled form) ...
-            float bm = -1e30f;
-#pragma unroll 1
-            for (int rr = 0; rr < 8; ++rr) {
-              if (!((warp_rows >> rr) & 1u)) continue;
-              uint32_t a[EWP];
-              tmem_ld_keyrow<EWP>(s_taddr + rr * EWP, a);
-              tmem_ld_wait();
-              float rm0 = -1e30f, rm1 = -1e30f;
+        // The block's two units (4 key rows each) are handled one after the other with the
+        // unit's scores held in registers: as soon as the last unit the warp can see has been
+        // copied out of S, the warp gives S back (s_free) and the MMA warp computes the next
+        // block's scores while the exponentials of this one are still being evaluated. P is
+        // stored once the previous block's P V has completed (pv_done), which has normally
+        // happened long before.
+        bool s_released = false, p_free = false;
+        bool stored0 = false;     // unit 0 wrote non-zero P that a later move of the reference must rescale
 #pragma unroll
-              for (int k2 = 0; k2 < EW / 2; ++k2) {
-                float t0, t1;
-                unpack2(ffma2(pack2u(a[2 * k2], a[2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-                if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t need4 = (warp_rows >> (4 * u)) & 15u;   // rows some query of the warp sees
+          const uint32_t mine4 = (rowmask >> (4 * u)) & 15u;     // rows this query sees
+          const bool last_load = (u == 1) || ((warp_rows >> 4) == 0u);
+          uint32_t pk[UNIT_PCOLS];
+          if (need4 != 0u) {
+            uint32_t a[4][EWP];
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) tmem_ld_keyrow<EWP>(s_taddr + (4 * u + rr) * EWP, a[rr]);
+            tmem_ld_wait();
+            if (last_load && !s_released) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(s_free);
+              s_released = true;
+            }
+            bool take_max = __any_sync(0xffffffffu, has_query && l_run == 0.f);
+            bool settled = false;
+            float rs_unit;
+#pragma unroll 1
+            while (true) {
+              if (take_max) {
+                // masked maximum of this thread's visible scores (scaled form) ...
+                float bm = -1e30f;
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                  if (!((need4 >> rr) & 1u)) continue;
+                  float rm0 = -1e30f, rm1 = -1e30f;
+#pragma unroll
+                  for (int k2 = 0; k2 < EW / 2; ++k2) {
+                    float t0, t1;
+                    unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                    if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
+                  }
+                  bm = fmaxf(bm, ((mine4 >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
+                }
+                // ... moves the reference up by bm where that is called for: always while nothing
+                // has been accumulated yet (free), otherwise only beyond a margin of 2^8 - then the
+                // TMEM accumulator, the running sum and the P already stored for this block are
+                // rescaled (the previous block's P V must have completed first).
+                const bool fresh = l_run == 0.f;
+                const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
+                const bool rescale = grow && !fresh;
+                if (__any_sync(0xffffffffu, rescale)) {
+                  if (!p_free) {
+                    if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
+                    tc_fence_after();
+                    p_free = true;
+                  }
+                  const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
+                  l_run *= alpha;
+                  if (i != 0) {   // O of this item exists only after its first block
+#pragma unroll 1
+                    for (int hh = 0; hh < 4; ++hh) {
+                      uint32_t ob[16];
+                      tmem_ld_x16(o_taddr + 16 * hh, ob);
+                      tmem_ld_wait();
+#pragma unroll
+                      for (int j = 0; j < 16; ++j)
+                        ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+                      tmem_st_x16(o_taddr + 16 * hh, ob);
+                    }
+                  }
+                  if (u == 1 && stored0) {
+                    tmem_st_wait();   // unit 0's P stores have landed before they are read back
+#pragma unroll 1
+                    for (int hh = 0; hh < UNIT_PCOLS / 8; ++hh) {
+                      uint32_t pb[8];
+                      tmem_ld_x8(p_taddr + 8 * hh, pb);
+                      tmem_ld_wait();
+#pragma unroll
+                      for (int j = 0; j < 8; ++j)
+                        pb[j] = pack_bf16(bf16_lo(pb[j]) * alpha, bf16_hi(pb[j]) * alpha);
+                      tmem_st_x8(p_taddr + 8 * hh, pb);
+                    }
+                  }
+                  tmem_st_wait();
+                }
+                if (grow) {
+                  mc += bm;
+                  set_nb(mc);
+                }
+                settled = true;
               }
-              bm = fmaxf(bm, ((rowmask >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
-            }
-            // ... moves the reference up by bm where that is called for: always while nothing
-            // has been accumulated yet (free), otherwise only beyond a margin of 2^8 - then the
-            // TMEM accumulator and the running sum are rescaled (the previous block's P V has
-            // completed: its commit precedes this block's S-full commit).
-            const bool fresh = l_run == 0.f;
-            const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
-            const bool rescale = grow && !fresh;
-            if (__any_sync(0xffffffffu, rescale)) {
-              const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
-              l_run *= alpha;
-#pragma unroll 1
-              for (int hh = 0; hh < 4; ++hh) {
-                uint32_t ob[16];
-                tmem_ld_x16(o_taddr + 16 * hh, ob);
-                tmem_ld_wait();
+              // exponentials, row sum and bf16 P (two keys per 32-bit column)
+              uint64_t rs2 = 0ull;
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
-                tmem_st_x16(o_taddr + 16 * hh, ob);
-              }
-              tmem_st_wait();
-            }
-            if (grow) {
-              mc += bm;
-              set_nb(mc);
-            }
-            settled = true;
-          }
-          // exponentials, row sum and bf16 P (two keys per 32-bit column), two key rows at a time
-          uint64_t rs2 = 0ull;
-#pragma unroll 1
-          for (int pr = 0; pr < 4; ++pr) {
-            const uint32_t need2 = (warp_rows >> (2 * pr)) & 3u;
-            const uint32_t mine2 = (rowmask >> (2 * pr)) & 3u;
-            uint32_t pk[2][Cfg::PCOLS_ROW];
-            if (need2 == 0u) {
+              for (int rr = 0; rr < 4; ++rr) {
+                if (!((need4 >> rr) & 1u)) {
 #pragma unroll
-              for (int j = 0; j < Cfg::PCOLS_ROW; ++j) pk[0][j] = pk[1][j] = 0u;
-            } else {
-              uint32_t a[2][EWP];
-              tmem_ld_keyrow<EWP>(s_taddr + (2 * pr) * EWP, a[0]);
-              tmem_ld_keyrow<EWP>(s_taddr + (2 * pr + 1) * EWP, a[1]);
-              tmem_ld_wait();
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const bool mine = (mine2 >> h) & 1u;
+                  for (int j = 0; j < PC; ++j) pk[rr * PC + j] = 0u;
+                  continue;
+                }
+                const bool mine = (mine4 >> rr) & 1u;
                 const uint32_t keep = mine ? 0xffffffffu : 0u;
                 uint64_t rsa = 0ull, rsb = 0ull;
 #pragma unroll
-                for (int k2 = 0; k2 < Cfg::PCOLS_ROW; ++k2) {
+                for (int k2 = 0; k2 < PC; ++k2) {
                   uint32_t packed = 0u;
                   if (k2 < EW / 2) {
                     float t0, t1;
-                    unpack2(ffma2(pack2u(a[h][2 * k2], a[h][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                    unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
                     const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
                     if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
                     packed = pack_bf16(p0, p1) & keep;
                   }
-                  pk[h][k2] = packed;
+                  pk[rr * PC + k2] = packed;
                 }
                 if (mine) rs2 = fadd2(rs2, fadd2(rsa, rsb));
               }
+              {
+                float r0, r1;
+                unpack2(rs2, r0, r1);
+                rs_unit = r0 + r1;
+              }
+              // a sum this large (or infinite, or NaN) means a score far above the reference:
+              // take the maximum after all and redo the unit (its scores are still in registers)
+              if (settled || !__any_sync(0xffffffffu, !(rs_unit < SUM_LIMIT))) break;
+              take_max = true;
             }
-            if constexpr (EWP == 16) {
-              tmem_st_x16(p_taddr + 16 * pr, &pk[0][0]);
-            } else {
-              tmem_st_x8(p_taddr + 8 * pr, &pk[0][0]);
+            l_run += rs_unit;
+            if (u == 0) stored0 = true;
+          } else {
+#pragma unroll
+            for (int j = 0; j < UNIT_PCOLS; ++j) pk[j] = 0u;
+            if (last_load && !s_released) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(s_free);
+              s_released = true;
             }
           }
-          {
-            float r0, r1;
-            unpack2(rs2, r0, r1);
-            rs_blk = r0 + r1;
+          if (!p_free) {
+            if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
+            tc_fence_after();
+            p_free = true;
           }
-          // a sum this large (or infinite, or NaN) means a score far above the reference:
-          // take the maximum after all and redo the block (S is still intact)
-          if (settled || !__any_sync(0xffffffffu, !(rs_blk < SUM_LIMIT))) break;
-          take_max = true;
+          if constexpr (EWP == 16) {
+            tmem_st_x16(p_taddr + u * UNIT_PCOLS, &pk[0]);
+            tmem_st_x16(p_taddr + u * UNIT_PCOLS + 16, &pk[16]);
+          } else {
+            tmem_st_x16(p_taddr + u * UNIT_PCOLS, &pk[0]);
+          }
         }
-        l_run += rs_blk;
+        if (!ok) break;
         // every lane completes its P stores, then one lane arrives for the warp
         tmem_st_wait();
         tc_fence_before();
