@@ -11,6 +11,8 @@
  *     the device (a bounded wait that ran out) are recorded in a device status word read
  *     back with strata_device_status().
  *   - Unless stated otherwise no entry point allocates device memory; scratch is passed in.
+ *   - Entry points may be called from several host threads (one stream each); the few
+ *     per-device values the library caches on first use are stored atomically.
  *
  * The reference implements this path in Python on top of third-party kernels; each entry
  * point cites the reference call it stands in for (path inside the reference project).

@@ -4,6 +4,8 @@
 
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_tcgen05.cuh"
 #include "layernorm.cuh"
@@ -16,21 +18,24 @@ using namespace strata;
 
 namespace {
 
+// SM count of the current device (-1: no sm_100 device). The per-device cache is written with
+// relaxed atomics: concurrent first calls from several host threads store the same values.
 int current_sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
-  static int cached_dev = -1, cached_sms = 0, cached_major = 0;
-  if (dev != cached_dev) {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int> cached_sms[kMaxDev];     // 0 = not looked up yet, -1 = not sm_100
+  if (dev < 0 || dev >= kMaxDev) return -1;
+  int v = cached_sms[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
     int sms = 0, major = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
       return -1;
-    cached_dev = dev;
-    cached_sms = sms;
-    cached_major = major;
+    v = (major == 10 && sms > 0) ? sms : -1;
+    cached_sms[dev].store(v, std::memory_order_relaxed);
   }
-  if (cached_major != 10) return -1;
-  return cached_sms;
+  return v;
 }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
@@ -700,7 +705,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[STRATA_STATIC_SC
 
 namespace {
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_addr[kMaxDevices] = {};
+// written once per device with the same value by whichever host thread calls first
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];
 }  // namespace
 
 extern "C" int strata_block_forward_static_scratch_bf16(
@@ -716,15 +722,15 @@ extern "C" int strata_block_forward_static_scratch_bf16(
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
   if (dev < 0 || dev >= kMaxDevices) return STRATA_ERR_NO_DEVICE;
-  if (g_static_scratch_addr[dev] == nullptr) {
+  void* scratch = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // One-time set-up for this device (which is current): resolve the array's device address.
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    e = cudaGetSymbolAddress(&scratch, g_static_scratch);
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
-    if (p == nullptr) return STRATA_ERR_NO_DEVICE;
-    g_static_scratch_addr[dev] = p;
+    if (scratch == nullptr) return STRATA_ERR_NO_DEVICE;
+    g_static_scratch_addr[dev].store(scratch, std::memory_order_release);
   }
   return strata_block_forward_bf16(x, y, n_tiles, D, H, W, C, heads, hidden, kd, kh, kw, wts,
-                                   rope_cs, qk_norm, ln_eps, qk_eps,
-                                   g_static_scratch_addr[dev], STRATA_STATIC_SCRATCH_BYTES, stream);
+                                   rope_cs, qk_norm, ln_eps, qk_eps, scratch,
+                                   STRATA_STATIC_SCRATCH_BYTES, stream);
 }

@@ -30,6 +30,8 @@
 #pragma once
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -588,16 +590,16 @@ inline int launch_gemm_t(const __nv_bfloat16* A, long long lda, const __nv_bfloa
     cfg.numAttrs = 1;
     // A persistent grid must be resident at once: not every SM has a partner for a pair, so the
     // number of clusters that fit is asked for (once per kernel and device), not assumed.
-    static int max_clusters[64] = {0};
+    static std::atomic<int> max_clusters[64];   // per device; concurrent first calls store the same value
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return -24;
-    if (max_clusters[dev] == 0) {
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) return -24;
-      max_clusters[dev] = n;
+    int fit = max_clusters[dev].load(std::memory_order_relaxed);
+    if (fit == 0) {
+      if (cudaOccupancyMaxActiveClusters(&fit, kern, &cfg) != cudaSuccess || fit <= 0) return -24;
+      max_clusters[dev].store(fit, std::memory_order_relaxed);
     }
-    const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    const int clusters = tiles < fit ? tiles : fit;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, tmAux, p);
     return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;

@@ -726,7 +726,7 @@ inline int launch_na3d(const __nv_bfloat16* q, long long ldq, const __nv_bfloat1
   p.QW = kw <= 9 ? 8 : (kw <= 13 ? 4 : 2);
   if (p.QW == 8) {
     // 16 query rows as 1 x 16, 2 x 8 or 4 x 4 (depth x height): the shape whose key box has the
-    // fewest (plane, 4-row) units - deep windows (kd >= 7) favour 4 x 4; ties keep the taller tile
+    // fewest (plane, 4-row) units - deep windows (kd >= 7) favour 4 x 4; a tie goes to 2 x 8
     int best_units = 1 << 30;
     for (int qd = 1; qd <= 4; qd <<= 1) {
       const int qh = 16 / qd;

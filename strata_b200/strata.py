@@ -14,8 +14,11 @@ manifest (tests/regression_data/sweep1_*.param_order.txt):
 
 so checkpoints keyed `strata.*` load unchanged. The blocks run in bf16 through
 libstrata_b200.so (fused QKV+RoPE GEMM, 3-D neighbourhood attention, GELU / residual GEMM
-epilogues); there is no PyTorch fallback for them. The patch embedding and the final
-projection are once-per-forward library calls (cuDNN conv / cuBLAS), as in the reference.
+epilogues); there is no PyTorch fallback for them. The patch embedding (one strided bf16 copy
+of the patches, or the fused pre-processing kernel) and the final projection (LayerNorm kernel)
+feed the same tcgen05 GEMM. The one place foreign code runs is a `patch_embed` module that a
+caller has assigned in place of the two this package provides (the reference leaves that
+attribute assignable): it is the caller's module and is executed as given.
 """
 from __future__ import annotations
 
@@ -352,7 +355,8 @@ class StrataTransformer3D(nn.Module):
             tokens = self.patch_embed.tokens_bf16(x.contiguous())
         elif isinstance(self.patch_embed, DealiasedPatchEmbed3D):
             tokens = self.patch_embed(x).flatten(2).transpose(1, 2).contiguous()
-        else:   # a caller-assigned embed module: run it as it is
+        else:   # a caller-assigned embed module (not one of this package's): the caller's own
+            # code, run as it is - the only step of the forward that is not a kernel of this library
             with torch.autocast("cuda", dtype=torch.bfloat16, enabled=x.is_cuda):
                 tokens = self.patch_embed(x)
             tokens = tokens.to(torch.bfloat16).contiguous()

@@ -39,6 +39,58 @@ FACE_LINKS = (
 )
 
 
+# ---------------------------------------------------------------- element order <-> face rasters
+# The model's native column order lists, face by face, the ne x ne spectral elements and inside
+# each element its npg x npg physics points; a face raster is the (ne*npg) x (ne*npg) image of
+# the same values. Pure index permutations (bit-exact), interface of
+# screamcast/cubesphere_transforms.py:20-146.
+
+def _swap_element_axes(x: torch.Tensor, lead: tuple, a: int, b: int, c: int, d: int) -> torch.Tensor:
+    """View the trailing block as [a, b, c, d] and exchange the two middle axes."""
+    n = len(lead)
+    return x.reshape(*lead, a, b, c, d).transpose(n + 1, n + 2)
+
+
+def reorder_cubesphere_to_2d_tensor(array: torch.Tensor, *, ne: int, npg: int) -> torch.Tensor:
+    """(..., ne*ne*npg*npg) element-major values of one face -> (..., ne*npg, ne*npg) raster."""
+    if ne <= 0 or npg <= 0:
+        raise ValueError(f"ne and npg must be positive, got ne={ne}, npg={npg}")
+    expected = ne * ne * npg * npg
+    if array.size(-1) != expected:
+        raise ValueError(f"Expected last dim = {expected} (=ne^2*npg^2), got {array.size(-1)}")
+    lead = tuple(array.shape[:-1])
+    return _swap_element_axes(array, lead, ne, ne, npg, npg).reshape(*lead, ne * npg, ne * npg)
+
+
+def reorder_2d_tensor_to_cubesphere(array: torch.Tensor, *, ne: int, npg: int) -> torch.Tensor:
+    """Inverse of reorder_cubesphere_to_2d_tensor: (..., ne*npg, ne*npg) -> (..., ne*ne*npg*npg)."""
+    if ne <= 0 or npg <= 0:
+        raise ValueError(f"ne and npg must be positive, got ne={ne}, npg={npg}")
+    side = ne * npg
+    if array.shape[-1] != side or array.shape[-2] != side:
+        raise ValueError(f"Expected last two dims = ({side}, {side}), got {tuple(array.shape[-2:])}")
+    lead = tuple(array.shape[:-2])
+    return _swap_element_axes(array, lead, ne, npg, ne, npg).reshape(*lead, ne * ne * npg * npg)
+
+
+def unstructured_to_6faces(data: torch.Tensor, ne: int = 1024, npg: int = 2) -> torch.Tensor:
+    """(..., 6*ne^2*npg^2) global columns -> (..., 6, ne*npg, ne*npg) face rasters."""
+    per_face = (ne * npg) ** 2
+    if data.shape[-1] != 6 * per_face:
+        raise ValueError(f"Expected last dim = {6 * per_face} (=6*ne^2*npg^2), got {data.shape[-1]}")
+    faces = data.reshape(*data.shape[:-1], 6, per_face)
+    return reorder_cubesphere_to_2d_tensor(faces, ne=ne, npg=npg)
+
+
+def faces_to_unstructured(data: torch.Tensor, ne: int = 1024, npg: int = 2) -> torch.Tensor:
+    """Inverse of unstructured_to_6faces: (..., 6, ne*npg, ne*npg) -> (..., 6*ne^2*npg^2)."""
+    side = ne * npg
+    if data.dim() < 3 or tuple(data.shape[-3:]) != (6, side, side):
+        raise ValueError(f"Expected last 3 dims = (6, {side}, {side}), got {tuple(data.shape[-3:])}")
+    flat = reorder_2d_tensor_to_cubesphere(data, ne=ne, npg=npg)
+    return flat.reshape(*data.shape[:-3], 6 * side * side)
+
+
 @dataclass(frozen=True)
 class TileTopology:
     """Distributed cubed-sphere tile decomposition (same fields and methods as the reference)."""

@@ -1,8 +1,11 @@
 """GPU parity of the kernels and of the whole block against the CPU oracle, through the C ABI.
 
-Tolerances (stated by the task): bf16 outputs within 2e-2 max-abs relative error of the fp32
-oracle; against the oracle that rounds to bf16 at the same points as the GPU path
-(fp32 accumulation on both sides) the relative RMS difference stays below 1e-3.
+Tolerances (stated by the task): bf16 outputs within 2e-2 max-abs relative error
+(max|got - want| / max|want|) of the fp32 oracle. The "fp32-accumulate agreement <= 1e-3" is
+taken in the relative RMS norm (rms(got - want) / rms(want)) against the oracle that rounds to
+bf16 at the same points as the GPU path with fp32 accumulation on both sides; the max-abs figure
+of that comparison is bounded too (one bf16 ulp of the largest value = 2^-8, i.e. 4e-3 relative,
+doubled for values that round the other way) and printed with the RMS.
 """
 import pytest
 import torch
@@ -12,7 +15,8 @@ from tests.util import device_block_weights, rel_max_err, rel_rms_err, tile_latl
 
 pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
-TOL_FP32_ACC = 1e-3
+TOL_FP32_ACC = 1e-3        # relative RMS vs the bf16-rounding oracle
+TOL_FP32_ACC_MAX = 8e-3    # max-abs relative of the same comparison (two bf16 ulps)
 
 
 @pytest.fixture(scope="module")
@@ -245,3 +249,81 @@ def test_host_pipeline_matches_device_call(ops):
     assert _status() == 0
     with pytest.raises(TypeError):
         pipe.run(x, y_host, w, grid=grid, num_heads=heads, kernel=kernel)   # not pinned
+
+
+# ---------------------------------------------------------------------------------------------
+# The shapes the benchmark times (one tile each, so that the CPU oracle finishes in seconds):
+# wide GEMMs run as CTA pairs, the attention grid runs several waves of work items per CTA.
+
+def _block_case(ops, C, heads, grid, kernel, n_tiles=1, gated=False, qk_norm=False, seed=3):
+    D, H, W = grid
+    p = bo.init_block_params(C, gated=gated, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(n_tiles, D * H * W, C, generator=g)
+    lat, lon = tile_latlon(n_tiles, H, W)
+    cos, sin = bo.stereographic_rope_tables(lat, lon, C // heads, 1, bo.default_rope_length_scale(1))
+    y = ops.block_forward(x.bfloat16().cuda().contiguous(), device_block_weights(p, "cuda"),
+                          grid=grid, num_heads=heads, kernel=kernel, rope_cos=cos.cuda(),
+                          rope_sin=sin.cuda(), qk_norm=qk_norm)
+    assert _status() == 0
+    kw = dict(grid=grid, num_heads=heads, kernel=kernel, rope_cos=cos, rope_sin=sin,
+              qk_norm=qk_norm, gated=gated)
+    ref = bo.block_forward(x.bfloat16().float(), p, **kw)
+    ref_bf16 = bo.block_forward(x.bfloat16().float(), p, emulate_bf16=True, **kw)
+    e_max, e_rms, e_rms_max = rel_max_err(y, ref), rel_rms_err(y, ref_bf16), rel_max_err(y, ref_bf16)
+    print(f"block C={C} heads={heads} grid={grid} kernel={kernel}: max-abs rel vs fp32 {e_max:.2e}; "
+          f"vs bf16-rounding oracle: rms {e_rms:.2e}, max-abs {e_rms_max:.2e}")
+    assert e_max < TOL_BF16
+    assert e_rms < TOL_FP32_ACC
+    assert e_rms_max < TOL_FP32_ACC_MAX
+
+
+def test_block_forward_benchmark_tile(ops):
+    # one tile of the headline workload: 16 x 64 x 64 tokens, dim 512, 8 heads, kernel (3, 9, 9),
+    # stereographic RoPE (65 536 rows: CTA-pair GEMMs, 4096 attention work items over 296 CTAs)
+    _block_case(ops, 512, 8, (16, 64, 64), (3, 9, 9))
+
+
+@pytest.mark.parametrize("C,heads,grid,kernel,gated,qk_norm", [
+    (768, 12, (6, 16, 32), (5, 13, 13), False, False),    # width / kernel of the 12-block encoder
+    (1024, 16, (4, 32, 32), (3, 9, 9), True, True),       # width of the 24-block global model
+])
+def test_block_forward_wide_models(ops, C, heads, grid, kernel, gated, qk_norm):
+    _block_case(ops, C, heads, grid, kernel, gated=gated, qk_norm=qk_norm, seed=5)
+
+
+@pytest.mark.parametrize("kernel,nh,D", [((3, 7, 7), 2, 6), ((3, 13, 13), 1, 8), ((5, 15, 15), 1, 8)])
+def test_na3d_sweep_plane_size(ops, kernel, nh, D):
+    # the standalone attention sweep's 96 x 96 planes and head_dim 64 (fewer planes and heads)
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (torch.randn(1, D, 96, 96, nh, 64, generator=g).bfloat16() for _ in range(3))
+    o = ops.na3d(q.cuda(), k.cuda(), v.cuda(), kernel)
+    assert _status() == 0
+    ref = bo.na3d(q.float(), k.float(), v.float(), kernel)
+    assert rel_max_err(o, ref) < TOL_BF16
+
+
+def test_qkv_without_rope_but_with_qk_norm(ops):
+    # rope_mode 'none' with qk_norm=True (accepted by the wrappers): projection, then the row
+    # kernel normalises the q and k heads
+    n_tiles, D, H, W, C, hd = 1, 2, 8, 8, 128, 64
+    heads = C // hd
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(n_tiles * D * H * W, C, generator=g).bfloat16()
+    w = (torch.randn(3 * C, C, generator=g) * 0.08).bfloat16()
+    b = torch.randn(3 * C, generator=g) * 0.1
+    y = ops.qkv_rope(x.cuda(), w.cuda(), b.cuda(), hd, None, None, D * H * W, H * W, qk_norm=True)
+    assert _status() == 0
+    qkv = (x.float() @ w.float().T + b).reshape(-1, 3, heads, hd)
+    q, k, v = bo.rms_norm(qkv[:, 0]), bo.rms_norm(qkv[:, 1]), qkv[:, 2]
+    ref = torch.stack([q, k, v], dim=1).reshape(-1, 3 * C)
+    assert rel_max_err(y, ref) < TOL_BF16
+    # and the whole block in that configuration
+    p = bo.init_block_params(C, seed=2)
+    xb = torch.randn(1, D * H * W, C, generator=g)
+    yb = ops.block_forward(xb.bfloat16().cuda().contiguous(), device_block_weights(p, "cuda"),
+                           grid=(D, H, W), num_heads=heads, kernel=(1, 3, 3), rope_cos=None,
+                           rope_sin=None, qk_norm=True)
+    ref_b = bo.block_forward(xb.bfloat16().float(), p, grid=(D, H, W), num_heads=heads,
+                             kernel=(1, 3, 3), rope_cos=None, rope_sin=None, qk_norm=True, gated=False)
+    assert rel_max_err(yb, ref_b) < TOL_BF16

@@ -91,3 +91,22 @@ def test_interior_tile_halo_equals_neighbour_data():
     g = full.global_tiles.index((2, 1, 2))
     want = x[2, 1 * ts - hw:2 * ts + hw, 2 * ts - hw:3 * ts + hw]
     assert np.array_equal(padded[g], want)
+
+
+def test_element_order_to_face_rasters(golden_dir):
+    # outputs of the reference's own functions on a 3-element, 2-point face (bit-exact)
+    g = np.load(golden_dir / "face_padding.npz")
+    u = torch.from_numpy(g["reorder_in"])
+    faces = tp.unstructured_to_6faces(u, ne=3, npg=2)
+    assert torch.equal(faces, torch.from_numpy(g["reorder_faces"]))
+    back = tp.faces_to_unstructured(faces, ne=3, npg=2)
+    assert torch.equal(back, torch.from_numpy(g["reorder_back"])) and torch.equal(back, u)
+    one = tp.reorder_cubesphere_to_2d_tensor(u[:, :36], ne=3, npg=2)
+    assert torch.equal(one, faces[:, 0])
+    assert torch.equal(tp.reorder_2d_tensor_to_cubesphere(one, ne=3, npg=2), u[:, :36])
+    with pytest.raises(ValueError, match="must be positive"):
+        tp.reorder_cubesphere_to_2d_tensor(u, ne=0, npg=2)
+    with pytest.raises(ValueError, match="Expected last dim"):
+        tp.unstructured_to_6faces(u[:, :-1], ne=3, npg=2)
+    with pytest.raises(ValueError, match="Expected last 3 dims"):
+        tp.faces_to_unstructured(faces[:, :5], ne=3, npg=2)

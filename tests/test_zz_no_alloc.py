@@ -54,10 +54,21 @@ def test_static_scratch_block_matches_workspace_block():
         want = ops.block_forward(x, w, grid=grid, num_heads=heads, kernel=kernel, rope_cos=cos,
                                  rope_sin=sin)
         got = torch.full_like(x, float("nan"))
+        if call == 1:
+            # The entry point's whole contract: it obtains no device memory. From the second
+            # call on (the first one may still load the kernels' code onto the device) neither
+            # the driver's free-memory figure nor torch's allocator moves across the call.
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            torch_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         rc = lib.strata_block_forward_static_scratch_bf16(
             x.data_ptr(), got.data_ptr(), n_tiles, D, H, W, C, heads, hidden, *kernel,
             ctypes.byref(ws_struct), cs.data_ptr(), 0, 1e-6, 1e-6, stream)
         assert rc == 0, lib.strata_error_string(rc)
+        if call == 1:
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
         assert _lib.device_status() == 0
         assert not torch.isnan(got).any()
         assert rel_max_err(got, want.float()) < TOL_BF16
