@@ -278,7 +278,11 @@ int strata_dealias_patches_bf16(const void* x_rows, int64_t ldx, int B, int C, i
  * [me] of every rank's flag array h_flags[r] (int32[world], zero-initialised, peer-mapped) and
  * waits - for at most timeout_ms - until all slots of this rank's own array reached it. Work
  * enqueued before it is visible to the peers' kernels enqueued after their barrier. A timeout
- * sets device status 105. Every rank must run on its own GPU. */
+ * sets device status 105 and, until the next barrier that completes or until the status is
+ * cleared with strata_device_status(.., reset = 1), makes every halo gather / adjoint kernel of
+ * this device fill its output with NaN (the peers' data may be missing or stale): a failed
+ * exchange cannot pass for a good one even if the caller polls the status rarely. Every rank
+ * must run on its own GPU. */
 int strata_halo_barrier(int* const* h_flags, int me, int world, int epoch, int timeout_ms,
                         void* stream);
 

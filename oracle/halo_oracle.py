@@ -254,6 +254,37 @@ def halo_adjoint(padded_all: np.ndarray, topo: TileTopology, window: np.ndarray 
     return (acc / wsum).astype(np.float32).reshape(*lead, topo.tiles_per_rank, T, T)
 
 
+def knn_halo_adjoint(padded_all: np.ndarray, topo: TileTopology, idx_all: np.ndarray,
+                     w_all: np.ndarray, window: np.ndarray | None = None):
+    """D_w^-1 A^T (w . y) for the k-nearest-neighbour halo A (out[p] = sum_j w[p,j] x[idx[p,j]]),
+    the operator of the reference's NormalizedHaloAdjoint (screamcast/distributed_halo.py:330-448),
+    evaluated densely in float64: scatter-add of every padded cell's windowed value to its k
+    sources, divided by the scatter-add of the window itself.
+
+    padded_all: (..., total_tiles, P, P), idx_all / w_all: [total_tiles*P*P, k] for the padded
+    cells of every tile in global tile order. Returns this rank's (..., tiles_per_rank, T, T).
+    """
+    T, P, G = topo.tile_size, topo.padded_tile_size, topo.total_tiles
+    w = np.ones((P, P)) if window is None else np.asarray(window, np.float64)
+    wflat = np.tile(w.reshape(-1), G)
+    lead = padded_all.shape[:-3]
+    y = padded_all.reshape(*lead, -1).astype(np.float64) * wflat
+    n_src = G * T * T
+    acc = np.zeros((*lead, n_src))
+    wsum = np.zeros(n_src)
+    for j in range(idx_all.shape[1]):
+        np.add.at(wsum, idx_all[:, j], w_all[:, j].astype(np.float64) * wflat)
+        flat_acc = acc.reshape(-1, n_src)
+        flat_y = y.reshape(-1, y.shape[-1])
+        for r in range(flat_acc.shape[0]):
+            np.add.at(flat_acc[r], idx_all[:, j], w_all[:, j].astype(np.float64) * flat_y[r])
+    n_local = topo.tiles_per_rank * T * T
+    lo = topo.rank * n_local
+    with np.errstate(invalid="ignore", divide="ignore"):
+        out = acc[..., lo:lo + n_local] / wsum[lo:lo + n_local]
+    return out.reshape(*lead, topo.tiles_per_rank, T, T)
+
+
 def knn_halo(all_tiles: np.ndarray, topo: TileTopology, lon_deg: np.ndarray, lat_deg: np.ndarray,
              pad_width_data: int, k: int = 4, eps: float = 1e-7):
     """k-nearest-neighbour halo of this rank's tiles, after

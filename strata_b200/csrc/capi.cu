@@ -73,8 +73,11 @@ int strata_device_status(int* h_status, int reset) {
   e = cudaMemcpyFromSymbol(h_status, g_status, sizeof(int));
   if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
   if (reset && *h_status != 0) {
-    int zero = 0;
+    int zero = 0, one = 1;
     e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    // a failed halo barrier also left the "exchange ok" word at 0 (gathers write NaN meanwhile)
+    e = cudaMemcpyToSymbol(g_halo_ok, &one, sizeof(int));
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
   }
   return STRATA_OK;

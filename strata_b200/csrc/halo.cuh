@@ -29,6 +29,17 @@ struct FlagPtrs {
   int* p[HALO_MAX_RANKS];
 };
 
+// 1 while the last cross-GPU flag barrier on this device completed (or none has run), 0 after
+// one whose bounded wait ran out. The gather kernels that follow a barrier on the stream read
+// it: after a failed barrier the peers' slots may be unpublished or stale, so they fill their
+// output with NaN instead of plausible-looking numbers. Set back to 1 by the next barrier that
+// completes, or when the host clears the device status word.
+__device__ int g_halo_ok = 1;
+__device__ __forceinline__ bool halo_exchange_failed() {
+  return *reinterpret_cast<volatile int*>(&g_halo_ok) == 0;
+}
+constexpr uint32_t BF16_NAN2 = 0x7fc07fc0u;
+
 // Token layout: source buffers [tiles_per_rank, D, T*T, C] bf16, output [tiles_per_rank, D, P*P, C].
 // grid: x over (padded cell, 16-byte vector) pairs, y over (tile, depth).
 __global__ void __launch_bounds__(256)
@@ -39,6 +50,7 @@ halo_gather_tokens_kernel(__nv_bfloat16* __restrict__ out, const PeerPtrs src,
   const int vpc = C >> 3;  // 16-byte vectors per cell
   const int tile = blockIdx.y / D;
   const int d = blockIdx.y - tile * D;
+  const bool failed = halo_exchange_failed();
   const long long total = static_cast<long long>(PP) * vpc;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -72,6 +84,7 @@ halo_gather_tokens_kernel(__nv_bfloat16* __restrict__ out, const PeerPtrs src,
         rw[t] = pack_bf16(lo, hi);
       }
     }
+    if (failed) r = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
     const long long ooff = ((static_cast<long long>(tile) * D + d) * PP + pc) * C + (v << 3);
     *reinterpret_cast<uint4*>(out + ooff) = r;
   }
@@ -83,6 +96,7 @@ __global__ void __launch_bounds__(256)
 halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
                           const int* __restrict__ src_a, const int* __restrict__ src_b,
                           int n_out_cells, int cells_per_rank, int L) {
+  const bool failed = halo_exchange_failed();
   for (int oc = blockIdx.x * blockDim.x + threadIdx.x; oc < n_out_cells;
        oc += gridDim.x * blockDim.x) {
     const int a = __ldg(src_a + oc);
@@ -98,7 +112,7 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
       const long long so = static_cast<long long>(l) * cells_per_rank;
       float v = pa[so];
       if (pb) v = (v + pb[so]) / 2.0f;
-      out[static_cast<long long>(l) * n_out_cells + oc] = v;
+      out[static_cast<long long>(l) * n_out_cells + oc] = failed ? __int_as_float(0x7fc00000) : v;
     }
   }
 }
@@ -114,6 +128,7 @@ __global__ void __launch_bounds__(256)
 halo_gather_knn_fields_kernel(float* __restrict__ out, const PeerPtrs src,
                               const int* __restrict__ idx, const float* __restrict__ w,
                               int n_out_cells, int cells_per_rank, int L) {
+  const bool failed = halo_exchange_failed();
   for (int oc = blockIdx.x * blockDim.x + threadIdx.x; oc < n_out_cells;
        oc += gridDim.x * blockDim.x) {
     const float* sp[K];
@@ -130,7 +145,7 @@ halo_gather_knn_fields_kernel(float* __restrict__ out, const PeerPtrs src,
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < K; ++j) acc = __fadd_rn(acc, __fmul_rn(wk[j], sp[j][so]));
-      out[static_cast<long long>(l) * n_out_cells + oc] = acc;
+      out[static_cast<long long>(l) * n_out_cells + oc] = failed ? __int_as_float(0x7fc00000) : acc;
     }
   }
 }
@@ -151,9 +166,12 @@ halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
                            int padded_cells_per_rank, int PP, int L) {
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n_cells; c += gridDim.x * blockDim.x) {
     const int e0 = __ldg(offsets + c), e1 = __ldg(offsets + c + 1);
-    const float wsum = __ldg(weights + c);
-    // coef is 1 or 1/2, so coef * (window * y) == (coef * window) * y bit for bit: the per-entry
-    // factor and source pointer are set up once, outside the loop over the leading index
+    // (after a failed barrier the divisor is NaN, and with it every output)
+    const float wsum = halo_exchange_failed() ? __int_as_float(0x7fc00000) : __ldg(weights + c);
+    // with the copy halo's coefficients (1 or 1/2) coef * (window * y) == (coef * window) * y bit
+    // for bit, so the per-entry factor and source pointer are set up once, outside the loop over
+    // the leading index (general coefficients - the k-nearest-neighbour lists - agree with the
+    // long-list branch below to rounding only)
     constexpr int FAST = 4;
     const int ne = e1 - e0;
     if (ne <= FAST) {
@@ -305,6 +323,7 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
       o4.y = pack_bf16(ra[2], ra[3]);
       o4.z = pack_bf16(ra[4], ra[5]);
       o4.w = pack_bf16(ra[6], ra[7]);
+      if (halo_exchange_failed()) o4 = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
       *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
     }
   }
@@ -318,6 +337,7 @@ __global__ void halo_barrier_kernel(const FlagPtrs flags, int me, int world, int
                                     long long limit_cycles) {
   const int r = threadIdx.x;
   if (r >= world) return;
+  if (r == 0) *reinterpret_cast<volatile int*>(&g_halo_ok) = 1;   // long before any wait can run out
   __threadfence_system();
   int* remote = flags.p[r] + me;
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
@@ -329,6 +349,7 @@ __global__ void halo_barrier_kernel(const FlagPtrs flags, int me, int world, int
     if (v >= epoch) break;
     if (clock64() - t0 > limit_cycles) {
       atomicCAS(&g_status, 0, ST_TIMEOUT_PEER_FLAG);
+      *reinterpret_cast<volatile int*>(&g_halo_ok) = 0;   // the gathers behind this barrier write NaN
       break;
     }
     __nanosleep(200);

@@ -28,7 +28,8 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .topology import TileTopology, halo_adjoint_lists, halo_source_maps, knn_halo_weights
+from .topology import (TileTopology, halo_adjoint_lists, halo_source_maps, knn_adjoint_lists,
+                       knn_halo_weights)
 
 
 class _DevPtrTensorView:
@@ -115,6 +116,7 @@ class DistributedTileCopyHaloPadding(torch.nn.Module):
         self._shared = None
         self._slot_bytes = 0
         self._epoch = 0
+        self._stream = None     # the stream every exchange through this module is issued on
         self._max_bytes = int(max_bytes_per_call)
         if topology.world_size > 1:
             if not dist.is_initialized():
@@ -158,8 +160,19 @@ class DistributedTileCopyHaloPadding(torch.nn.Module):
             arr = (ctypes.c_void_p * 1)()
             arr[0] = x_flat_bytes.data_ptr()
             return arr
+        # The two alternating slots are safe only while every exchange through this module (the
+        # un-pad adjoint shares its buffer) is issued on ONE stream, in the same order on all
+        # ranks: a second stream could overwrite a slot a peer is still reading.
+        cur = torch.cuda.current_stream().cuda_stream
+        if self._stream is None:
+            self._stream = cur
+        elif self._stream != cur:
+            raise RuntimeError("halo exchanges of one module must all be issued on the same CUDA "
+                               "stream (first used: %#x, now: %#x)" % (self._stream, cur))
         nbytes = x_flat_bytes.numel()
         if self._shared is None or nbytes > self._slot_bytes:
+            # growth re-allocates the peer-shared buffer: a collective (synchronise, barrier,
+            # IPC handles) - size it with max_bytes_per_call to keep it out of the steps
             self._ensure_shared(nbytes)
         self._epoch += 1
         off = self.FLAG_BYTES + (self._epoch & 1) * self._slot_bytes
@@ -171,7 +184,9 @@ class DistributedTileCopyHaloPadding(torch.nn.Module):
         return self._shared.ptr_array(off)
 
     def check_status(self) -> None:
-        """Synchronise and raise if a peer never reached a barrier (or any kernel timed out)."""
+        """Synchronise and raise if a peer never reached a barrier (or any kernel timed out).
+        Until this is called (it clears the condition) every padded tile produced after the
+        failed barrier is NaN, so a missed poll cannot let a rollout continue on stale halos."""
         st = _lib.device_status()
         if st != 0:
             raise RuntimeError(f"halo exchange failed on the device (status {st}: "
@@ -323,12 +338,15 @@ class NormalizedCopyHaloAdjoint(torch.nn.Module):
 
     def __init__(self, halo_exchange: DistributedTileCopyHaloPadding, window: torch.Tensor | None = None):
         super().__init__()
+        if type(self) is NormalizedCopyHaloAdjoint and isinstance(halo_exchange, DistributedTileKNNHaloPadding):
+            raise TypeError("NormalizedCopyHaloAdjoint transposes the copy halo; for a "
+                            "DistributedTileKNNHaloPadding module use NormalizedHaloAdjoint")
         self.halo_exchange = halo_exchange
         topo = halo_exchange.topology
         P = topo.padded_tile_size
         dev = halo_exchange.src_a.device
         w = None if window is None else window.detach().to("cpu", torch.float32).numpy()
-        offsets, cell, coef, weights = halo_adjoint_lists(topo, w)
+        offsets, cell, coef, weights = self._lists(halo_exchange, w)
         self.register_buffer("_offsets", torch.from_numpy(offsets).to(dev), persistent=False)
         self._cell = torch.from_numpy(cell).to(dev)
         self._coef = torch.from_numpy(coef).to(dev)
@@ -336,6 +354,10 @@ class NormalizedCopyHaloAdjoint(torch.nn.Module):
         self.register_buffer("window", win.reshape(-1).to(dev).contiguous(), persistent=False)
         self.register_buffer("weights", torch.from_numpy(weights).to(dev).reshape(
             1, 1, topo.tiles_per_rank, topo.tile_size, topo.tile_size), persistent=False)
+
+    @staticmethod
+    def _lists(halo_exchange, window):
+        return halo_adjoint_lists(halo_exchange.topology, window)
 
     def forward(self, padded: torch.Tensor) -> torch.Tensor:
         topo = self.halo_exchange.topology
@@ -360,6 +382,42 @@ class NormalizedCopyHaloAdjoint(torch.nn.Module):
                 topo.halo_width, L, torch.cuda.current_stream().cuda_stream),
                 "strata_halo_adjoint_fields_f32")
         return out
+
+
+class NormalizedHaloAdjoint(NormalizedCopyHaloAdjoint):
+    """D_w^-1 A^T (w . y) for the halo module it is given - the reference's class of that name
+    (screamcast/distributed_halo.py:330-448), whose A is the k-nearest-neighbour regrid.
+
+    Given a `DistributedTileKNNHaloPadding` it transposes that module's weighted gather: every
+    rank contributes the (index, weight) lists of its padded cells (one all-gather at
+    construction, nothing per call), each interior cell keeps the entries that draw on it, and
+    the pull kernel of the copy-halo adjoint sums them with coefficient weight * window in a
+    fixed order. Given a copy-halo module it behaves as `NormalizedCopyHaloAdjoint`. Same
+    constructor, `forward`, `.window` and `.weights` as the reference.
+    """
+
+    @staticmethod
+    def _lists(halo_exchange, window):
+        topo = halo_exchange.topology
+        if not isinstance(halo_exchange, DistributedTileKNNHaloPadding):
+            return halo_adjoint_lists(topo, window)
+        idx_all, w_all = gather_knn_lists(topo, halo_exchange.knn_idx, halo_exchange.knn_weights,
+                                          halo_exchange.group)
+        return knn_adjoint_lists(topo, idx_all, w_all, window)
+
+
+def gather_knn_lists(topo: TileTopology, idx: torch.Tensor, weights: torch.Tensor, group=None):
+    """All ranks' k-nearest-neighbour (index, weight) lists in global tile order, as numpy arrays
+    [total_tiles*P*P, k] (one all-gather; a set-up step of the adjoint, nothing per call)."""
+    if topo.world_size > 1:
+        backend = dist.get_backend(group)
+        dev = idx.device if backend == "nccl" else torch.device("cpu")
+        parts_i = [torch.empty(idx.shape, dtype=idx.dtype, device=dev) for _ in range(topo.world_size)]
+        parts_w = [torch.empty(weights.shape, dtype=weights.dtype, device=dev) for _ in range(topo.world_size)]
+        dist.all_gather(parts_i, idx.to(dev).contiguous(), group=group)
+        dist.all_gather(parts_w, weights.to(dev).contiguous(), group=group)
+        idx, weights = torch.cat(parts_i), torch.cat(parts_w)
+    return idx.cpu().numpy(), weights.cpu().numpy()
 
 
 def kbd_window(padded_size: int, beta: float = 10 * np.pi) -> torch.Tensor:

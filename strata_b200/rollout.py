@@ -97,20 +97,38 @@ class TiledSphereStepper(torch.nn.Module):
     """
 
     def __init__(self, network: torch.nn.Module, topology: TileTopology, device=None, group=None,
-                 unpad: str = "crop", window: str | None = None):
+                 unpad: str = "crop", window: str | None = None, check_every: int = 0,
+                 out_channels: int | None = None, in_channels: int | None = None, depth: int | None = None):
         """unpad: "crop" (drop the halo, `topology.crop`) or "adjoint" (windowed overlap-add of
         the padded outputs, `--halo-adjoint` of the reference's launcher); window: None
-        (uniform) or "kbd" (`--halo-window`)."""
+        (uniform) or "kbd" (`--halo-window`).
+
+        A halo barrier whose wait runs out does not stop the stream: the padded tiles (and
+        everything computed from them) come back as NaN and the device status word is set.
+        check_every = n > 0 additionally synchronises and raises on every n-th step (callers
+        that must not synchronise poll `halo.check_status()` themselves, e.g. where they write
+        output anyway). in_channels / out_channels / depth, when given, size the peer-shared
+        buffer for the larger of the two payloads (input fields, padded outputs of the adjoint)
+        at construction; otherwise the first step that needs more room re-allocates it, which is
+        a collective over the group."""
         super().__init__()
+        self.check_every = int(check_every)
+        self._steps = 0
         if unpad not in ("crop", "adjoint"):
             raise ValueError(f"unpad must be 'crop' or 'adjoint', got {unpad!r}")
         self.network = network
         self.topology = topology
         plat, plon = padded_tile_latlon(topology)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        max_bytes = 0
+        if depth is not None and (in_channels is not None or out_channels is not None):
+            T, P, tpr = topology.tile_size, topology.padded_tile_size, topology.tiles_per_rank
+            max_bytes = 4 * depth * tpr * max((in_channels or 0) * T * T,
+                                              (out_channels or 0) * P * P if unpad == "adjoint" else 0)
         self.halo = DistributedTileCopyHaloPadding(
             topology=topology, lat_deg=torch.from_numpy(plat).float().to(dev),
-            lon_deg=torch.from_numpy(plon).float().to(dev), device=dev, group=group)
+            lon_deg=torch.from_numpy(plon).float().to(dev), device=dev, group=group,
+            **({"max_bytes_per_call": max_bytes} if max_bytes else {}))
         self.unpad = None
         if unpad == "adjoint":
             win = kbd_window(topology.padded_tile_size) if window == "kbd" else None
@@ -125,8 +143,13 @@ class TiledSphereStepper(torch.nn.Module):
         y = self.network(xin, {"lat": self.lat_rad, "lon": self.lon_rad})
         if self.unpad is None:
             y = self.topology.crop(y)                           # [tpr, C_out, D, T, T]
-            return y.permute(1, 2, 0, 3, 4).contiguous()
-        return self.unpad(y.permute(1, 2, 0, 3, 4).float().contiguous())
+            out = y.permute(1, 2, 0, 3, 4).contiguous()
+        else:
+            out = self.unpad(y.permute(1, 2, 0, 3, 4).float().contiguous())
+        self._steps += 1
+        if self.check_every > 0 and self._steps % self.check_every == 0:
+            self.halo.check_status()
+        return out
 
     def close(self):
         self.halo.close()

@@ -340,10 +340,17 @@ def halo_adjoint_lists(topo: TileTopology, window: np.ndarray | None = None):
     dst = np.concatenate([pid[single], pid[~single], pid[~single]])
     coef = np.concatenate([np.ones(single.sum(), np.float32),
                            np.full(2 * (~single).sum(), 0.5, np.float32)])
+    return _pull_lists(topo, src, dst, coef, window)
+
+
+def _pull_lists(topo: TileTopology, src: np.ndarray, dst: np.ndarray, coef: np.ndarray, window):
+    """Entries (interior cell src <- padded cell dst, coefficient) of a gather operator, grouped
+    by this rank's interior cells: (offsets, cell, coef, weights) as `halo_adjoint_lists` returns."""
+    T, P = topo.tile_size, topo.padded_tile_size
     n_local = topo.tiles_per_rank * T * T
     lo = topo.rank * n_local
     keep = (src >= lo) & (src < lo + n_local)
-    src, dst, coef = src[keep] - lo, dst[keep], coef[keep]
+    src, dst, coef = src[keep] - lo, dst[keep], coef[keep].astype(np.float32)
     order = np.lexsort((dst, src))
     src, dst, coef = src[order], dst[order], coef[order]
     offsets = np.zeros(n_local + 1, dtype=np.int64)
@@ -354,7 +361,7 @@ def halo_adjoint_lists(topo: TileTopology, window: np.ndarray | None = None):
     w = np.ones((P, P), np.float32) if window is None else np.asarray(window, np.float32)
     if w.shape != (P, P):
         raise ValueError(f"window must be [{P}, {P}]")
-    wv = coef * w.reshape(-1)[dst % (P * P)]
+    wv = (coef * w.reshape(-1)[dst % (P * P)]).astype(np.float32)
     weights = np.zeros(n_local, dtype=np.float32)
     # same summation order as the kernel: entry by entry, in float32
     k = np.arange(dst.size) - offsets[src]
@@ -362,6 +369,31 @@ def halo_adjoint_lists(topo: TileTopology, window: np.ndarray | None = None):
         m = k == j
         weights[src[m]] = (weights[src[m]] + wv[m]).astype(np.float32)
     return offsets.astype(np.int32), dst.astype(np.int32), coef, weights
+
+
+def knn_adjoint_lists(topo: TileTopology, idx_all: np.ndarray, weights_all: np.ndarray,
+                      window: np.ndarray | None = None):
+    """Transpose of the k-nearest-neighbour halo operator A (out[p] = sum_j w[p, j] x[idx[p, j]]),
+    as pull lists for this rank's interior cells - the operator whose normalised transpose
+    D_w^-1 A^T (w . y) the reference's NormalizedHaloAdjoint applies
+    (screamcast/distributed_halo.py:330-448, there as a vector-Jacobian product of the regrid
+    followed by a reduce_scatter).
+
+    idx_all / weights_all: [total_tiles*P*P, k] for the padded cells of EVERY tile of the globe in
+    global tile order (the concatenation of all ranks' `knn_halo_weights` results). Returns the
+    same four arrays as `halo_adjoint_lists`; an interior cell that no padded cell draws on gets
+    weight 0 (and the kernel's division then yields NaN for it, as the reference's does).
+    """
+    P = topo.padded_tile_size
+    n_padded = topo.total_tiles * P * P
+    idx_all = np.asarray(idx_all)
+    weights_all = np.asarray(weights_all, np.float32)
+    if idx_all.shape != weights_all.shape or idx_all.ndim != 2 or idx_all.shape[0] != n_padded:
+        raise ValueError(f"idx_all / weights_all must be [{n_padded}, k]")
+    k = idx_all.shape[1]
+    src = idx_all.reshape(-1).astype(np.int64)
+    dst = np.repeat(np.arange(n_padded, dtype=np.int64), k)
+    return _pull_lists(topo, src, dst, weights_all.reshape(-1), window)
 
 
 def knn_halo_weights(topo: TileTopology, lon_deg: np.ndarray, lat_deg: np.ndarray,

@@ -56,3 +56,47 @@ def test_two_rank_gloo_halo_maps():
         assert ok1, f"rank {rank}: gather_tiles_to_faces mismatch"
         assert ok2, f"rank {rank}: halo maps differ from the oracle"
         assert set(owners) == {0, 1}                              # halos do cross ranks
+
+
+def _knn_worker(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    from strata_b200.halo import gather_knn_lists
+    from strata_b200.rollout import padded_face_latlon
+    from strata_b200.topology import TileTopology, knn_adjoint_lists, knn_halo_weights
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        N, T, H, PW = 16, 4, 2, 4
+        lat, lon = padded_face_latlon(N, PW)
+        topo = TileTopology(world, rank, N, T, H)
+        idx, w = knn_halo_weights(topo, lon, lat, PW)            # this rank's padded cells only
+        idx_all, w_all = gather_knn_lists(topo, torch.from_numpy(idx), torch.from_numpy(w))
+        ref_idx, ref_w = knn_halo_weights(TileTopology(1, 0, N, T, H), lon, lat, PW)
+        ok1 = np.array_equal(idx_all, ref_idx) and np.array_equal(w_all, ref_w)
+        got = knn_adjoint_lists(topo, idx_all, w_all)
+        want = knn_adjoint_lists(topo, ref_idx, ref_w)
+        ok2 = all(np.array_equal(a, b) for a, b in zip(got, want))
+        # every padded cell that draws on a local interior cell is listed, wherever it lives
+        owners = set((got[1] // (topo.tiles_per_rank * (T + 2 * H) ** 2)).tolist())
+        q.put((rank, ok1, ok2, sorted(owners)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_knn_adjoint_lists():
+    # set-up of the KNN halo's adjoint (NormalizedHaloAdjoint): the ranks' weight lists are
+    # all-gathered, each rank keeps the entries that draw on its own interior cells
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() % 90)
+    procs = [ctx.Process(target=_knn_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok1, ok2, owners in res:
+        assert ok1, f"rank {rank}: gathered lists differ from the single-rank lists"
+        assert ok2, f"rank {rank}: adjoint lists differ"
+        assert set(owners) == {0, 1}

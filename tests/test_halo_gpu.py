@@ -147,6 +147,76 @@ def test_knn_halo_bit_exact_against_host_evaluation():
     with pytest.raises(TypeError):
         mod(x.cuda().double())
 
+def test_knn_halo_adjoint_matches_oracle():
+    # the reference's un-pad operator proper: D_w^-1 A^T (w . y) with A the KNN regrid
+    # (NormalizedHaloAdjoint, screamcast/distributed_halo.py:330-448)
+    from strata_b200.halo import (DistributedTileKNNHaloPadding, NormalizedCopyHaloAdjoint,
+                                  NormalizedHaloAdjoint, kbd_window)
+    from strata_b200.rollout import padded_face_latlon
+    from strata_b200.topology import TileTopology
+    N, T, H, PW = 16, 4, 2, 4
+    lat, lon = padded_face_latlon(N, PW)
+    topo = TileTopology(1, 0, N, T, H)
+    P = topo.padded_tile_size
+    mod = DistributedTileKNNHaloPadding.from_padded_face_grid(
+        topology=topo, lon=torch.from_numpy(lon).float(), lat=torch.from_numpy(lat).float(),
+        pad_width_data=PW, device="cuda")
+    with pytest.raises(TypeError, match="NormalizedHaloAdjoint"):
+        NormalizedCopyHaloAdjoint(mod)                      # the copy transpose refuses a KNN module
+    for win in (None, kbd_window(P)):
+        unpad = NormalizedHaloAdjoint(mod, window=win)
+        g = torch.Generator().manual_seed(31)
+        y = torch.randn(2, 3, topo.tiles_per_rank, P, P, generator=g)
+        got = unpad(y.cuda())
+        mod.check_status()
+        want = ho.knn_halo_adjoint(y.numpy(), ho.TileTopology(1, 0, N, T, H),
+                                   mod.knn_idx.cpu().numpy(), mod.knn_weights.cpu().numpy(),
+                                   None if win is None else win.numpy())
+        assert np.allclose(got.cpu().numpy(), want, rtol=2e-5, atol=2e-6)
+        # constant fields survive pad -> un-pad to the reference's tolerance
+        # (tests/distributed/test_distributed_halo.py:61-107)
+        c = torch.full((1, topo.tiles_per_rank, T, T), 1.75, device="cuda")
+        assert torch.allclose(unpad(mod(c)), c, rtol=1e-3, atol=0)
+    # on a copy-halo module the class is the copy transpose
+    from strata_b200.halo import DistributedTileCopyHaloPadding
+    cp = DistributedTileCopyHaloPadding(topology=topo)
+    y = torch.randn(1, topo.tiles_per_rank, P, P, generator=torch.Generator().manual_seed(3)).cuda()
+    assert torch.equal(NormalizedHaloAdjoint(cp)(y), NormalizedCopyHaloAdjoint(cp)(y))
+
+
+def test_failed_barrier_poisons_the_padded_tiles():
+    # failure made on the host side of the protocol (a partner flag nobody sets, a 20 ms limit):
+    # the gathers that follow on the stream must not hand back plausible numbers
+    import ctypes
+    from strata_b200 import _lib
+    from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint
+    from strata_b200.topology import TileTopology
+    lib = _lib.load()
+    topo = TileTopology(1, 0, 8, 4, 2)
+    mod = DistributedTileCopyHaloPadding(topology=topo)
+    unpad = NormalizedCopyHaloAdjoint(mod)
+    x = torch.ones(2, topo.tiles_per_rank, 4, 4, device="cuda")
+    assert torch.isfinite(mod(x)).all()
+    flags = torch.zeros(2, 64, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.strata_halo_barrier(ptrs, 0, 2, 1, 20, stream), "strata_halo_barrier")
+    padded = mod(x)                                 # issued behind the failed barrier
+    assert torch.isnan(padded).all()
+    assert torch.isnan(unpad(torch.ones(2, topo.tiles_per_rank, 8, 8, device="cuda"))).all()
+    tok = torch.ones(topo.tiles_per_rank, 2, 16, 8, dtype=torch.bfloat16, device="cuda")
+    assert torch.isnan(mod.pad_tokens(tok, 2).float()).all()
+    with pytest.raises(RuntimeError, match="status 105"):
+        mod.check_status()                          # reports and clears
+    assert torch.equal(mod(x)[..., 2:-2, 2:-2], x)  # the next exchange is clean again
+    assert _lib.device_status() == 0
+    # exchanges of one module stay on one stream
+    with torch.cuda.stream(torch.cuda.Stream()):
+        if topo.world_size > 1:
+            with pytest.raises(RuntimeError, match="same CUDA stream"):
+                mod(x)
+
+
 def _two_gpus():
     return torch.cuda.is_available() and torch.cuda.device_count() >= 2
 

@@ -6,7 +6,7 @@ import pytest
 
 from oracle import halo_oracle as ho
 from strata_b200.rollout import equiangular_cubed_sphere_latlon, padded_face_latlon
-from strata_b200.topology import TileTopology, knn_halo_weights
+from strata_b200.topology import TileTopology, knn_adjoint_lists, knn_halo_weights
 
 N, T, H, PW = 16, 4, 2, 4
 
@@ -81,3 +81,54 @@ def test_bad_grids_are_rejected():
         knn_halo_weights(TileTopology(1, 0, N, T, H), lon[:, 1:], lat[:, 1:], PW)
     with pytest.raises(ValueError):
         knn_halo_weights(TileTopology(1, 0, N, T, 6), lon, lat, PW)
+
+
+def _eval_lists(padded_all, lists, window, P):
+    """D_w^-1 A^T (w . y) from the pull lists, in float64 (what the adjoint kernel computes)."""
+    off, cell, coef, weights = lists
+    flat = padded_all.reshape(*padded_all.shape[:-3], -1).astype(np.float64)
+    win = window.reshape(-1).astype(np.float64)
+    out = np.zeros((*flat.shape[:-1], off.size - 1))
+    for c in range(off.size - 1):
+        e = slice(off[c], off[c + 1])
+        out[..., c] = (flat[..., cell[e]] * (coef[e].astype(np.float64) * win[cell[e] % (P * P)])).sum(-1)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        return out / weights.astype(np.float64)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_knn_adjoint_lists_are_the_transpose(world):
+    # the reference's un-pad operator is the normalised transpose of the KNN regrid
+    # (NormalizedHaloAdjoint, screamcast/distributed_halo.py:330-448)
+    lat, lon = padded_face_latlon(N, PW)
+    full = TileTopology(1, 0, N, T, H)
+    P = T + 2 * H
+    idx_all, w_all = knn_halo_weights(full, lon, lat, PW)
+    rng = np.random.default_rng(5)
+    y = rng.standard_normal((3, full.total_tiles, P, P)).astype(np.float32)
+    x = rng.standard_normal((3, full.total_tiles * T * T))
+    win = np.outer(np.hanning(P + 2)[1:-1], np.hanning(P + 2)[1:-1]).astype(np.float32) + 0.05
+    got = []
+    for rank in range(world):
+        topo = TileTopology(world, rank, N, T, H)
+        lists = knn_adjoint_lists(topo, idx_all, w_all, win)
+        out = _eval_lists(y, lists, win, P)
+        want = ho.knn_halo_adjoint(y, ho.TileTopology(world, rank, N, T, H), idx_all, w_all, win)
+        assert np.allclose(out, want.reshape(out.shape), rtol=1e-5, atol=1e-6, equal_nan=True)
+        # un-normalised: <A x, w y> == <x, A^T (w y)>
+        off, cell, coef, weights = lists
+        aty = out * weights.astype(np.float64)
+        got.append(aty)
+    aty = np.concatenate(got, axis=-1)
+    ax = np.stack([(w_all[:, j].astype(np.float64) * x[:, idx_all[:, j]]) for j in range(idx_all.shape[1])]).sum(0)
+    lhs = (ax * (y.reshape(3, -1) * np.tile(win.reshape(-1), full.total_tiles))).sum(-1)
+    rhs = (x * aty).sum(-1)
+    assert np.allclose(lhs, rhs, rtol=1e-5)
+    # constant fields survive pad -> un-pad (reference: tests/distributed/test_distributed_halo.py:61-107)
+    const = np.full((1, full.total_tiles, P, P), 3.25, np.float32)
+    for rank in range(world):
+        topo = TileTopology(world, rank, N, T, H)
+        back = _eval_lists(const, knn_adjoint_lists(topo, idx_all, w_all, win), win, P)
+        assert np.allclose(back, 3.25, atol=1e-3)
+    with pytest.raises(ValueError, match="idx_all"):
+        knn_adjoint_lists(full, idx_all[:-1], w_all[:-1])
