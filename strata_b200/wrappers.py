@@ -14,7 +14,7 @@ from typing import Mapping, Optional, Tuple
 import torch
 import torch.nn as nn
 
-from . import rope
+from . import rope, torch_ops
 from .checkpoint_compat import remap_legacy_pre_hook
 from .strata import Mlp, StrataTransformer3D
 
@@ -168,17 +168,39 @@ class _StrataModelBase(nn.Module):
         # translation also happens when this wrapper is a submodule of the module being loaded
         # (reference: strata_wrappers.py:193-199)
         self.register_load_state_dict_pre_hook(remap_legacy_pre_hook)
+        self._op_handle = torch_ops.register_module(self)
+
+    def __setstate__(self, state):
+        # a copy (copy.deepcopy, pickle) is a module of its own for the operator registry
+        super().__setstate__(state)
+        self._op_handle = torch_ops.register_module(self)
 
     @property
     def _index_is_latlon(self) -> bool:
         return self.geometry.index_is_latlon
 
-    def _preprocess(self, x, index):
-        B, _, dd, _, _ = x.shape
+    def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+        """network(x[B, C, D, H, W], index) -> [B, C_out, D, H, W] (reference:
+        strata_wrappers.py:408-415, 673-680). The index lookup is plain tensor code; everything
+        behind it is one registered operator, so the module can be compiled whole
+        (`torch.compile(network)`, also with fullgraph=True) and called under inference mode."""
         lat, lon = self.geometry.lat_lon_from_index(index)
+        return torch.ops.strata_b200.network_forward(x, lat, lon, self._op_handle)
+
+    def _latlon_for(self, x: torch.Tensor, lat: torch.Tensor, lon: torch.Tensor):
+        B = x.shape[0]
         if lat.shape[0] != B:
             lat = lat.expand(B, -1, -1)
             lon = lon.expand(B, -1, -1)
+        return lat, lon
+
+    def _preprocess(self, x, index):
+        lat, lon = self.geometry.lat_lon_from_index(index)
+        return self._preprocess_latlon(x, lat, lon)
+
+    def _preprocess_latlon(self, x, lat, lon):
+        B, _, dd, _, _ = x.shape
+        lat, lon = self._latlon_for(x, lat, lon)
         lat_lon_data = None
         if self._do_rotate_wind:
             lat0, lon0 = TileGeometry.tile_center(lat, lon)
@@ -300,22 +322,19 @@ class StrataBackboneModel(_StrataModelBase):
         self._rope_length_scale_base = base
         self.strata.rope_length_scale = base * self.strata.patch_size[1]
 
-    def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+    def _forward_eager(self, x: torch.Tensor, lat: torch.Tensor, lon: torch.Tensor) -> torch.Tensor:
+        """What `strata_b200::network_forward` runs for this module."""
         if self.strata.fused_path_available(x):
-            return self._forward_fused(x, index)
-        x, pos, lat_lon_data = self._preprocess(x, index)
-        x = self.strata(x, pos=pos)
-        return self._postprocess(x, lat_lon_data)
+            return self._forward_fused(x, lat, lon).to(x.dtype)
+        xin, pos, lat_lon_data = self._preprocess_latlon(x, lat, lon)
+        y = self.strata(xin, pos=pos)
+        return self._postprocess(y, lat_lon_data).to(x.dtype)
 
-    def _forward_fused(self, x: torch.Tensor, index) -> torch.Tensor:
+    def _forward_fused(self, x: torch.Tensor, lat: torch.Tensor, lon: torch.Tensor) -> torch.Tensor:
         """Same result as _preprocess -> strata -> _postprocess, with the wind rotation, the
         latitude channels and the patch gathering done by one kernel on the way in and the
         un-patchify and inverse rotation by one kernel on the way out."""
-        B = x.shape[0]
-        lat, lon = self.geometry.lat_lon_from_index(index)
-        if lat.shape[0] != B:
-            lat = lat.expand(B, -1, -1)
-            lon = lon.expand(B, -1, -1)
+        lat, lon = self._latlon_for(x, lat, lon)
         lat = lat.to(device=x.device, dtype=torch.float32).contiguous()
         lon = lon.to(device=x.device, dtype=torch.float32).contiguous()
         lat0 = lon0 = wind = None
@@ -465,15 +484,12 @@ class StrataModel(_StrataModelBase):
         if pixel_stereo:
             self.strata.rope_length_scale_pixel = base
 
-    def forward(self, x: torch.Tensor, index) -> torch.Tensor:
+    def _forward_eager(self, x: torch.Tensor, lat: torch.Tensor, lon: torch.Tensor) -> torch.Tensor:
+        """What `strata_b200::network_forward` runs for this module."""
         if not (x.is_cuda and x.dtype == torch.float32):
             raise RuntimeError("the two-stage model runs on CUDA fp32 fields only (its kernels "
                                "have no CPU fallback)")
-        B = x.shape[0]
-        lat, lon = self.geometry.lat_lon_from_index(index)
-        if lat.shape[0] != B:
-            lat = lat.expand(B, -1, -1)
-            lon = lon.expand(B, -1, -1)
+        lat, lon = self._latlon_for(x, lat, lon)
         lat = lat.to(device=x.device, dtype=torch.float32).contiguous()
         lon = lon.to(device=x.device, dtype=torch.float32).contiguous()
         lat0 = lon0 = wind = None
