@@ -12,11 +12,12 @@ neighbouring tiles, whose keys and values arrive through peer memory each block:
     attention of the interior queries over the padded K/V planes
     projection, residual, LN, MLP               interior tokens, compact
 
-With overlap=True the exchange runs on a side stream while the main stream already computes the
-attention of the queries whose windows stay inside the tile (they need no halo); the border
-strips follow once the halo has arrived. Everything that is token-wise (LN, the GEMMs) runs in
-chunks of tiles, so that only x, y, the attention output and the padded qkv buffer are ever held
-for all tiles at once.
+The exchange runs in line on the compute stream: it moves about 3 % of a block's time, and
+hiding it behind the attention of the queries whose windows stay inside the tile was built and
+measured slower (the four border strips that have to follow fill their 128-query tiles badly
+and cost four more launches per block), so that variant was taken out again. Everything that
+is token-wise (LN, the GEMMs) runs in chunks of tiles, so that only x, y, the attention output
+and the padded qkv buffer are ever held for all tiles at once.
 
 Stereographic RoPE coordinates are relative to each tile's centre, so a key rotated in its
 owner's frame is wrong for the receiver; the owner stores K in its own frame (it needs that
@@ -60,7 +61,7 @@ class TiledBlockRunner:
     def __init__(self, topology: TileTopology, *, depth: int, dim: int, num_heads: int, kernel,
                  lat_deg: np.ndarray, lon_deg: np.ndarray, rope_base: float = 100.0,
                  rope_length_scale: float | None = None, device=None, group=None,
-                 timeout_ms: int = 2000, overlap: bool = False, chunk_tiles: int | None = None):
+                 timeout_ms: int = 2000, chunk_tiles: int | None = None):
         """lat_deg / lon_deg: [total_tiles, T, T] cell centres of ALL tiles in global tile order."""
         T, h = topology.tile_size, topology.halo_width
         kd, kh, kw = (int(kernel),) * 3 if isinstance(kernel, int) else tuple(int(v) for v in kernel)
@@ -123,8 +124,6 @@ class TiledBlockRunner:
         else:
             self._shared = None
             self._local = torch.zeros(total, dtype=torch.uint8, device=dev)
-        self.overlap = bool(overlap)
-        self._side = torch.cuda.Stream(device=dev) if self.overlap else None
         if chunk_tiles is None:   # hidden activations of a chunk stay below ~4 GB
             chunk_tiles = max(1, int(4e9 // (depth * T * T * 4 * dim * 2)))
         self.chunk_tiles = min(int(chunk_tiles), tpr)
@@ -176,28 +175,8 @@ class TiledBlockRunner:
                                 qk_norm=qk_norm)
         q6 = qkv.view(tpr, D, P, P, 3, self.heads, C // self.heads)
         q, k, v = q6[..., 0, :, :], q6[..., 1, :, :], q6[..., 2, :, :]
-        r = max(self.kernel[1], self.kernel[2]) // 2
-        if not self.overlap or T - 2 * r < 8:
-            self._exchange(qkv, ptrs)
-            o = ops.na3d_region(q, k, v, self.kernel, (h, T, h, T))
-            return o.view(tpr * D * T * T, C)
-        # halo exchange on the side stream, inner queries (windows inside the tile) meanwhile
-        main = torch.cuda.current_stream()
-        ready = torch.cuda.Event()
-        ready.record(main)
-        with torch.cuda.stream(self._side):
-            self._side.wait_event(ready)
-            self._exchange(qkv, ptrs)
-            arrived = torch.cuda.Event()
-            arrived.record(self._side)
-        o = torch.empty((tpr, D, T, T, self.heads, C // self.heads), dtype=torch.bfloat16,
-                        device=qkv.device)
-        win = (h, T, h, T)
-        ops.na3d_region(q, k, v, self.kernel, (h + r, T - 2 * r, h + r, T - 2 * r), out=o, out_window=win)
-        main.wait_event(arrived)
-        for reg in ((h, r, h, T), (h + T - r, r, h, T),
-                    (h + r, T - 2 * r, h, r), (h + r, T - 2 * r, h + T - r, r)):
-            ops.na3d_region(q, k, v, self.kernel, reg, out=o, out_window=win)
+        self._exchange(qkv, ptrs)
+        o = ops.na3d_region(q, k, v, self.kernel, (h, T, h, T))
         return o.view(tpr * D * T * T, C)
 
     def block_forward(self, x: torch.Tensor, weights: dict, qk_norm: bool = False) -> torch.Tensor:

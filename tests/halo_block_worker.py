@@ -27,7 +27,7 @@ def main():
     lat, lon = _grid(face, tile)
     scale = np.radians(90.0 / face)
     run = TiledBlockRunner(topo, depth=D, dim=C, num_heads=heads, kernel=kernel, lat_deg=lat,
-                           lon_deg=lon, rope_length_scale=scale, overlap=bool(int(os.environ.get("HALO_OVERLAP", "0"))))
+                           lon_deg=lon, rope_length_scale=scale)
     params = [bo.init_block_params(C, seed=30 + i, scheme="xavier") for i in range(n_blocks)]
     g = torch.Generator().manual_seed(3)
     x = torch.randn(topo.total_tiles, D * tile * tile, C, generator=g).bfloat16()

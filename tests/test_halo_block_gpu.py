@@ -110,9 +110,9 @@ def _own_frame_coords(okw):
 
 @pytest.mark.parametrize("gated,qk_norm,kernel,halo,runner_kw", [
     (False, False, (1, 5, 5), 2, {}), (True, True, (2, 7, 7), 4, {}),
-    # exchange on a side stream while the inner queries are computed; token-wise stages in chunks
-    (True, False, (2, 7, 7), 4, {"overlap": True, "chunk_tiles": 5}),
-    (False, True, (1, 5, 5), 3, {"overlap": True}),
+    # token-wise stages in chunks of tiles
+    (True, False, (2, 7, 7), 4, {"chunk_tiles": 5}),
+    (False, True, (1, 5, 5), 3, {}),
 ])
 def test_tiled_block_matches_oracle(gated, qk_norm, kernel, halo, runner_kw):
     run, topo, p, x, okw = _setup(halo, kernel, gated=gated, **runner_kw)
@@ -124,14 +124,13 @@ def test_tiled_block_matches_oracle(gated, qk_norm, kernel, halo, runner_kw):
 
 @pytest.mark.skipif(not (torch.cuda.is_available() and torch.cuda.device_count() >= 2),
                     reason="needs 2 GPUs on one node")
-@pytest.mark.parametrize("overlap", ["0", "1"])
-def test_two_rank_tiled_block_stack(overlap):
+def test_two_rank_tiled_block_stack():
     import os, subprocess, sys
     from pathlib import Path
     worker = Path(__file__).resolve().parent / "halo_block_worker.py"
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                         "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                         "29533", str(worker)], capture_output=True, text=True, timeout=600,
-                       env={**os.environ, "NCCL_NVLS_ENABLE": "0", "HALO_OVERLAP": overlap})
+                       env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "HALO BLOCK WORKER OK" in r.stdout
