@@ -838,8 +838,15 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
-    else:
-        run_gpu_arm(args)
+        return
+    # Libraries may print to stdout (NCCL prints a version banner there): while the benchmark
+    # runs, file descriptor 1 points at stderr, and the one JSON line goes to the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
+    run_gpu_arm(args)
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":

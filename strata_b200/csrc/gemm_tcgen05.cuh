@@ -128,10 +128,21 @@ template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_16(float (&v)[16], bool rotate, float b_lane,
                                                  int src_lane0, const uint32_t (&aux)[8],
                                                  float qk_scale, const uint32_t (&cs)[8],
-                                                 const GemmParams& p) {
+                                                 const GemmParams& p, const float* bias16) {
   if (p.bias != nullptr) {
+    if (bias16 != nullptr) {
+      // the 16 biases of this column group, the same for every row: four 16-byte loads at an
+      // address that is uniform over the warp (one L1 line, broadcast) instead of one shuffle
+      // per output element
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, src_lane0 + j);
+      for (int q = 0; q < 4; ++q) {
+        const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias16) + q);
+        v[4 * q] += b4.x; v[4 * q + 1] += b4.y; v[4 * q + 2] += b4.z; v[4 * q + 3] += b4.w;
+      }
+    } else {   // ragged right edge of the matrix: lane j of the group holds column j's bias
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] += __shfl_sync(0xffffffffu, b_lane, src_lane0 + j);
+    }
   }
   if constexpr (EPI == EPI_GELU) {
     // tanh GELU on pairs: the polynomial part runs on packed fp32x2 instructions
@@ -412,10 +423,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 uint32_t r[16];
                 tmem_ld_32x16(taddr + 32 * cc + 16 * g, r);
                 tmem_ld_wait();
+                const int nb0 = n_warp0 + 32 * cc + 16 * g;
+                if (p.bias != nullptr && nb0 + 16 <= p.N) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const float x = __uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bl, 16 * g + j);
-                  acc += x * x;
+                  for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + nb0) + q4);
+                    const float x0 = __uint_as_float(r[4 * q4]) + b4.x;
+                    const float x1 = __uint_as_float(r[4 * q4 + 1]) + b4.y;
+                    const float x2 = __uint_as_float(r[4 * q4 + 2]) + b4.z;
+                    const float x3 = __uint_as_float(r[4 * q4 + 3]) + b4.w;
+                    acc += x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) {
+                    const float x = __uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bl, 16 * g + j);
+                    acc += x * x;
+                  }
                 }
               }
               ss[cc] = acc;
@@ -487,7 +511,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                              : "memory");
               }
             }
-            gemm_epilogue_16<EPI>(v, rotate, b_lane, 16 * g, aux, qk_scale[c], cs, p);
+            // (the bias group is read directly when all its 16 columns exist; p.bias is
+            // 16-byte aligned and n0 a multiple of 32)
+            const float* bias16 = (p.bias != nullptr && n0 + 16 * g + 16 <= p.N)
+                                      ? p.bias + n0 + 16 * g : nullptr;
+            gemm_epilogue_16<EPI>(v, rotate, b_lane, 16 * g, aux, qk_scale[c], cs, p, bias16);
             if constexpr (LATE_WAIT) {
               if (g == 0) {
                 // the previous sub-chunk's TMA store must have finished reading the staging
