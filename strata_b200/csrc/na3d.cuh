@@ -83,6 +83,10 @@ struct Na3dParams {
   unsigned short blk[NA_MAX_BLOCKS][2];
   __nv_bfloat16* out;    // [B, D, q_H, q_W, ldo] with head h at channel offset h*64
   long long ldo;
+  // the operands as plain pointers (token-major, row strides in elements): only the
+  // recomputation of a row whose scores left the range of the fast path reads them
+  const __nv_bfloat16 *q, *k, *v;
+  long long ldq, ldk, ldv;
   float scale_log2e;
 };
 
@@ -138,6 +142,111 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+// One query row computed the plain way - scores, online softmax and P V in fp32 on the CUDA
+// cores, operands read from global memory. Thousands of times slower than the tensor-core
+// path and only used for a row whose scores rose more than 2^119 above its reference within
+// one unit (or are infinite or NaN), which the fast path cannot represent.
+struct NaSlowArgs {   // passed by value: a reference to the kernel's parameters would force a local copy
+  const __nv_bfloat16 *q, *k, *v;
+  long long ldq, ldk, ldv;
+  int D, H, W, kd, kh;
+  float scale_log2e;
+};
+template <int KW>
+__device__ __noinline__ void na_slow_row(const NaSlowArgs p, int b, int head, int id, int ih,
+                                         int iw, __nv_bfloat16* op) {
+  auto token = [&](int d, int h, int w) {
+    return ((static_cast<long long>(b) * p.D + d) * p.H + h) * p.W + w;
+  };
+  float qf[64], o[64];
+  {
+    const uint4* qp = reinterpret_cast<const uint4*>(p.q + token(id, ih, iw) * p.ldq + head * 64);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 x = qp[j];
+      const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        qf[8 * j + 2 * t] = bf16_lo(w4[t]);
+        qf[8 * j + 2 * t + 1] = bf16_hi(w4[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 64; ++c) o[c] = 0.f;
+  const int d0 = na_window_start(id, p.D, p.kd);
+  const int h0 = na_window_start(ih, p.H, p.kh);
+  const int w0 = na_window_start(iw, p.W, KW);
+  float m = -3.0e38f, l = 0.f;
+  const int nkeys = p.kd * p.kh * KW;
+#pragma unroll 1
+  for (int n = 0; n < nkeys; ++n) {
+    const int ww = n % KW, hh = (n / KW) % p.kh, dd = n / (KW * p.kh);
+    const long long tok = token(d0 + dd, h0 + hh, w0 + ww);
+    const uint4* kp = reinterpret_cast<const uint4*>(p.k + tok * p.ldk + head * 64);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 x = kp[j];
+      const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        dot = fmaf(qf[8 * j + 2 * t], bf16_lo(w4[t]), dot);
+        dot = fmaf(qf[8 * j + 2 * t + 1], bf16_hi(w4[t]), dot);
+      }
+    }
+    const float t = dot * p.scale_log2e;
+    if (t > m) {
+      const float alpha = exp2f(m - t);
+      l *= alpha;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) o[c] *= alpha;
+      m = t;
+    }
+    const float pw = exp2f(t - m);
+    l += pw;
+    const float pb = __bfloat162float(__float2bfloat16_rn(pw));   // P enters P V as bf16
+    const uint4* vp = reinterpret_cast<const uint4*>(p.v + tok * p.ldv + head * 64);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 x = vp[j];
+      const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int t2 = 0; t2 < 4; ++t2) {
+        o[8 * j + 2 * t2] = fmaf(pb, bf16_lo(w4[t2]), o[8 * j + 2 * t2]);
+        o[8 * j + 2 * t2 + 1] = fmaf(pb, bf16_hi(w4[t2]), o[8 * j + 2 * t2 + 1]);
+      }
+    }
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int j = 0; j < 64; j += 8) {
+    uint4 v4;
+    v4.x = pack_bf16(o[j] * inv, o[j + 1] * inv);
+    v4.y = pack_bf16(o[j + 2] * inv, o[j + 3] * inv);
+    v4.z = pack_bf16(o[j + 4] * inv, o[j + 5] * inv);
+    v4.w = pack_bf16(o[j + 6] * inv, o[j + 7] * inv);
+    *reinterpret_cast<uint4*>(op + j) = v4;
+  }
+}
+
+// Multiplies this thread's row of the O accumulator (64 fp32 columns in tensor memory) by 2^-e
+// and returns that factor. Called by a whole warp; out of line because it is rare.
+__device__ __noinline__ float na_scale_o_row(uint32_t o_taddr, int e) {
+  const float alpha = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+#pragma unroll 1
+  for (int hh = 0; hh < 4; ++hh) {
+    uint32_t ob[16];
+    tmem_ld_x16(o_taddr + 16 * hh, ob);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+    tmem_st_x16(o_taddr + 16 * hh, ob);
+  }
+  tmem_st_wait();
+  return alpha;
+}
+
 struct NaItem {
   int b, head, d0, h0, w0, bd0, bh0, bw0;
 };
@@ -176,6 +285,26 @@ struct Na3dCfg {
   static_assert(EWP <= 16, "key rows of at most 16 columns");
   static_assert(TOTAL <= 115712, "two CTAs per SM: at most half of the SM's shared memory");
 };
+
+// The rows of one thread (tile position zd, zh, zw) in the CTA's items that the fast path gave
+// up on: the first 64 items are remembered one by one (bad_items), later ones as a group.
+template <int KW, int QW>
+__device__ __noinline__ void na_slow_rows(const Na3dParams& p, uint64_t bad_items, bool bad_rest,
+                                          int n_my, bool has_query, int zd, int zh, int zw) {
+  const NaSlowArgs sa = {p.q, p.k, p.v, p.ldq, p.ldk, p.ldv, p.D, p.H, p.W, p.kd, p.kh, p.scale_log2e};
+#pragma unroll 1
+  for (int n = 0; n < n_my; ++n) {
+    if (!(n < 64 ? ((bad_items >> n) & 1ull) != 0ull : bad_rest)) continue;
+    const NaItem it = na_decode_item<KW, QW>(static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x), p);
+    const bool q_ok = has_query && (it.d0 + zd < p.D) && (it.h0 + zh < p.q_h0 + p.q_H) &&
+                      (it.w0 + zw < p.q_w0 + p.q_W);
+    if (!q_ok) continue;
+    const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.o_H +
+                           (it.h0 + zh - p.o_h0)) * p.o_W + (it.w0 + zw - p.o_w0);
+    na_slow_row<KW>(sa, it.b, it.head, it.d0 + zd, it.h0 + zh, it.w0 + zw,
+                    p.out + tok * p.ldo + it.head * 64);
+  }
+}
 
 template <int KW, int QW>
 __global__ void __launch_bounds__(Na3dCfg<KW, QW>::THREADS, 2)
@@ -353,10 +482,13 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
     const uint32_t p_taddr = lane_taddr + Cfg::P_COL;
     const uint32_t o_taddr = lane_taddr + Cfg::O_COL;
     const float c = p.scale_log2e;
-    constexpr float SUM_LIMIT = 65536.0f;
+    constexpr float SUM_LIMIT = 65536.0f;          // 2^16
+    constexpr float SUM_REPAIRABLE = 1.0e30f;      // ~2^100: P, O and 2^-e stay well inside fp32
 
     bool ok = true;
     uint32_t gb = 0;
+    uint64_t bad_items = 0ull;    // see the end of this branch
+    bool bad_rest = false;
     int st_prev = STAGES - 1;     // ring stage and phase of block gb-1 (for pv_done)
     uint32_t ph_prev = 1;
     for (int n = 0; n < n_my && ok; ++n) {
@@ -402,6 +534,27 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (!has_query) rowmask = 0u;
         }
         const uint32_t warp_rows = __reduce_or_sync(0xffffffffu, rowmask);
+        bool p_free = false;      // the previous block's P V has completed: P may be overwritten
+        if (i != 0 && __any_sync(0xffffffffu, l_run >= SUM_LIMIT)) {
+          // rare: some row's scores have risen far above its reference. Move that reference up
+          // by e whole binades: what has been accumulated under the old one - O (complete once
+          // the previous P V is) and the running sum - is multiplied by 2^-e, which is exact.
+          // A sum beyond SUM_REPAIRABLE (or infinite, or NaN) is left alone: the row is
+          // recomputed from global memory when the kernel ends.
+          if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          p_free = true;
+          const int e = (l_run >= SUM_LIMIT && l_run < SUM_REPAIRABLE)
+                            ? static_cast<int>((__float_as_uint(l_run) >> 23) & 255u) - 127 : 0;
+          l_run *= na_scale_o_row(o_taddr, e);
+          if (e != 0) {
+            mc += static_cast<float>(e);
+            set_nb(mc);
+          }
+        }
         if (!mbar_wait(s_full, gb & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
           ok = false;
           break;
@@ -414,8 +567,14 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
         // block's scores while the exponentials of this one are still being evaluated. P is
         // stored once the previous block's P V has completed (pv_done), which has normally
         // happened long before.
-        bool s_released = false, p_free = false;
-        bool stored0 = false;     // unit 0 wrote non-zero P that a later move of the reference must rescale
+        //
+        // The exponentials are taken against the row's current reference without looking for
+        // the maximum first. A row that has no reference yet takes the maximum of its first
+        // visible scores (one extra pass, once per row and item). Afterwards the running sum
+        // is the detector: once it has reached 2^16 a score lies far above the reference, and
+        // at the start of the next block (see above) the reference moves up. Rows of the unit
+        // that this query does not see are masked (zero P, left out of the sum).
+        bool s_released = false;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const uint32_t need4 = (warp_rows >> (4 * u)) & 15u;   // rows some query of the warp sees
@@ -433,112 +592,53 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
               if (lane == 0) mbar_arrive(s_free);
               s_released = true;
             }
-            bool take_max = __any_sync(0xffffffffu, has_query && l_run == 0.f);
-            bool settled = false;
-            float rs_unit;
-#pragma unroll 1
-            while (true) {
-              if (take_max) {
-                // masked maximum of this thread's visible scores (scaled form) ...
-                float bm = -1e30f;
-#pragma unroll
-                for (int rr = 0; rr < 4; ++rr) {
-                  if (!((need4 >> rr) & 1u)) continue;
-                  float rm0 = -1e30f, rm1 = -1e30f;
-#pragma unroll
-                  for (int k2 = 0; k2 < EW / 2; ++k2) {
-                    float t0, t1;
-                    unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-                    if (k2 & 1) rm1 = fmax3(rm1, t0, t1); else rm0 = fmax3(rm0, t0, t1);
-                  }
-                  bm = fmaxf(bm, ((mine4 >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
-                }
-                // ... moves the reference up by bm where that is called for: always while nothing
-                // has been accumulated yet (free), otherwise only beyond a margin of 2^8 - then the
-                // TMEM accumulator, the running sum and the P already stored for this block are
-                // rescaled (the previous block's P V must have completed first).
-                const bool fresh = l_run == 0.f;
-                const bool grow = fresh ? (bm > -1e29f) : (bm > 8.0f);
-                const bool rescale = grow && !fresh;
-                if (__any_sync(0xffffffffu, rescale)) {
-                  if (!p_free) {
-                    if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
-                    tc_fence_after();
-                    p_free = true;
-                  }
-                  const float alpha = rescale ? fast_exp2(-bm) : 1.0f;
-                  l_run *= alpha;
-                  if (i != 0) {   // O of this item exists only after its first block
-#pragma unroll 1
-                    for (int hh = 0; hh < 4; ++hh) {
-                      uint32_t ob[16];
-                      tmem_ld_x16(o_taddr + 16 * hh, ob);
-                      tmem_ld_wait();
-#pragma unroll
-                      for (int j = 0; j < 16; ++j)
-                        ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
-                      tmem_st_x16(o_taddr + 16 * hh, ob);
-                    }
-                  }
-                  if (u == 1 && stored0) {
-                    tmem_st_wait();   // unit 0's P stores have landed before they are read back
-#pragma unroll 1
-                    for (int hh = 0; hh < UNIT_PCOLS / 8; ++hh) {
-                      uint32_t pb[8];
-                      tmem_ld_x8(p_taddr + 8 * hh, pb);
-                      tmem_ld_wait();
-#pragma unroll
-                      for (int j = 0; j < 8; ++j)
-                        pb[j] = pack_bf16(bf16_lo(pb[j]) * alpha, bf16_hi(pb[j]) * alpha);
-                      tmem_st_x8(p_taddr + 8 * hh, pb);
-                    }
-                  }
-                  tmem_st_wait();
-                }
-                if (grow) {
-                  mc += bm;
-                  set_nb(mc);
-                }
-                settled = true;
-              }
-              // exponentials, row sum and bf16 P (two keys per 32-bit column)
-              uint64_t rs2 = 0ull;
+            const bool fresh = has_query && l_run == 0.f;
+            if (__any_sync(0xffffffffu, fresh)) {
+              // masked maximum of this thread's visible scores (scaled form)
+              float bm = -1e30f;
 #pragma unroll
               for (int rr = 0; rr < 4; ++rr) {
-                if (!((need4 >> rr) & 1u)) {
+                float rm0 = -1e30f, rm1 = -1e30f;
 #pragma unroll
-                  for (int j = 0; j < PC; ++j) pk[rr * PC + j] = 0u;
-                  continue;
+                for (int k2 = 0; k2 < EW / 2; ++k2) {
+                  float t0, t1;
+                  unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                  if (k2 & 1) rm1 = fmaxf(rm1, fmaxf(t0, t1)); else rm0 = fmaxf(rm0, fmaxf(t0, t1));
                 }
-                const bool mine = (mine4 >> rr) & 1u;
-                const uint32_t keep = mine ? 0xffffffffu : 0u;
-                uint64_t rsa = 0ull, rsb = 0ull;
-#pragma unroll
-                for (int k2 = 0; k2 < PC; ++k2) {
-                  uint32_t packed = 0u;
-                  if (k2 < EW / 2) {
-                    float t0, t1;
-                    unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-                    const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-                    if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
-                    packed = pack_bf16(p0, p1) & keep;
-                  }
-                  pk[rr * PC + k2] = packed;
-                }
-                if (mine) rs2 = fadd2(rs2, fadd2(rsa, rsb));
+                bm = fmaxf(bm, ((mine4 >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
               }
-              {
-                float r0, r1;
-                unpack2(rs2, r0, r1);
-                rs_unit = r0 + r1;
+              // nothing has been accumulated for a fresh row (its earlier P were zeros)
+              if (fresh && bm > -1e29f) {
+                mc += bm;
+                set_nb(mc);
               }
-              // a sum this large (or infinite, or NaN) means a score far above the reference:
-              // take the maximum after all and redo the unit (its scores are still in registers)
-              if (settled || !__any_sync(0xffffffffu, !(rs_unit < SUM_LIMIT))) break;
-              take_max = true;
             }
-            l_run += rs_unit;
-            if (u == 0) stored0 = true;
+            // exponentials, row sum and bf16 P (two keys per 32-bit column)
+            uint64_t rs2 = 0ull;
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+              const bool mine = (mine4 >> rr) & 1u;
+              const uint32_t keep = mine ? 0xffffffffu : 0u;
+              uint64_t rsa = 0ull, rsb = 0ull;
+#pragma unroll
+              for (int k2 = 0; k2 < PC; ++k2) {
+                uint32_t packed = 0u;
+                if (k2 < EW / 2) {
+                  float t0, t1;
+                  unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
+                  const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                  if (k2 & 1) rsb = fadd2(rsb, pack2(p0, p1)); else rsa = fadd2(rsa, pack2(p0, p1));
+                  packed = pack_bf16(p0, p1) & keep;
+                }
+                pk[rr * PC + k2] = packed;
+              }
+              if (mine) rs2 = fadd2(rs2, fadd2(rsa, rsb));
+            }
+            {
+              float r0, r1;
+              unpack2(rs2, r0, r1);
+              l_run += r0 + r1;
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < UNIT_PCOLS; ++j) pk[j] = 0u;
@@ -579,6 +679,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       tc_fence_after();
       {
         const float inv = 1.0f / l_run;
+        if (!(l_run < SUM_REPAIRABLE)) {   // beyond repair (or NaN): this row is computed again below
+          if (n < 64) bad_items |= 1ull << n; else bad_rest = true;
+        }
         const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.o_H +
                                (it.h0 + zh - p.o_h0)) * p.o_W + (it.w0 + zw - p.o_w0);
         __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64;
@@ -601,6 +704,11 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         tc_fence_before();
       }
+    }
+    // rows whose scores left the range of the fast path: computed again the plain way
+    if (ok && (bad_items != 0ull || bad_rest)) {
+      const Na3dParams pc = p;   // a callee cannot address the kernel's parameter bank
+      na_slow_rows<KW, QW>(pc, bad_items, bad_rest, n_my, has_query, zd, zh, zw);
     }
   }
 
@@ -701,6 +809,8 @@ inline int launch_na3d_t(const __nv_bfloat16* q, long long ldq, const __nv_bfloa
   if (make(&tmQ, q, ldq, QW, p.QH, p.QD) != 0) return -20;
   if (make(&tmK, k, ldk, Cfg::EWP, 4, 1) != 0) return -20;
   if (make(&tmV, v, ldv, Cfg::EWP, 4, 1) != 0) return -20;
+  p.q = q; p.k = k; p.v = v;
+  p.ldq = ldq; p.ldk = ldk; p.ldv = ldv;
   auto kern = na3d_fwd_kernel<KW, QW>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::TOTAL);

@@ -165,6 +165,27 @@ def test_na3d_large_score_range(ops, kernel, shape):
     assert rel_max_err(o, ref) < TOL_BF16
 
 
+@pytest.mark.parametrize("kernel,shape", [((3, 9, 9), (1, 6, 24, 24, 2)), ((5, 13, 13), (1, 8, 26, 26, 1)),
+                                          ((1, 15, 15), (1, 2, 20, 20, 1))])
+def test_na3d_score_jump_beyond_fp32_range(ops, kernel, shape):
+    # A few keys whose scores lie hundreds of binades above everything a query has seen before
+    # them (and below, for other queries): 2^t overflows fp32 against the reference in force, the
+    # running sum cannot be repaired by a rescale, and the kernel has to fall back to computing
+    # those rows again from global memory. The result is still the exact softmax (one key wins).
+    B, D, H, W, nh = shape
+    g = torch.Generator().manual_seed(78)
+    q = (torch.randn(B, D, H, W, nh, 64, generator=g) * 3).bfloat16()
+    k = torch.randn(B, D, H, W, nh, 64, generator=g)
+    hot = torch.rand(B, D, H, W, nh, 1, generator=g) < 0.01
+    k = torch.where(hot, k * 200.0, k).bfloat16()
+    v = torch.randn(B, D, H, W, nh, 64, generator=g).bfloat16()
+    o = ops.na3d(q.cuda(), k.cuda(), v.cuda(), kernel)
+    assert _status() == 0
+    assert torch.isfinite(o).all()
+    ref = bo.na3d(q.float(), k.float(), v.float(), kernel)
+    assert rel_max_err(o, ref) < TOL_BF16
+
+
 def test_na3d_packed_qkv_views_and_unwritten_cells(ops):
     B, D, H, W, nh = 2, 4, 16, 16, 2
     g = torch.Generator().manual_seed(5)
