@@ -247,6 +247,29 @@ __device__ __noinline__ float na_scale_o_row(uint32_t o_taddr, int e) {
   return alpha;
 }
 
+// Reads this thread's row of the O accumulator, scales it by inv and stores it as 64 bf16 at op
+// (nullptr: the row carries no query). Called by a whole warp, once per item.
+__device__ __noinline__ void na_store_o_row(uint32_t o_taddr, float inv, __nv_bfloat16* op) {
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    uint32_t ob[32];
+    tmem_ld_32x32(o_taddr + 32 * hh, ob);
+    tmem_ld_wait();
+    if (op != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 v4;
+        v4.x = pack_bf16(__uint_as_float(ob[j]) * inv, __uint_as_float(ob[j + 1]) * inv);
+        v4.y = pack_bf16(__uint_as_float(ob[j + 2]) * inv, __uint_as_float(ob[j + 3]) * inv);
+        v4.z = pack_bf16(__uint_as_float(ob[j + 4]) * inv, __uint_as_float(ob[j + 5]) * inv);
+        v4.w = pack_bf16(__uint_as_float(ob[j + 6]) * inv, __uint_as_float(ob[j + 7]) * inv);
+        *reinterpret_cast<uint4*>(op + 32 * hh + j) = v4;
+      }
+    }
+  }
+  tc_fence_before();
+}
+
 struct NaItem {
   int b, head, d0, h0, w0, bd0, bh0, bw0;
 };
@@ -487,6 +510,9 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
 
     bool ok = true;
     uint32_t gb = 0;
+    bool pend = false;            // the previous item's row is still to be stored
+    float pend_inv = 0.f;
+    __nv_bfloat16* pend_op = nullptr;
     uint64_t bad_items = 0ull;    // see the end of this branch
     bool bad_rest = false;
     int st_prev = STAGES - 1;     // ring stage and phase of block gb-1 (for pv_done)
@@ -653,6 +679,12 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
             if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
             tc_fence_after();
             p_free = true;
+            if (u == 0 && i == 0 && pend && ok) {
+              // O still holds the previous item (this item's first P V has not been issued):
+              // its rows are normalised and stored now
+              na_store_o_row(o_taddr, pend_inv, pend_op);
+              pend = false;
+            }
           }
           if constexpr (EWP == 16) {
             tmem_st_x16(p_taddr + u * UNIT_PCOLS, &pk[0]);
@@ -671,38 +703,26 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       }
       if (!ok) break;
 
-      // item epilogue: wait for the last P V, normalise this thread's row and store it
-      if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
-        ok = false;
-        break;
+      // The item's row is normalised and stored later - while the first block of the next
+      // item waits for this item's last P V anyway (or after the loop) - so that the wait is
+      // spent on that block's exponentials.
+      if (!(l_run < SUM_REPAIRABLE)) {   // beyond repair (or NaN): this row is computed again below
+        if (n < 64) bad_items |= 1ull << n; else bad_rest = true;
       }
-      tc_fence_after();
       {
-        const float inv = 1.0f / l_run;
-        if (!(l_run < SUM_REPAIRABLE)) {   // beyond repair (or NaN): this row is computed again below
-          if (n < 64) bad_items |= 1ull << n; else bad_rest = true;
-        }
         const long long tok = ((static_cast<long long>(it.b) * p.D + (it.d0 + zd)) * p.o_H +
                                (it.h0 + zh - p.o_h0)) * p.o_W + (it.w0 + zw - p.o_w0);
-        __nv_bfloat16* op = p.out + tok * p.ldo + it.head * 64;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t ob[32];
-          tmem_ld_32x32(o_taddr + 32 * hh, ob);
-          tmem_ld_wait();
-          if (q_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v4;
-              v4.x = pack_bf16(__uint_as_float(ob[j]) * inv, __uint_as_float(ob[j + 1]) * inv);
-              v4.y = pack_bf16(__uint_as_float(ob[j + 2]) * inv, __uint_as_float(ob[j + 3]) * inv);
-              v4.z = pack_bf16(__uint_as_float(ob[j + 4]) * inv, __uint_as_float(ob[j + 5]) * inv);
-              v4.w = pack_bf16(__uint_as_float(ob[j + 6]) * inv, __uint_as_float(ob[j + 7]) * inv);
-              *reinterpret_cast<uint4*>(op + 32 * hh + j) = v4;
-            }
-          }
-        }
-        tc_fence_before();
+        pend_op = q_ok ? p.out + tok * p.ldo + it.head * 64 : nullptr;
+        pend_inv = 1.0f / l_run;
+        pend = true;
+      }
+    }
+    if (ok && pend) {
+      if (mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+        tc_fence_after();
+        na_store_o_row(o_taddr, pend_inv, pend_op);
+      } else {
+        ok = false;
       }
     }
     // rows whose scores left the range of the fast path: computed again the plain way
