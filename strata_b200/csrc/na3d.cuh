@@ -620,18 +620,25 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
             const bool fresh = has_query && l_run == 0.f;
             if (__any_sync(0xffffffffu, fresh)) {
-              // masked maximum of this thread's visible scores (scaled form)
+              // The first reference of a row: the largest of some scores it sees in this unit
+              // (scaled form). Any visible score will do - whatever lies above it by less than
+              // 2^100 is absorbed by the running sum and the moves of the reference that follow
+              // from it - so only the key columns that every query of the tile has in its
+              // window (QW-1 .. KW-1, clamped windows included) are looked at when there are
+              // any, all columns otherwise.
+              constexpr int K2_LO = (KW >= QW) ? (QW - 1) / 2 : 0;
+              constexpr int K2_HI = (KW >= QW) ? (QW - 1) / 2 + 1 : EW / 2;
               float bm = -1e30f;
 #pragma unroll
               for (int rr = 0; rr < 4; ++rr) {
-                float rm0 = -1e30f, rm1 = -1e30f;
+                float rm = -1e30f;
 #pragma unroll
-                for (int k2 = 0; k2 < EW / 2; ++k2) {
+                for (int k2 = K2_LO; k2 < K2_HI; ++k2) {
                   float t0, t1;
                   unpack2(ffma2(pack2u(a[rr][2 * k2], a[rr][2 * k2 + 1]), c2, nb2[k2]), t0, t1);
-                  if (k2 & 1) rm1 = fmaxf(rm1, fmaxf(t0, t1)); else rm0 = fmaxf(rm0, fmaxf(t0, t1));
+                  rm = fmaxf(rm, fmaxf(t0, t1));
                 }
-                bm = fmaxf(bm, ((mine4 >> rr) & 1u) ? fmaxf(rm0, rm1) : -1e30f);
+                bm = fmaxf(bm, ((mine4 >> rr) & 1u) ? rm : -1e30f);
               }
               // nothing has been accumulated for a fresh row (its earlier P were zeros)
               if (fresh && bm > -1e29f) {
