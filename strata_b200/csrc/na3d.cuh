@@ -270,6 +270,16 @@ __device__ __noinline__ void na_store_o_row(uint32_t o_taddr, float inv, __nv_bf
   tc_fence_before();
 }
 
+// mbar_wait with the (bounded) polling loop out of line: the common case - the phase has
+// already completed - costs one test in the softmax warps' hot loop.
+__device__ __noinline__ bool na_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  return mbar_wait(bar, parity, abort_flag, code);
+}
+__device__ __forceinline__ bool na_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return na_wait_slow(bar, parity, abort_flag, code);
+}
+
 struct NaItem {
   int b, head, d0, h0, w0, bd0, bh0, bw0;
 };
@@ -567,7 +577,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
           // the previous P V is) and the running sum - is multiplied by 2^-e, which is exact.
           // A sum beyond SUM_REPAIRABLE (or infinite, or NaN) is left alone: the row is
           // recomputed from global memory when the kernel ends.
-          if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+          if (!na_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
             ok = false;
             break;
           }
@@ -581,7 +591,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
             set_nb(mc);
           }
         }
-        if (!mbar_wait(s_full, gb & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+        if (!na_wait(s_full, gb & 1u, abort_flag, ST_TIMEOUT_SOFTMAX)) {
           ok = false;
           break;
         }
@@ -683,7 +693,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
           }
           if (!p_free) {
-            if (!mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
+            if (!na_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
             tc_fence_after();
             p_free = true;
             if (u == 0 && i == 0 && pend && ok) {
@@ -725,7 +735,7 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
       }
     }
     if (ok && pend) {
-      if (mbar_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
+      if (na_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) {
         tc_fence_after();
         na_store_o_row(o_taddr, pend_inv, pend_op);
       } else {
