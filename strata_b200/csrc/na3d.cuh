@@ -31,23 +31,26 @@
 //               Q K^T has completed) and K / V units (one box of 4 rows x EWP keys per unit;
 //               5-D tensor maps over [B, D, H, W, channels], 128-byte swizzle, a key's 64
 //               channels are one 128-byte row).
-//   warp 1      MMA issuer. After P(i) is ready it issues P V of block i (A operand = P from
-//               TMEM), then Q K^T of block i+1; the S-full arrival of block i+1 therefore
-//               also says that P(i) has been consumed and O is up to date. Barrier arrivals
-//               through tcgen05.commit are kept to two per block (P V done, S full): a commit
-//               costs the issuing thread about as much as three MMAs.
-//   warps 2-5   softmax, one thread per query row (TMEM lane quarter = warp & 3), so a thread
-//               has 64-128 independent scores per block to keep the FMA and exponential units
-//               fed. First block of an item seen by a warp: masked maximum first, to fix the
-//               reference. Afterwards a block is handled in ONE pass against the current
-//               reference with no maximum at all: the block's row sum doubles as the overflow
-//               detector (a sum beyond 2^16, infinite or NaN means some score outran the
-//               reference); only then the block maximum is taken, the reference moved (TMEM
-//               accumulator and running sum rescaled) and the block redone. S is not
-//               overwritten by P, so a redo is always possible. The row loops are kept rolled:
-//               the per-block code stays small enough for the instruction caches with two
-//               CTAs resident. Key rows no query of the warp can see are skipped (zeros
-//               written) without touching the exponential unit.
+//   warp 1      MMA issuer. Q K^T of block i+1 is issued as soon as the softmax warps have
+//               copied the scores of block i out of S (s_free), i.e. while they evaluate its
+//               exponentials; P V of block i (A operand = P from TMEM) follows when P(i) is
+//               ready. Barrier arrivals through tcgen05.commit are kept to two per block (P V
+//               done, S full): a commit costs the issuing thread about as much as three MMAs.
+//   warps 2-5   softmax, one thread per query row (TMEM lane quarter = warp & 3). Per visible
+//               unit: load the 4 x EWP scores into registers, hand S back, one straight-line
+//               pass of exponentials against the row's current reference, add the row sum.
+//               There is no maximum pass: a row's first reference is the largest of a few
+//               scores it certainly sees (any visible score serves), the running sum is the
+//               detector for scores far above the reference, and at the next block's start
+//               the reference then moves up by a whole number of binades e - O and the sum
+//               are multiplied by 2^-e, which is exact, and nothing needs the raw scores
+//               again. A row whose sum leaves the repairable range (2^100, infinite, NaN)
+//               within one block is recomputed from global memory by a plain loop after the
+//               CTA's last item. Everything rare - that loop, the rescale of O, the polling
+//               loops of the barrier waits - and the item's output store are functions out
+//               of line: rare code left inline in this loop cost 2-15 % each without running.
+//               The store of an item's rows happens while the next item's first block waits
+//               for the item's last P V anyway.
 //   P           bf16 pairs, column j of the P region holds keys 2j, 2j+1 of the block; rows a
 //               query cannot see hold zeros.
 //   mask        per (query, key): the key's box coordinates must fall in the query's window
