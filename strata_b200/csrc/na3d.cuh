@@ -694,12 +694,15 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
               if (lane == 0) mbar_arrive(s_free);
               s_released = true;
             }
+            // The zeros of a first unit the warp does not see are stored after the second
+            // unit's exponentials: the wait for the previous P V must not come before them.
+            if (u == 0 && (warp_rows >> 4) != 0u) continue;
           }
           if (!p_free) {
             if (!na_wait(pv_done(st_prev), ph_prev, abort_flag, ST_TIMEOUT_SOFTMAX)) ok = false;
             tc_fence_after();
             p_free = true;
-            if (u == 0 && i == 0 && pend && ok) {
+            if (i == 0 && pend && ok) {
               // O still holds the previous item (this item's first P V has not been issued):
               // its rows are normalised and stored now
               na_store_o_row(o_taddr, pend_inv, pend_op);
@@ -712,6 +715,13 @@ na3d_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
           } else {
             tmem_st_x16(p_taddr + u * UNIT_PCOLS, &pk[0]);
           }
+        }
+        if ((warp_rows & 15u) == 0u && (warp_rows >> 4) != 0u) {   // the postponed zeros of unit 0
+          uint32_t z[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) z[j] = 0u;
+          tmem_st_x16(p_taddr, z);
+          if constexpr (EWP == 16) tmem_st_x16(p_taddr + 16, z);
         }
         if (!ok) break;
         // every lane completes its P stores, then one lane arrives for the warp
