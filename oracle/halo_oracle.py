@@ -326,6 +326,39 @@ def knn_halo(all_tiles: np.ndarray, topo: TileTopology, lon_deg: np.ndarray, lat
     return acc.reshape(*lead, topo.tiles_per_rank, P, P), idx.astype(np.int32), w
 
 
+def plan_halo_forward(all_tiles: np.ndarray, entries, tile_size: int, halo_width: int,
+                      local_tile_ids) -> np.ndarray:
+    """Forward of the plan-based tile halo after DistributedTileKNNHaloPadding.forward
+    (screamcast/distributed_cubesphere_transforms.py:697-781), without the transport: padded
+    tiles start as NaN, interiors are copied, and every plan entry (source tile id, destination
+    tile id, positions [n] in the padded tile, index [n, k] into the source tile, weight [n, k])
+    scatters its interpolated values into its destination tile.
+
+    all_tiles: (..., total_tiles, T, T) float32 in global tile order; entries: iterable of
+    (src_tile_id, dst_tile_id, positions, index, weight). Returns (..., len(local_tile_ids), S, S).
+    Sums run in neighbour order, every product and sum rounded to float32 (no fused multiply-add).
+    """
+    T, h = tile_size, halo_width
+    S = T + 2 * h
+    lead = all_tiles.shape[:-3]
+    local = list(local_tile_ids)
+    out = np.full((*lead, len(local), S, S), np.nan, np.float32)
+    for n, g in enumerate(local):
+        out[..., n, h:h + T, h:h + T] = all_tiles[..., g, :, :]
+    flat_out = out.reshape(*lead, len(local), S * S)
+    where = {g: n for n, g in enumerate(local)}
+    for src, dst, pos, index, weight in entries:
+        if dst not in where:
+            continue
+        tile = all_tiles[..., src, :, :].reshape(*lead, T * T).astype(np.float32)
+        acc = np.zeros((*lead, len(pos)), np.float32)
+        for j in range(index.shape[1]):
+            acc = (acc + (weight[:, j].astype(np.float32) * tile[..., index[:, j]]).astype(np.float32)
+                   ).astype(np.float32)
+        flat_out[..., where[dst], np.asarray(pos)] = acc
+    return flat_out.reshape(*lead, len(local), S, S)
+
+
 # --------------------------------------------------------------------------- wind rotation
 def _basis(lat, lon):
     R = (np.cos(lat) * np.cos(lon), np.cos(lat) * np.sin(lon), np.sin(lat))

@@ -29,7 +29,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .topology import (TileTopology, halo_adjoint_lists, halo_source_maps, knn_adjoint_lists,
-                       knn_halo_weights)
+                       knn_halo_weights, plan_gather_lists)
 
 
 class _DevPtrTensorView:
@@ -320,6 +320,48 @@ class DistributedTileKNNHaloPadding(DistributedTileCopyHaloPadding):
                 self.knn_weights.data_ptr(), self.k, tpr, topo.tile_size, topo.halo_width, L,
                 torch.cuda.current_stream().cuda_stream), "strata_halo_gather_knn_fields_f32")
         return out
+
+class DistributedTilePlanHaloPadding(DistributedTileKNNHaloPadding):
+    """The plan-based tile halo: `DistributedTileKNNHaloPadding(plan, rank, group)` of the
+    reference's screamcast/distributed_cubesphere_transforms.py:611-781.
+
+    Same constructor arguments (a `TileHaloPlan` from `build_distributed_tile_halo_plan`, this
+    rank, an optional process group) and the same `forward(data_local[..., tiles_per_rank, T, T])
+    -> [..., tiles_per_rank, T + 2h, T + 2h]`: interiors copied, every halo cell interpolated
+    from the k nearest cells of the ONE source tile the plan assigned it to. The reference
+    interpolates on the sending rank, packs a send buffer and runs `all_to_all_single`; here
+    the receiving rank reads the k source cells of each of its halo cells from their owner's
+    tile (local or peer memory) with the weighted-gather kernel, so nothing is packed, sent or
+    scattered and the plan's send / receive sizes are bookkeeping only.
+    """
+
+    def __init__(self, plan, rank: int, group=None, device=None, **kw):
+        topo = TileTopology(plan.world_size, int(rank), plan.face_size, plan.tile_size,
+                            plan.halo_width)
+        idx, w = plan_gather_lists(plan, int(rank))
+        torch.nn.Module.__init__(self)
+        DistributedTileCopyHaloPadding.__init__(self, topology=topo, device=device, group=group, **kw)
+        dev = self.src_a.device
+        self.k = int(idx.shape[1])
+        self.register_buffer("knn_idx", torch.from_numpy(idx).to(dev).contiguous(), persistent=False)
+        self.register_buffer("knn_weights", torch.from_numpy(w).to(dev).contiguous(), persistent=False)
+        self.plan = plan
+        self.rank = int(rank)
+        self.world_size = plan.world_size
+        self.tile_size = plan.tile_size
+        self.halo_width = plan.halo_width
+        self.tiles_per_rank = plan.tiles_per_rank
+        self.tiles_per_dim = plan.tiles_per_dim
+        self.padded_size = plan.tile_size + 2 * plan.halo_width
+        self.my_tiles = list(topo.local_tiles)
+        self._send_sizes = [plan.send_sizes[self.rank][r] for r in range(plan.world_size)]
+        self._recv_sizes = [plan.recv_sizes[self.rank][r] for r in range(plan.world_size)]
+
+    @classmethod
+    def from_padded_face_grid(cls, **kw):
+        raise TypeError("the plan-based halo is built from a TileHaloPlan "
+                        "(build_distributed_tile_halo_plan), not from padded face grids")
+
 
 class NormalizedCopyHaloAdjoint(torch.nn.Module):
     """Windowed overlap-add un-pad: D_w^-1 A^T (w . y) for the copy-halo exchange A.

@@ -441,3 +441,263 @@ def knn_halo_weights(topo: TileTopology, lon_deg: np.ndarray, lat_deg: np.ndarra
     lam = 1.0 / (dist + eps)
     lam = lam / lam.sum(axis=1, keepdims=True)
     return idx.astype(np.int32), lam.astype(np.float32)
+
+
+# --------------------------------------------------------------------------- plan-based KNN halo
+@dataclass
+class TileSendEntry:
+    """One (source tile -> part of a destination tile's halo) entry of a plan, as the reference
+    lays it out (screamcast/distributed_cubesphere_transforms.py:48-55). The regridder state is
+    {"index": int64 [n, k] cells of the source tile (row-major T*T), "weight": float32 [n, k]}."""
+
+    src_tile: tuple
+    regridder_state_dict: dict
+    dst_halo_positions: torch.Tensor
+
+
+@dataclass
+class TileHaloPlan:
+    """Routing plan of the tile-level KNN halo: fields of the reference's TileHaloPlan
+    (screamcast/distributed_cubesphere_transforms.py:57-78) plus the same information as dense
+    tables, which is what the gather kernel consumes.
+
+    Every tile has the same halo cells (`halo_positions`: flat row-major positions in the padded
+    tile, ascending). Halo cell n of tile g is interpolated from the k cells `knn_index[g, n]`
+    (row-major inside the source tile) of tile `src_tile_id[g, n]` with `knn_weight[g, n]`.
+    """
+
+    face_size: int
+    tile_size: int
+    tiles_per_dim: int
+    halo_width: int
+    ne: int
+    npg: int
+    world_size: int
+    tiles_per_rank: int
+    tile_to_rank: dict
+    recv_counts: dict
+    send_sizes: dict
+    recv_sizes: dict
+    halo_positions: np.ndarray      # [n_halo] int64
+    src_tile_id: np.ndarray         # [total_tiles, n_halo] int32
+    knn_index: np.ndarray           # [total_tiles, n_halo, k] int32
+    knn_weight: np.ndarray          # [total_tiles, n_halo, k] float32
+
+    @property
+    def send_plans(self) -> dict:
+        """send_plans[src_rank][(face, ti, tj) of the destination] = [TileSendEntry, ...], built
+        on demand from the tables (one entry per source tile, ascending tile id)."""
+        tpd = self.tiles_per_dim
+        out = {r: {} for r in range(self.world_size)}
+        for g in range(self.src_tile_id.shape[0]):
+            dst_tile = tile_id_to_tuple(g, tpd)
+            for s in np.unique(self.src_tile_id[g]):
+                m = self.src_tile_id[g] == s
+                src_tile = tile_id_to_tuple(int(s), tpd)
+                entry = TileSendEntry(
+                    src_tile=src_tile,
+                    regridder_state_dict={
+                        "index": torch.from_numpy(self.knn_index[g][m].astype(np.int64)),
+                        "weight": torch.from_numpy(self.knn_weight[g][m])},
+                    dst_halo_positions=torch.from_numpy(self.halo_positions[m]))
+                out[self.tile_to_rank[src_tile]].setdefault(dst_tile, []).append(entry)
+        return out
+
+
+def tile_id_to_tuple(tile_id: int, tiles_per_dim: int) -> tuple:
+    """Linear tile id -> (face, ti, tj) (reference _tile_id_to_tuple, :174-181)."""
+    face, rem = divmod(int(tile_id), tiles_per_dim * tiles_per_dim)
+    return (face, rem // tiles_per_dim, rem % tiles_per_dim)
+
+
+def tile_tuple_to_id(face: int, ti: int, tj: int, tiles_per_dim: int) -> int:
+    return face * tiles_per_dim * tiles_per_dim + ti * tiles_per_dim + tj
+
+
+def build_tile_to_rank_map(tiles_per_dim: int, world_size: int) -> dict:
+    """(face, ti, tj) -> rank: consecutive tile ids in equal shares (reference :189-199)."""
+    total = 6 * tiles_per_dim * tiles_per_dim
+    per_rank = total // world_size
+    return {tile_id_to_tuple(t, tiles_per_dim): t // per_rank for t in range(total)}
+
+
+def tile_halo_positions(tile_size: int, halo_width: int) -> np.ndarray:
+    """Flat row-major positions of the halo cells of a padded tile, ascending (the order in which
+    the reference extracts a tile's halo, :262-283, and `_halo_dst_flat_indices_per_face`)."""
+    S = tile_size + 2 * halo_width
+    ii, jj = np.meshgrid(np.arange(S), np.arange(S), indexing="ij")
+    halo = (ii < halo_width) | (ii >= halo_width + tile_size) | \
+           (jj < halo_width) | (jj >= halo_width + tile_size)
+    return (ii[halo] * S + jj[halo]).astype(np.int64)
+
+
+def _unit_f32(lon_deg: np.ndarray, lat_deg: np.ndarray) -> np.ndarray:
+    """Unit vectors in the precision the reference's assignment step works in (float32 degrees ->
+    float32 radians -> float32 components, :126-141 and :319-324)."""
+    lo, la = np.deg2rad(lon_deg.astype(np.float32)), np.deg2rad(lat_deg.astype(np.float32))
+    return np.stack([np.cos(la) * np.cos(lo), np.cos(la) * np.sin(lo), np.sin(la)], axis=-1)
+
+
+def _unit_f64(lon_deg: np.ndarray, lat_deg: np.ndarray) -> np.ndarray:
+    lo, la = np.radians(lon_deg.astype(np.float64)), np.radians(lat_deg.astype(np.float64))
+    return np.stack([np.cos(la) * np.cos(lo), np.cos(la) * np.sin(lo), np.sin(la)], axis=-1)
+
+
+def padded_lonlat_from_target_grid(grid_tgt: dict, face_size: int, halo_width: int,
+                                   num_pg_cells: int) -> np.ndarray:
+    """(2, 6, S, S) lon / lat of the padded faces cut out of a padded target grid in element
+    order (reference `_padded_lonlat_from_target_grid`, :346-401): the file's faces may carry a
+    wider halo than asked for; the centred window of S = face_size + 2*halo_width is taken."""
+    lon_t, lat_t = (np.asarray(grid_tgt[k]).astype(np.float32) for k in ("lon", "lat"))
+    n_cells = len(lon_t)
+    fs_file = int((n_cells / 6) ** 0.5)
+    if fs_file * fs_file * 6 != n_cells:
+        raise ValueError(f"Target grid has {n_cells} cells, not compatible with 6 square faces")
+    ne_file = fs_file // num_pg_cells
+    lon_f = unstructured_to_6faces(torch.from_numpy(lon_t), ne=ne_file, npg=num_pg_cells).numpy()
+    lat_f = unstructured_to_6faces(torch.from_numpy(lat_t), ne=ne_file, npg=num_pg_cells).numpy()
+    hw_file = (fs_file - face_size) // 2
+    if halo_width > hw_file:
+        raise ValueError(f"Requested halo_width={halo_width} exceeds target grid's "
+                         f"halo_width_file={hw_file}")
+    i0, i1 = hw_file - halo_width, hw_file + face_size + halo_width
+    S = face_size + 2 * halo_width
+    out = np.stack([lon_f[:, i0:i1, i0:i1], lat_f[:, i0:i1, i0:i1]], axis=0)
+    if out.shape != (2, 6, S, S):
+        raise ValueError(f"Expected padded shape (6, {S}, {S}), got {out.shape[1:]}")
+    return out
+
+
+def build_distributed_tile_halo_plan(grid_src: dict, num_elements: int, tile_size: int,
+                                     halo_width: int, num_pg_cells: int = 2, k: int = 4,
+                                     eps: float = 1e-7, world_size: int = 96,
+                                     grid_tgt: dict | None = None) -> TileHaloPlan:
+    """Routing plan of the tile-level KNN halo (same arguments and meaning as the reference's
+    build_distributed_tile_halo_plan, screamcast/distributed_cubesphere_transforms.py:404-608).
+
+    grid_src: {"lon": (6*N*N,), "lat": (6*N*N,)} degrees, element order. Every halo cell of every
+    tile gets a position on the sphere - from `grid_tgt` (a padded grid in element order) when
+    given, otherwise from the face-level copy / rot90 / corner padding of the source lon / lat -
+    then ONE source tile: the face whose nearest cell is closest (ties: lowest face), and on
+    that face the tile holding the nearest cell. Its value is the inverse-distance-weighted mean
+    (1 / (chord distance + eps), normalised) of the k nearest cells of THAT tile. The reference
+    builds one earth2grid regridder per (source tile, destination tile) pair; here the same
+    index / weight lists are kept as dense tables.
+    """
+    from scipy import spatial
+    face_size = num_elements * num_pg_cells
+    if face_size % tile_size != 0:
+        raise ValueError(f"face_size={face_size} must be divisible by tile_size={tile_size}")
+    tpd = face_size // tile_size
+    total_tiles = 6 * tpd * tpd
+    if total_tiles % world_size != 0:
+        raise ValueError(f"total_tiles={total_tiles} must be divisible by world_size={world_size}")
+    tiles_per_rank = total_tiles // world_size
+    tile_to_rank = build_tile_to_rank_map(tpd, world_size)
+    T, h, N = tile_size, halo_width, face_size
+
+    lon_faces, lat_faces = (unstructured_to_6faces(
+        torch.from_numpy(np.asarray(grid_src[key]).astype(np.float32)), ne=num_elements,
+        npg=num_pg_cells).numpy() for key in ("lon", "lat"))
+    if grid_tgt is not None:
+        padded = padded_lonlat_from_target_grid(grid_tgt, face_size, halo_width, num_pg_cells)
+    else:
+        a, b = face_halo_sources(N, h)
+        padded = np.stack([apply_face_maps(lon_faces, a, b), apply_face_maps(lat_faces, a, b)])
+    padded_lon, padded_lat = padded[0], padded[1]
+
+    face_xyz = _unit_f32(lon_faces, lat_faces).reshape(6, N * N, 3)
+    face_trees = [spatial.KDTree(face_xyz[f]) for f in range(6)]
+    tile_trees: dict = {}
+
+    def tree_of_tile(g: int):
+        if g not in tile_trees:
+            f, ti, tj = tile_id_to_tuple(g, tpd)
+            sl = (f, slice(ti * T, (ti + 1) * T), slice(tj * T, (tj + 1) * T))
+            tile_trees[g] = spatial.cKDTree(_unit_f64(lon_faces[sl], lat_faces[sl]).reshape(-1, 3))
+        return tile_trees[g]
+
+    pos = tile_halo_positions(T, h)
+    n_halo = len(pos)
+    S = T + 2 * h
+    src_tile_id = np.zeros((total_tiles, n_halo), np.int32)
+    knn_index = np.zeros((total_tiles, n_halo, k), np.int32)
+    knn_weight = np.zeros((total_tiles, n_halo, k), np.float32)
+    recv_counts: dict = {}
+    send_sizes = {sr: {dr: 0 for dr in range(world_size)} for sr in range(world_size)}
+    for g in range(total_tiles):
+        dst_tile = tile_id_to_tuple(g, tpd)
+        recv_counts[dst_tile] = {}
+        if n_halo == 0:
+            continue
+        f, ti, tj = dst_tile
+        hl_lon = padded_lon[f, ti * T:ti * T + S, tj * T:tj * T + S].reshape(-1)[pos].astype(np.float32)
+        hl_lat = padded_lat[f, ti * T:ti * T + S, tj * T:tj * T + S].reshape(-1)[pos].astype(np.float32)
+        q32 = _unit_f32(hl_lon, hl_lat)
+        best_face = np.zeros(n_halo, np.int64)
+        best_dist = np.full(n_halo, np.inf)
+        nearest = np.zeros((6, n_halo), np.int64)
+        for face_id, tree in enumerate(face_trees):
+            d, nearest[face_id] = tree.query(q32, k=1)
+            closer = d < best_dist
+            best_dist[closer] = d[closer]
+            best_face[closer] = face_id
+        cell = nearest[best_face, np.arange(n_halo)]
+        src = best_face * tpd * tpd + (cell // N // T) * tpd + (cell % N) // T
+        src_tile_id[g] = src
+        q64 = _unit_f64(hl_lon, hl_lat)
+        for s in np.unique(src):
+            m = src == s
+            dist, idx = tree_of_tile(int(s)).query(q64[m], k=k)
+            if k == 1:
+                dist, idx = dist[:, None], idx[:, None]
+            lam = 1.0 / (dist + eps)
+            knn_index[g][m] = idx
+            knn_weight[g][m] = (lam / lam.sum(axis=1, keepdims=True)).astype(np.float32)
+            sr = tile_to_rank[tile_id_to_tuple(int(s), tpd)]
+            n = int(m.sum())
+            recv_counts[dst_tile][sr] = recv_counts[dst_tile].get(sr, 0) + n
+            send_sizes[sr][tile_to_rank[dst_tile]] += n
+    recv_sizes = {dr: {sr: send_sizes[sr][dr] for sr in range(world_size)} for dr in range(world_size)}
+    return TileHaloPlan(face_size=face_size, tile_size=T, tiles_per_dim=tpd, halo_width=h,
+                        ne=num_elements, npg=num_pg_cells, world_size=world_size,
+                        tiles_per_rank=tiles_per_rank, tile_to_rank=tile_to_rank,
+                        recv_counts=recv_counts, send_sizes=send_sizes, recv_sizes=recv_sizes,
+                        halo_positions=pos, src_tile_id=src_tile_id, knn_index=knn_index,
+                        knn_weight=knn_weight)
+
+
+def apply_face_maps(faces: np.ndarray, src_a: np.ndarray, src_b: np.ndarray) -> np.ndarray:
+    """(..., 6, N, N) -> (..., 6, N+2p, N+2p) through the face-level source maps of
+    `face_halo_sources` (copy, rot90 orientation, corner rule; diagonal cells = mean of two)."""
+    lead = faces.shape[:-3]
+    flat = faces.reshape(*lead, -1)
+    va = flat[..., src_a]
+    vb = flat[..., np.where(src_b < 0, 0, src_b)]
+    return np.where(src_b < 0, va, (va + vb) / 2).astype(faces.dtype)
+
+
+def plan_gather_lists(plan: TileHaloPlan, rank: int):
+    """The plan as the weighted-gather kernel reads it: (idx int32 [tiles_per_rank*P*P, k] of
+    GLOBAL interior cell ids g*T*T + i*T + j, weights float32) for this rank's padded tiles.
+    An interior cell is itself with weight 1 (zeros for the other k-1 terms): copied exactly."""
+    T, h = plan.tile_size, plan.halo_width
+    P = T + 2 * h
+    k = plan.knn_index.shape[2]
+    tpr = plan.tiles_per_rank
+    idx = np.zeros((tpr, P * P, k), np.int64)
+    w = np.zeros((tpr, P * P, k), np.float32)
+    ii, jj = np.meshgrid(np.arange(T), np.arange(T), indexing="ij")
+    inner_pos = ((ii + h) * P + (jj + h)).reshape(-1)
+    inner_cell = (ii * T + jj).reshape(-1)
+    for n in range(tpr):
+        g = rank * tpr + n
+        idx[n, inner_pos, :] = (g * T * T + inner_cell)[:, None]
+        w[n, inner_pos, 0] = 1.0
+        if len(plan.halo_positions):
+            idx[n, plan.halo_positions, :] = plan.src_tile_id[g].astype(np.int64)[:, None] * T * T + \
+                plan.knn_index[g]
+            w[n, plan.halo_positions, :] = plan.knn_weight[g]
+    if plan.src_tile_id.shape[0] * T * T >= 2 ** 31:
+        raise ValueError("grid too large for 32-bit cell ids")
+    return idx.reshape(tpr * P * P, k).astype(np.int32), w.reshape(tpr * P * P, k)

@@ -73,7 +73,25 @@ def main():
         assert np.array_equal(got.cpu().numpy().reshape(want.shape), want), \
             f"rank {rank} step {step}: knn halo differs"
     knn.check_status()
+    # plan-based tile halo: each halo cell from ONE assigned source tile, read through peer memory
+    from strata_b200.halo import DistributedTilePlanHaloPadding
+    from strata_b200.rollout import equiangular_cubed_sphere_latlon
+    from strata_b200.topology import build_distributed_tile_halo_plan, faces_to_unstructured
+    npg = 2
+    la0, lo0 = equiangular_cubed_sphere_latlon(fs)
+    grid = {key: faces_to_unstructured(torch.from_numpy(v.astype(np.float32)), ne=fs // npg, npg=npg).numpy()
+            for key, v in (("lon", lo0), ("lat", la0))}
+    plan = build_distributed_tile_halo_plan(grid, fs // npg, ts, hw, num_pg_cells=npg, world_size=world)
+    pm = DistributedTilePlanHaloPadding(plan, rank)
+    for step in range(3):
+        got = pm((xa[:, s:s + topo.tiles_per_rank] * (step + 1)).cuda())
+        want = _apply((xa * (step + 1)).numpy(), pm.knn_idx.cpu().numpy(), pm.knn_weights.cpu().numpy())
+        assert np.array_equal(got.cpu().numpy().reshape(want.shape), want), \
+            f"rank {rank} step {step}: plan halo differs"
+        assert torch.equal(got[..., hw:-hw, hw:-hw].cpu(), xa[:, s:s + topo.tiles_per_rank] * (step + 1))
+    pm.check_status()
     dist.barrier()
+    pm.close()
     knn.close()
     mod.close()
     if rank == 0:

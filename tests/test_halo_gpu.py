@@ -147,6 +147,40 @@ def test_knn_halo_bit_exact_against_host_evaluation():
     with pytest.raises(TypeError):
         mod(x.cuda().double())
 
+def test_plan_halo_equals_the_reference_module(golden_dir):
+    # plan-based tile halo (reference DistributedTileKNNHaloPadding(plan, rank, group)): the
+    # reference module's own output at world_size 1 (tests/golden/make_plan_golden.py)
+    from strata_b200.halo import DistributedTilePlanHaloPadding, NormalizedHaloAdjoint
+    from strata_b200.topology import build_distributed_tile_halo_plan
+    from tests.test_halo_knn import _apply
+    gold = np.load(golden_dir / "tile_halo_plan.npz")
+    T, h = int(gold["tile"]), int(gold["halo"])
+    plan = build_distributed_tile_halo_plan({"lon": gold["grid_lon"], "lat": gold["grid_lat"]}, int(gold["ne"]),
+                                            T, h, num_pg_cells=int(gold["npg"]), world_size=1)
+    mod = DistributedTilePlanHaloPadding(plan, rank=0)
+    assert (mod.tile_size, mod.halo_width, mod.padded_size, mod.tiles_per_rank) == (T, h, T + 2 * h, 24)
+    x = torch.from_numpy(gold["ws1_forward_in"])
+    got = mod(x.cuda())
+    mod.check_status()
+    assert got.shape == gold["ws1_forward_out"].shape
+    assert not torch.isnan(got).any()
+    assert torch.equal(got[..., h:-h, h:-h].cpu(), x)                      # interiors copied exactly
+    assert np.allclose(got.cpu().numpy(), gold["ws1_forward_out"], rtol=0, atol=1e-6)
+    want = _apply(x.numpy(), mod.knn_idx.cpu().numpy(), mod.knn_weights.cpu().numpy())
+    assert np.array_equal(got.cpu().numpy().reshape(want.shape), want)
+    # one leading dimension, none, and a halo of width zero (tiles come back unchanged)
+    assert torch.equal(mod(x[0].cuda()), got[0]) and torch.equal(mod(x[1, 2].cuda()), got[1, 2])
+    plan0 = build_distributed_tile_halo_plan({"lon": gold["grid_lon"], "lat": gold["grid_lat"]}, int(gold["ne"]),
+                                             T, 0, num_pg_cells=int(gold["npg"]), world_size=1)
+    assert torch.equal(DistributedTilePlanHaloPadding(plan0, rank=0)(x.cuda()).cpu(), x)
+    # its normalised adjoint un-pads constant fields to themselves
+    unpad = NormalizedHaloAdjoint(mod)
+    c = torch.full((1, 24, T, T), 2.5, device="cuda")
+    assert torch.allclose(unpad(mod(c)), c, rtol=1e-5, atol=0)
+    with pytest.raises(TypeError):
+        DistributedTilePlanHaloPadding.from_padded_face_grid(topology=None)
+
+
 def test_knn_halo_adjoint_matches_oracle():
     # the reference's un-pad operator proper: D_w^-1 A^T (w . y) with A the KNN regrid
     # (NormalizedHaloAdjoint, screamcast/distributed_halo.py:330-448)
