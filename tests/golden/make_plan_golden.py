@@ -1,4 +1,6 @@
-"""Generates tests/golden/tile_halo_plan.npz from the reference's own plan builder and module.
+"""Generates tests/golden/tile_halo_plan.npz (plan-based tile halo) and
+tests/golden/knn_allgather_halo.npz (all-gather KNN halo and its normalised adjoint) from the
+reference's own code.
 
     python tests/golden/make_plan_golden.py /path/to/reference
 
@@ -10,6 +12,9 @@ compute inverse-distance weights 1 / (chord distance + eps), normalised, over th
 source points. Everything else - halo cell extraction, assignment of halo cells to source
 faces and tiles, grouping into send entries, send / receive sizes, and the module's forward
 (interior fill, per-entry interpolation, scatter) at world_size 1 - is the reference's code.
+The second file runs screamcast/distributed_halo.py's DistributedTileKNNHaloPadding_AllGather
+(source / destination point selection, all-gather, regrid) and NormalizedHaloAdjoint (vjp of the
+regrid, window, normalisation) at world_size 1 with the same stand-in interpolator.
 The tests never import the reference.
 """
 import sys
@@ -147,6 +152,36 @@ def main(ref_root):
     out["tgt_cells"] = np.array(rows, dtype=np.int64)
     np.savez_compressed(OUT / "tile_halo_plan.npz", **out)
     print("wrote", OUT / "tile_halo_plan.npz", {k: v.shape for k, v in out.items() if hasattr(v, "shape")})
+
+    # ---- all-gather KNN halo + normalised adjoint (screamcast/distributed_halo.py:208-448)
+    import os
+    import torch.distributed as dist
+    import screamcast.distributed_halo as dh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29655")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    pw, T, h = from_tgt * NPG, TILE, HALO       # the padded faces built above: N + 2*pw per side
+    topo = dh.TileTopology(world_size=1, rank=0, face_size=N, tile_size=T, halo_width=h)
+    mod = dh.DistributedTileKNNHaloPadding_AllGather.from_padded_face_grid(
+        topology=topo, lon=torch.from_numpy(lon_t), lat=torch.from_numpy(lat_t), pad_width_data=pw,
+        device=torch.device("cpu"))
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(2, 3, topo.tiles_per_rank, T, T, generator=g)
+    y = mod(x)
+    P = T + 2 * h
+    win1 = torch.sin((torch.arange(P) + 0.5) / P * np.pi) ** 2
+    window = (win1[:, None] * win1[None, :]).float()
+    yp = torch.randn(2, topo.tiles_per_rank, P, P, generator=g)
+    adj = dh.NormalizedHaloAdjoint(mod)(yp)
+    adj_w = dh.NormalizedHaloAdjoint(mod, window=window)(yp)
+    knn = {"face_size": np.int64(N), "tile": np.int64(T), "halo": np.int64(h), "pad_width_data": np.int64(pw),
+           "lon_padded": lon_t, "lat_padded": lat_t, "x": x.numpy(), "forward": y.numpy(),
+           "index": mod.regrid.index.numpy(), "weight": mod.regrid.weight.numpy(),
+           "lat_deg": mod.lat_deg.numpy(), "lon_deg": mod.lon_deg.numpy(),
+           "padded_in": yp.numpy(), "window": window.numpy(), "adjoint": adj.numpy(),
+           "adjoint_windowed": adj_w.numpy()}
+    dist.destroy_process_group()
+    np.savez_compressed(OUT / "knn_allgather_halo.npz", **knn)
+    print("wrote", OUT / "knn_allgather_halo.npz", {k: v.shape for k, v in knn.items() if hasattr(v, "shape")})
 
 
 if __name__ == "__main__":

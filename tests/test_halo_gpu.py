@@ -147,6 +147,30 @@ def test_knn_halo_bit_exact_against_host_evaluation():
     with pytest.raises(TypeError):
         mod(x.cuda().double())
 
+def test_knn_halo_and_adjoint_equal_the_reference_modules(golden_dir):
+    # the reference's DistributedTileKNNHaloPadding_AllGather / NormalizedHaloAdjoint outputs at
+    # world_size 1 (tests/golden/make_plan_golden.py: the reference's modules, earth2grid's
+    # interpolator replaced by a stand-in of the same interface)
+    from strata_b200.halo import DistributedTileKNNHaloPadding, NormalizedHaloAdjoint
+    from strata_b200.topology import TileTopology
+    gold = np.load(golden_dir / "knn_allgather_halo.npz")
+    n, t, h, pw = (int(gold[k]) for k in ("face_size", "tile", "halo", "pad_width_data"))
+    topo = TileTopology(1, 0, n, t, h)
+    mod = DistributedTileKNNHaloPadding.from_padded_face_grid(
+        topology=topo, lon=torch.from_numpy(gold["lon_padded"]), lat=torch.from_numpy(gold["lat_padded"]),
+        pad_width_data=pw, device="cuda")
+    assert torch.equal(mod.lat_deg.cpu(), torch.from_numpy(gold["lat_deg"]))
+    assert torch.equal(mod.lon_deg.cpu(), torch.from_numpy(gold["lon_deg"]))
+    got = mod(torch.from_numpy(gold["x"]).cuda())
+    assert np.allclose(got.cpu().numpy(), gold["forward"], rtol=0, atol=1e-6)
+    yp = torch.from_numpy(gold["padded_in"]).cuda()
+    for key, window in (("adjoint", None), ("adjoint_windowed", torch.from_numpy(gold["window"]))):
+        want = gold[key].reshape(yp.shape[:-2] + (t, t))
+        out = NormalizedHaloAdjoint(mod, window=window)(yp)
+        assert np.allclose(out.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+    mod.check_status()
+
+
 def test_plan_halo_equals_the_reference_module(golden_dir):
     # plan-based tile halo (reference DistributedTileKNNHaloPadding(plan, rank, group)): the
     # reference module's own output at world_size 1 (tests/golden/make_plan_golden.py)

@@ -132,3 +132,25 @@ def test_knn_adjoint_lists_are_the_transpose(world):
         assert np.allclose(back, 3.25, atol=1e-3)
     with pytest.raises(ValueError, match="idx_all"):
         knn_adjoint_lists(full, idx_all[:-1], w_all[:-1])
+
+
+def test_lists_forward_and_adjoint_equal_the_reference_modules():
+    # outputs of the reference's DistributedTileKNNHaloPadding_AllGather and NormalizedHaloAdjoint
+    # (screamcast/distributed_halo.py:208-448) at world_size 1, with earth2grid's interpolator
+    # replaced by a stand-in of the same interface (tests/golden/make_plan_golden.py): the
+    # selection of source and destination points, their order, the regrid and its normalised,
+    # windowed transpose are the reference's code
+    from pathlib import Path
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "knn_allgather_halo.npz")
+    n, t, h, pw = (int(gold[k]) for k in ("face_size", "tile", "halo", "pad_width_data"))
+    topo = TileTopology(1, 0, n, t, h)
+    idx, w = knn_halo_weights(topo, gold["lon_padded"], gold["lat_padded"], pw)
+    assert np.array_equal(idx, gold["index"])
+    assert np.allclose(w, gold["weight"], rtol=0, atol=1e-7)
+    got = _apply(gold["x"], idx, w).reshape(gold["forward"].shape)
+    assert np.allclose(got, gold["forward"], rtol=0, atol=1e-6)
+    otopo = ho.TileTopology(1, 0, n, t, h)
+    for key, window in (("adjoint", None), ("adjoint_windowed", gold["window"])):
+        want = gold[key].reshape(gold["padded_in"].shape[:-2] + (t, t))
+        adj = ho.knn_halo_adjoint(gold["padded_in"], otopo, idx, w, window)
+        assert np.allclose(adj, want, rtol=1e-5, atol=1e-5)
