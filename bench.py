@@ -371,13 +371,20 @@ def run_gpu_arm(args):
     # end to end: pinned host buffers in, pinned host buffers out, through the public host API
     # (copies and compute pipelined over chunks of tiles, the same C-ABI block call inside)
     from strata_b200.host_pipeline import HostBlockPipeline
-    pipe = HostBlockPipeline(T, C, hidden, device=dev, chunk_tiles=1)
+    pipe = HostBlockPipeline(T, C, hidden, device=dev, chunk_tiles=1, ring=4)
+    e2e_steps = max(2, min(args.steps, 10))
+
+    # steps are streamed: each copies its own input from pinned host memory and its own result
+    # back, but a step's first host->device copy does not wait for the previous step's last
+    # device->host copy; the timed region ends when the last result has landed (join)
+    calls = {"n": 0}
 
     def e2e_step():
-        pipe.run(x_host, y_host, weights, grid=(D, H, W), num_heads=heads, kernel=kernel, rope_cs=cs)
-    for _ in range(2):
+        calls["n"] += 1
+        pipe.run(x_host, y_host, weights, grid=(D, H, W), num_heads=heads, kernel=kernel, rope_cs=cs,
+                 join=calls["n"] % e2e_steps == 0)
+    for _ in range(e2e_steps):
         e2e_step()
-    e2e_steps = max(2, min(args.steps, 10))
     ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
     e2e_value = tokens_job / (ms_e2e * 1e-3)
 

@@ -275,6 +275,19 @@ def test_host_pipeline_matches_device_call(ops):
         pipe.run(x_host, y_host, w, grid=grid, num_heads=heads, kernel=kernel, rope_cs=cs)
         torch.cuda.synchronize()
         assert torch.equal(y_host, want.cpu())
+    # streamed calls: several steps with their own host buffers, copies of consecutive steps
+    # overlapping; results are complete after join()
+    pipe = HostBlockPipeline(D * H * W, C, 4 * C, chunk_tiles=1, ring=3)
+    xs = [(x * (1 + 0.25 * k)).bfloat16().pin_memory() for k in range(3)]
+    ys = [torch.zeros_like(x).pin_memory() for _ in range(3)]
+    for k in range(3):
+        pipe.run(xs[k], ys[k], w, grid=grid, num_heads=heads, kernel=kernel, rope_cs=cs, join=False)
+    pipe.join()
+    torch.cuda.current_stream().synchronize()
+    for k in range(3):
+        wk = ops.block_forward(xs[k].cuda(), w, grid=grid, num_heads=heads, kernel=kernel, rope_cos=None,
+                               rope_sin=None, rope_cs=cs)
+        assert torch.equal(ys[k], wk.cpu()), f"streamed step {k}"
     assert _status() == 0
     with pytest.raises(TypeError):
         pipe.run(x, y_host, w, grid=grid, num_heads=heads, kernel=kernel)   # not pinned
