@@ -188,6 +188,65 @@ __device__ __forceinline__ void gemm_epilogue_16(float (&v)[16], bool rotate, fl
   }
 }
 
+// Per-head RMS factors of the q/k norm for one output row: one extra pass over the warp's
+// WARP_COLS accumulator columns (+ bias). head_dim 64: the warp's 64 columns are one head, both
+// components carry its factor; head_dim 32: one factor per 32-column sub-chunk. Called by a
+// whole warp (tensor-memory loads).
+template <int NSUB>
+__device__ __noinline__ float2 gemm_qk_norm_scales(uint32_t taddr, const float* bias, int n_warp0,
+                                                   int N, int lane, int head_dim, float eps) {
+  static_assert(NSUB == 1 || NSUB == 2, "one or two 32-column sub-chunks per warp");
+  float ss[NSUB];
+#pragma unroll
+  for (int cc = 0; cc < NSUB; ++cc) {
+    float acc = 0.f;
+    float bl = 0.f;
+    if (bias != nullptr && n_warp0 + 32 * cc + lane < N) bl = __ldg(bias + n_warp0 + 32 * cc + lane);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      uint32_t r[16];
+      tmem_ld_32x16(taddr + 32 * cc + 16 * g, r);
+      tmem_ld_wait();
+      const int nb0 = n_warp0 + 32 * cc + 16 * g;
+      if (bias != nullptr && nb0 + 16 <= N) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + nb0) + q4);
+          const float x0 = __uint_as_float(r[4 * q4]) + b4.x;
+          const float x1 = __uint_as_float(r[4 * q4 + 1]) + b4.y;
+          const float x2 = __uint_as_float(r[4 * q4 + 2]) + b4.z;
+          const float x3 = __uint_as_float(r[4 * q4 + 3]) + b4.w;
+          acc += x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float x = __uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bl, 16 * g + j);
+          acc += x * x;
+        }
+      }
+    }
+    ss[cc] = acc;
+  }
+  if (head_dim == 64 && NSUB == 2) {
+    const float f = rsqrtf((ss[0] + ss[NSUB - 1]) * (1.0f / 64.0f) + eps);
+    return make_float2(f, f);
+  }
+  return make_float2(rsqrtf(ss[0] * (1.0f / 32.0f) + eps), rsqrtf(ss[NSUB - 1] * (1.0f / 32.0f) + eps));
+}
+
+// mbar_wait with the (bounded) polling loop out of line, for the epilogue warps: the phase has
+// usually completed, and rare code left inline in their loop costs registers and schedule.
+__device__ __noinline__ bool gemm_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int code) {
+  return mbar_wait(bar, parity, abort_flag, code);
+}
+__device__ __forceinline__ bool gemm_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return gemm_wait_slow(bar, parity, abort_flag, code);
+}
+
 template <int BN, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -400,7 +459,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (!acc_ready) {
-          if (!mbar_wait(accf_bar(buf), acc_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
+          if (!gemm_wait(accf_bar(buf), acc_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
             ok = false;
             break;
           }
@@ -411,52 +470,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                static_cast<uint32_t>(buf * BN + cg * WARP_COLS + c * 32);
         if constexpr (EPI == EPI_QKV_ROPE) {
           if (c == 0 && p.qk_norm && m_warp < p.M && n_warp0 < p.rope_cols && n_warp0 < p.N) {
-            float ss[NSUB];
-#pragma unroll
-            for (int cc = 0; cc < NSUB; ++cc) {
-              float acc = 0.f;
-              float bl = 0.f;
-              if (p.bias != nullptr && n_warp0 + 32 * cc + lane < p.N)
-                bl = __ldg(p.bias + n_warp0 + 32 * cc + lane);
-#pragma unroll
-              for (int g = 0; g < 2; ++g) {
-                uint32_t r[16];
-                tmem_ld_32x16(taddr + 32 * cc + 16 * g, r);
-                tmem_ld_wait();
-                const int nb0 = n_warp0 + 32 * cc + 16 * g;
-                if (p.bias != nullptr && nb0 + 16 <= p.N) {
-#pragma unroll
-                  for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + nb0) + q4);
-                    const float x0 = __uint_as_float(r[4 * q4]) + b4.x;
-                    const float x1 = __uint_as_float(r[4 * q4 + 1]) + b4.y;
-                    const float x2 = __uint_as_float(r[4 * q4 + 2]) + b4.z;
-                    const float x3 = __uint_as_float(r[4 * q4 + 3]) + b4.w;
-                    acc += x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3;
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) {
-                    const float x = __uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bl, 16 * g + j);
-                    acc += x * x;
-                  }
-                }
-              }
-              ss[cc] = acc;
-            }
-            if (p.head_dim == 64 && NSUB == 2) {
-              qk_scale[0] = rsqrtf((ss[0] + ss[NSUB - 1]) * (1.0f / 64.0f) + p.qk_eps);
-              qk_scale[NSUB - 1] = qk_scale[0];
-            } else {
-#pragma unroll
-              for (int cc = 0; cc < NSUB; ++cc)
-                qk_scale[cc] = rsqrtf(ss[cc] * (1.0f / 32.0f) + p.qk_eps);
-            }
+            // (out of line: most models run without the q/k norm)
+            const float2 sc = gemm_qk_norm_scales<NSUB>(taddr, p.bias, n_warp0, p.N, lane, p.head_dim,
+                                                        p.qk_eps);
+            qk_scale[0] = sc.x;
+            qk_scale[NSUB - 1] = sc.y;
           }
         }
         if constexpr (HAS_AUX) {
           if (chunk_live) {
-            if (!mbar_wait(aux_bar(e), aux_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
+            if (!gemm_wait(aux_bar(e), aux_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) {
               ok = false;
               break;
             }
