@@ -10,78 +10,63 @@
 
 namespace strata {
 
-// VEC_PER_LANE: number of 8-element (16-byte) vectors each lane holds of a row; ROWS: rows a
-// warp works on at once (their loads are all issued before the first reduction, which keeps
-// more bytes in flight per warp than the row-by-row loop did).
-template <int VEC_PER_LANE, int ROWS>
+template <int VEC_PER_LANE>  // number of 8-element (16-byte) vectors each lane holds
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                       __nv_bfloat16* __restrict__ y, long long ldy, int M, int C, float eps) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = C >> 3;
-  const long long stride = static_cast<long long>(gridDim.x) * warps_per_block;
-  for (long long row0 = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
-       row0 < M; row0 += stride * ROWS) {
-    float v[ROWS][VEC_PER_LANE][8];
-    float sum[ROWS];
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+       row < M; row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const uint4* xp = reinterpret_cast<const uint4*>(x + row * ldx);
+    float v[VEC_PER_LANE][8];
+    float sum = 0.f;
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const long long row = row0 + r * stride;
-      sum[r] = 0.f;
-      const uint4* xp = reinterpret_cast<const uint4*>(x + (row < M ? row : row0) * ldx);
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int vi = lane + 32 * i;
+      if (vi < nvec) {
+        uint4 r = __ldg(xp + vi);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-      for (int i = 0; i < VEC_PER_LANE; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) {
-          uint4 q = __ldg(xp + vi);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        for (int t = 0; t < 4; ++t) {
+          v[i][2 * t] = bf16_lo(w[t]);
+          v[i][2 * t + 1] = bf16_hi(w[t]);
+          sum += v[i][2 * t] + v[i][2 * t + 1];
+        }
+      } else {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            v[r][i][2 * t] = bf16_lo(w[t]);
-            v[r][i][2 * t + 1] = bf16_hi(w[t]);
-            sum[r] += v[r][i][2 * t] + v[r][i][2 * t + 1];
-          }
-        } else {
+        for (int t = 0; t < 8; ++t) v[i][t] = 0.f;
+      }
+    }
 #pragma unroll
-          for (int t = 0; t < 8; ++t) v[r][i][t] = 0.f;
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / static_cast<float>(C);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      if (lane + 32 * i < nvec) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float d = v[i][t] - mean;
+          sq += d * d;
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const long long row = row0 + r * stride;
-      float s1 = sum[r];
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / static_cast<float>(C) + eps);
+    uint4* yp = reinterpret_cast<uint4*>(y + row * ldy);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      const float mean = s1 / static_cast<float>(C);
-      float sq = 0.f;
-#pragma unroll
-      for (int i = 0; i < VEC_PER_LANE; ++i) {
-        if (lane + 32 * i < nvec) {
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            const float d = v[r][i][t] - mean;
-            sq += d * d;
-          }
-        }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      const float rstd = rsqrtf(sq / static_cast<float>(C) + eps);
-      if (row >= M) continue;
-      uint4* yp = reinterpret_cast<uint4*>(y + row * ldy);
-#pragma unroll
-      for (int i = 0; i < VEC_PER_LANE; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) {
-          uint4 o;
-          o.x = pack_bf16((v[r][i][0] - mean) * rstd, (v[r][i][1] - mean) * rstd);
-          o.y = pack_bf16((v[r][i][2] - mean) * rstd, (v[r][i][3] - mean) * rstd);
-          o.z = pack_bf16((v[r][i][4] - mean) * rstd, (v[r][i][5] - mean) * rstd);
-          o.w = pack_bf16((v[r][i][6] - mean) * rstd, (v[r][i][7] - mean) * rstd);
-          yp[vi] = o;
-        }
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int vi = lane + 32 * i;
+      if (vi < nvec) {
+        uint4 o;
+        o.x = pack_bf16((v[i][0] - mean) * rstd, (v[i][1] - mean) * rstd);
+        o.y = pack_bf16((v[i][2] - mean) * rstd, (v[i][3] - mean) * rstd);
+        o.z = pack_bf16((v[i][4] - mean) * rstd, (v[i][5] - mean) * rstd);
+        o.w = pack_bf16((v[i][6] - mean) * rstd, (v[i][7] - mean) * rstd);
+        yp[vi] = o;
       }
     }
   }
@@ -100,10 +85,10 @@ inline int launch_layernorm(const __nv_bfloat16* x, long long ldx, __nv_bfloat16
   const int nvec = C / 8;
   const int vpl = (nvec + 31) / 32;
   const int g = static_cast<int>(blocks);
-  if (vpl <= 1) layernorm_rows_kernel<1, 4><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
-  else if (vpl <= 2) layernorm_rows_kernel<2, 2><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
-  else if (vpl <= 4) layernorm_rows_kernel<4, 1><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
-  else layernorm_rows_kernel<8, 1><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
+  if (vpl <= 1) layernorm_rows_kernel<1><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
+  else if (vpl <= 2) layernorm_rows_kernel<2><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
+  else if (vpl <= 4) layernorm_rows_kernel<4><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
+  else layernorm_rows_kernel<8><<<g, threads, 0, stream>>>(x, ldx, y, ldy, M, C, eps);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
