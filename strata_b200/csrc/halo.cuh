@@ -7,7 +7,9 @@
 // remainder the cell's offset inside that rank's tile buffer, so the source may sit in this
 // GPU's memory or in a peer's (plain loads over NVLink through a peer-mapped pointer; no TMA,
 // no multicast). Face-edge rotation and the corner rule are entirely in the map, so the
-// kernel's result is bit-identical to applying the same index logic on the host.
+// kernel's result is bit-identical to applying the same index logic on the host (copies
+// always; the two-cell mean and the weighted sums of the other kernels of this file for
+// normal-range values - the library is built with flush-to-zero).
 //
 // Mean of two cells: (a + b) / 2 evaluated in the storage type's own arithmetic (fp32: one
 // add, one halving; bf16: the sum is rounded to bf16, then halved - what a bf16 tensor
@@ -156,7 +158,8 @@ halo_gather_knn_fields_kernel(float* __restrict__ out, const PeerPtrs src,
 //     out[l, c] = ( sum_j coef_j * (window[p_j] * y[l, p_j]) ) / weights[c]
 // with entries offsets[c]..offsets[c+1] sorted by padded cell id. Pull form: no atomics, a
 // fixed summation order, every product and sum rounded separately (no fused multiply-add), so
-// the result is bit-identical to the same loop on the host.
+// the result is bit-identical to the same loop on the host for normal-range values (the library
+// is built with flush-to-zero, so a denormal operand or result is zero here and not there).
 // Padded sources: [L, tiles_per_rank*P*P] fp32 per rank; out [L, tiles_per_rank*T*T].
 __global__ void __launch_bounds__(256)
 halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
