@@ -167,10 +167,11 @@ halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
                            const float* __restrict__ coef, const float* __restrict__ window,
                            const float* __restrict__ weights, int n_cells,
                            int padded_cells_per_rank, int PP, int L) {
+  const bool failed = halo_exchange_failed();
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n_cells; c += gridDim.x * blockDim.x) {
     const int e0 = __ldg(offsets + c), e1 = __ldg(offsets + c + 1);
     // (after a failed barrier the divisor is NaN, and with it every output)
-    const float wsum = halo_exchange_failed() ? __int_as_float(0x7fc00000) : __ldg(weights + c);
+    const float wsum = failed ? __int_as_float(0x7fc00000) : __ldg(weights + c);
     // with the copy halo's coefficients (1 or 1/2) coef * (window * y) == (coef * window) * y bit
     // for bit, so the per-entry factor and source pointer are set up once, outside the loop over
     // the leading index (general coefficients - the k-nearest-neighbour lists - agree with the
@@ -261,6 +262,7 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
   // 64 threads share a halo cell: its decoding and the source rows are worked out once per
   // cell, each thread then moves every 64th 16-byte vector of the cell's k|v channels
   const int sub = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
+  const bool failed = halo_exchange_failed();   // (read once: a volatile load per store halves the copy rate)
   const int cells_per_iter = blockDim.x >> 6;
   for (int hc = blockIdx.x * cells_per_iter + sub; hc < n_halo; hc += gridDim.x * cells_per_iter) {
     int pi, pj;
@@ -291,11 +293,10 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
     const __nv_bfloat16* row_b = b >= 0 ? source_row(b) : nullptr;
     const long long tab_row = (static_cast<long long>(tile) * PP + pc) * half;
     __nv_bfloat16* out_row = qkv + ((static_cast<long long>(tile) * D + d) * PP + pc) * ld + C;
-    auto rotate = [&](const uint4& x, const uint32_t* tab, int v, float (&o)[8]) {
+    // x: eight bf16 of the source row; t4: the four (cos, sin) pairs of a K vector
+    auto rotate = [&](const uint4& x, const uint4& t4, bool is_k, float (&o)[8]) {
       const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-      if (v < kvec) {
-        const int p0 = (((v << 3) % head_dim) >> 1);   // first channel pair of this vector
-        const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(tab + tab_row + p0));
+      if (is_k) {
         const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -312,22 +313,45 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
         }
       }
     };
-    for (int v = lane64; v < vpc; v += 64) {
-      float ra[8];
-      rotate(*reinterpret_cast<const uint4*>(row_a + (v << 3)), dcs_a, v, ra);
-      if (row_b != nullptr) {
-        float rb[8];
-        rotate(*reinterpret_cast<const uint4*>(row_b + (v << 3)), dcs_b, v, rb);
+    auto table = [&](const uint32_t* tab, int v) {   // first channel pair of vector v: ((8v) % head_dim) / 2
+      return __ldg(reinterpret_cast<const uint4*>(tab + tab_row + (((v << 3) % head_dim) >> 1)));
+    };
+    // four vectors per thread and pass, all loads issued before the first use: the copy is
+    // bound by the bytes a thread keeps in flight
+    constexpr int UNROLL = 4;
+    for (int v0 = lane64; v0 < vpc; v0 += 64 * UNROLL) {
+      uint4 xa[UNROLL], ta[UNROLL];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+      for (int u = 0; u < UNROLL; ++u) {
+        const int v = v0 + 64 * u;
+        if (v < vpc) {
+          xa[u] = *reinterpret_cast<const uint4*>(row_a + (v << 3));
+          if (v < kvec) ta[u] = table(dcs_a, v);
+        }
       }
-      uint4 o4;
-      o4.x = pack_bf16(ra[0], ra[1]);
-      o4.y = pack_bf16(ra[2], ra[3]);
-      o4.z = pack_bf16(ra[4], ra[5]);
-      o4.w = pack_bf16(ra[6], ra[7]);
-      if (halo_exchange_failed()) o4 = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
-      *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int v = v0 + 64 * u;
+        if (v >= vpc) continue;
+        float ra[8];
+        rotate(xa[u], ta[u], v < kvec, ra);
+        if (row_b != nullptr) {   // corner diagonal: the mean of two individually rotated sources
+          float rb[8];
+          const uint4 xb = *reinterpret_cast<const uint4*>(row_b + (v << 3));
+          uint4 tb = make_uint4(0u, 0u, 0u, 0u);
+          if (v < kvec) tb = table(dcs_b, v);
+          rotate(xb, tb, v < kvec, rb);
+#pragma unroll
+          for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+        }
+        uint4 o4;
+        o4.x = pack_bf16(ra[0], ra[1]);
+        o4.y = pack_bf16(ra[2], ra[3]);
+        o4.z = pack_bf16(ra[4], ra[5]);
+        o4.w = pack_bf16(ra[6], ra[7]);
+        if (failed) o4 = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
+        *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
+      }
     }
   }
 }
