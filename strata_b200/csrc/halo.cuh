@@ -110,7 +110,22 @@ halo_gather_fields_kernel(float* __restrict__ out, const PeerPtrs src,
       const int rb = b / cells_per_rank, lb = b - rb * cells_per_rank;
       pb = static_cast<const float*>(src.p[rb]) + lb;
     }
-    for (int l = blockIdx.y; l < L; l += gridDim.y) {
+    constexpr int UL = 4;   // leading indices in flight per thread (independent loads)
+    int l = blockIdx.y;
+    for (; l + (UL - 1) * static_cast<int>(gridDim.y) < L; l += UL * gridDim.y) {
+      float v[UL];
+#pragma unroll
+      for (int u = 0; u < UL; ++u) {
+        const long long so = static_cast<long long>(l + u * gridDim.y) * cells_per_rank;
+        v[u] = pa[so];
+        if (pb) v[u] = (v[u] + pb[so]) / 2.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < UL; ++u)
+        out[static_cast<long long>(l + u * gridDim.y) * n_out_cells + oc] =
+            failed ? __int_as_float(0x7fc00000) : v[u];
+    }
+    for (; l < L; l += gridDim.y) {
       const long long so = static_cast<long long>(l) * cells_per_rank;
       float v = pa[so];
       if (pb) v = (v + pb[so]) / 2.0f;
