@@ -186,6 +186,30 @@ def test_na3d_score_jump_beyond_fp32_range(ops, kernel, shape):
     assert rel_max_err(o, ref) < TOL_BF16
 
 
+def test_na3d_score_jump_in_a_late_item_of_a_long_launch(ops):
+    # The same fallback when the CTA has more than 64 work items (it remembers its first 64
+    # items one by one and later ones as a group): 20000 query tiles over 296 CTAs, the hot keys
+    # in the last planes. Checked against the oracle on a crop that holds the complete windows
+    # of the compared queries (the crop's upper depth border is the tensor's own).
+    D, H, W, kernel = 64, 200, 200, (3, 9, 9)
+    g = torch.Generator(device="cuda").manual_seed(79)
+    q = (torch.randn(1, D, H, W, 1, 64, generator=g, device="cuda") * 3).bfloat16()
+    k = torch.randn(1, D, H, W, 1, 64, generator=g, device="cuda").bfloat16()
+    v = torch.randn(1, D, H, W, 1, 64, generator=g, device="cuda").bfloat16()
+    d0, d1, h0, h1, w0, w1 = 56, 64, 80, 120, 80, 120
+    hot = torch.rand(1, 3, 20, 20, 1, 1, generator=g, device="cuda") < 0.02
+    k[:, 60:63, 90:110, 90:110] = torch.where(hot, k[:, 60:63, 90:110, 90:110] * 200.0,
+                                              k[:, 60:63, 90:110, 90:110])
+    o = ops.na3d(q, k, v, kernel)
+    assert _status() == 0
+    assert torch.isfinite(o).all()
+    crop = lambda t: t[:, d0:d1, h0:h1, w0:w1].float().cpu()
+    ref = bo.na3d(crop(q), crop(k), crop(v), kernel)
+    # queries at least half a window away from the crop's artificial borders
+    sel = (slice(None), slice(2, None), slice(4, -4), slice(4, -4))
+    assert rel_max_err(crop(o)[sel], ref[sel]) < TOL_BF16
+
+
 def test_na3d_packed_qkv_views_and_unwritten_cells(ops):
     B, D, H, W, nh = 2, 4, 16, 16, 2
     g = torch.Generator().manual_seed(5)
