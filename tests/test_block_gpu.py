@@ -7,6 +7,7 @@ bf16 at the same points as the GPU path with fp32 accumulation on both sides; th
 of that comparison is bounded too (one bf16 ulp of the largest value = 2^-8, i.e. 4e-3 relative,
 doubled for values that round the other way) and printed with the RMS.
 """
+import numpy as np
 import pytest
 import torch
 
@@ -208,6 +209,37 @@ def test_na3d_score_jump_in_a_late_item_of_a_long_launch(ops):
     # queries at least half a window away from the crop's artificial borders
     sel = (slice(None), slice(2, None), slice(4, -4), slice(4, -4))
     assert rel_max_err(crop(o)[sel], ref[sel]) < TOL_BF16
+
+
+def _random_na_cases(n, seed):
+    rng = np.random.default_rng(seed)
+    cases = []
+    while len(cases) < n:
+        kd, kh, kw = (int(rng.choice([1, 3, 5])), int(rng.choice([1, 3, 5, 7, 9, 11, 13, 15])),
+                      int(rng.choice([1, 3, 5, 7, 9, 11, 13, 15])))
+        D = int(rng.integers(kd, kd + 6))
+        H = int(rng.integers(kh, kh + 14))
+        W = int(rng.integers(kw, kw + 14))
+        if (D + kd) * ((8 + kh + 2) // 4) > 128:      # key box beyond the kernel's unit table
+            continue
+        cases.append((1, D, H, W, int(rng.integers(1, 3)), (kd, kh, kw)))
+    return cases
+
+
+@pytest.mark.parametrize("B,D,H,W,nh,kernel", _random_na_cases(24, 2024))
+def test_na3d_random_shapes(ops, B, D, H, W, nh, kernel):
+    # seeded random tensor extents and window sizes (odd tile overhangs on every axis, windows
+    # as large as the axis, every query-tile width); half of the cases with a score scale that
+    # makes the running reference move
+    g = torch.Generator().manual_seed(D * 10000 + H * 100 + W)
+    scale = 4.0 if (D + H + W) % 2 else 1.0
+    q = (torch.randn(B, D, H, W, nh, 64, generator=g) * scale).bfloat16()
+    k = (torch.randn(B, D, H, W, nh, 64, generator=g) * scale).bfloat16()
+    v = torch.randn(B, D, H, W, nh, 64, generator=g).bfloat16()
+    o = ops.na3d(q.cuda(), k.cuda(), v.cuda(), kernel)
+    assert _status() == 0
+    ref = bo.na3d(q.float(), k.float(), v.float(), kernel)
+    assert rel_max_err(o, ref) < TOL_BF16
 
 
 def test_na3d_packed_qkv_views_and_unwritten_cells(ops):
