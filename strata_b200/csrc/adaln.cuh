@@ -353,6 +353,23 @@ __device__ __forceinline__ void cond_stencil(const float4* tb, int stride, const
   }
 }
 
+// The same with the 3 x 3 tokens already unpacked to fp32 (once per cell instead of once per
+// pixel) and the bias in registers.
+__device__ __forceinline__ void cond_stencil_f(const float4* tb, int stride, const float (&t)[9][8],
+                                               const float (&bias)[8], float (&acc)[8]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = bias[c];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) {
+    const float4 w0 = tb[k * stride];
+    const float4 w1 = tb[k * stride + 1];
+    acc[0] = fmaf(w0.x, t[k][0], acc[0]); acc[1] = fmaf(w0.y, t[k][1], acc[1]);
+    acc[2] = fmaf(w0.z, t[k][2], acc[2]); acc[3] = fmaf(w0.w, t[k][3], acc[3]);
+    acc[4] = fmaf(w1.x, t[k][4], acc[4]); acc[5] = fmaf(w1.y, t[k][5], acc[5]);
+    acc[6] = fmaf(w1.z, t[k][6], acc[6]); acc[7] = fmaf(w1.w, t[k][7], acc[7]);
+  }
+}
+
 // One thread: one cell (factor x factor pixels of one backbone token) x 8 channels. A warp
 // holds 8 consecutive cells x 4 consecutive channel vectors (32 channels), so a token read and
 // a row write are 64 contiguous bytes per cell. A block works on 256 consecutive cells of one
@@ -428,6 +445,20 @@ adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table
 #pragma unroll
       for (int k = 0; k < 9; ++k)
         tk[k] = __ldg(base + (static_cast<long long>(rb + k / 3) * p.w + (cb + k % 3)) * nvec);
+      float tf[9][8], bias[8];
+      if constexpr (!BORDER) {   // interior cells: tokens and bias to fp32 once per cell
+#pragma unroll
+        for (int k = 0; k < 9; ++k) unpack8(tk[k], tf[k]);
+        if (p.bdw != nullptr) {
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bdw) + cv * 2);
+          const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bdw) + cv * 2 + 1);
+          bias[0] = b0.x; bias[1] = b0.y; bias[2] = b0.z; bias[3] = b0.w;
+          bias[4] = b1.x; bias[5] = b1.y; bias[6] = b1.z; bias[7] = b1.w;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) bias[c] = 0.f;
+        }
+      }
       for (int phy = 0; phy < f; ++phy) {
         const int y = R * f + phy;
         for (int phx = 0; phx < f; ++phx) {
@@ -436,8 +467,8 @@ adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table
           if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
           float acc[8];
           if constexpr (!BORDER) {
-            cond_stencil(reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + (lane & 3) * 2,
-                         8, tk, p.bdw, cv, acc);
+            cond_stencil_f(reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + (lane & 3) * 2,
+                           8, tf, bias, acc);
           } else {
             const long long cls = static_cast<long long>(ycls0 + phy) * ncls + (xcls0 + phx);
             cond_stencil(reinterpret_cast<const float4*>(table + cls * 9 * p.Cb) + cv * 2, p.Cb >> 2,
