@@ -353,40 +353,16 @@ __device__ __forceinline__ void cond_stencil(const float4* tb, int stride, const
   }
 }
 
-// The same with the 3 x 3 tokens already unpacked to fp32 (once per cell instead of once per
-// pixel) and the bias in registers.
-__device__ __forceinline__ void cond_stencil_f(const float4* tb, int stride, const float (&t)[9][8],
-                                               const float (&bias)[8], float (&acc)[8]) {
-#pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = bias[c];
-#pragma unroll
-  for (int k = 0; k < 9; ++k) {
-    const float4 w0 = tb[k * stride];
-    const float4 w1 = tb[k * stride + 1];
-    acc[0] = fmaf(w0.x, t[k][0], acc[0]); acc[1] = fmaf(w0.y, t[k][1], acc[1]);
-    acc[2] = fmaf(w0.z, t[k][2], acc[2]); acc[3] = fmaf(w0.w, t[k][3], acc[3]);
-    acc[4] = fmaf(w1.x, t[k][4], acc[4]); acc[5] = fmaf(w1.y, t[k][5], acc[5]);
-    acc[6] = fmaf(w1.z, t[k][6], acc[6]); acc[7] = fmaf(w1.w, t[k][7], acc[7]);
-  }
-}
+// Cells of the outermost ring of every plane (first / last cell classes of the table), enumerated
+// densely. One thread: one cell (factor x factor pixels of one backbone token) x 8 channels; a
+// warp holds 8 consecutive ring cells x 4 consecutive channel vectors (32 channels). The ring is
+// 6 % of the cells of a 64 x 64 plane: its table entries are read from global memory (L2) and a
+// block takes only 64 cells, so that the few cells still spread over every SM.
+constexpr int COND_CELLS_PER_ITEM = 256;   // interior kernel: cells a block walks per slab load
+constexpr int COND_BORDER_CELLS_PER_ITEM = 64;
 
-// One thread: one cell (factor x factor pixels of one backbone token) x 8 channels. A warp
-// holds 8 consecutive cells x 4 consecutive channel vectors (32 channels), so a token read and
-// a row write are 64 contiguous bytes per cell. A block works on 256 consecutive cells of one
-// 32-channel group at a time and keeps the interior-phase slab of that group's table
-// ([factor^2][9][32] fp32) in shared memory; the cells on the image border (a launch of their
-// own) read their classes' entries from global memory.
-constexpr int COND_CELLS_PER_ITEM = 256;
-
-#ifndef COND_CELLS_MIN_BLOCKS
-#define COND_CELLS_MIN_BLOCKS 2
-#endif
-// BORDER = false: interior cells (the others are skipped); BORDER = true: the cells of the
-// outermost ring of every plane, enumerated densely so that a warp does not mix the two paths.
-template <bool BORDER>
-__global__ void __launch_bounds__(256, COND_CELLS_MIN_BLOCKS)
-adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table) {
-  extern __shared__ __align__(16) float slab[];
+__global__ void __launch_bounds__(256, 2)
+adaln_cond_border_kernel(const AdalnCondParams p, const float* __restrict__ table) {
   const int nvec = p.Cb >> 3;
   const int ncvg = nvec >> 2;
   const int f = p.factor;
@@ -396,86 +372,154 @@ adaln_cond_cells_kernel(const AdalnCondParams p, const float* __restrict__ table
   const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
   const long long ring = 2LL * p.w + 2LL * (p.h - 2);        // border cells of one plane
   const long long plane0 = gR0 / p.h;
-  const long long n_cells = BORDER ? (gR1 / p.h - plane0 + 1) * ring : (gR1 - gR0 + 1) * p.w;
+  const long long n_cells = (gR1 / p.h - plane0 + 1) * ring;
+  const long long n_chunks = (n_cells + COND_BORDER_CELLS_PER_ITEM - 1) / COND_BORDER_CELLS_PER_ITEM;
+  const long long n_items = n_chunks * ncvg;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (long long item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int cvg = static_cast<int>(item / n_chunks);
+    const long long cell = (item % n_chunks) * COND_BORDER_CELLS_PER_ITEM + warp * 8 + (lane >> 2);
+    if (cell >= n_cells) continue;
+    const int cv = cvg * 4 + (lane & 3);
+    const long long plane = plane0 + cell / ring;
+    long long k = cell % ring;
+    int R, Cc;
+    if (k < p.w) { R = 0; Cc = static_cast<int>(k); }
+    else if (k < 2LL * p.w) { R = p.h - 1; Cc = static_cast<int>(k - p.w); }
+    else { k -= 2LL * p.w; R = 1 + static_cast<int>(k >> 1); Cc = (k & 1) ? p.w - 1 : 0; }
+    const int rb = R == 0 ? 0 : (R == p.h - 1 ? p.h - 3 : R - 1);
+    const int cb = Cc == 0 ? 0 : (Cc == p.w - 1 ? p.w - 3 : Cc - 1);
+    const int ycls0 = R == 0 ? 0 : (R == p.h - 1 ? 2 * f : f);
+    const int xcls0 = Cc == 0 ? 0 : (Cc == p.w - 1 ? 2 * f : f);
+    const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
+    uint4 tk[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t)
+      tk[t] = __ldg(base + (static_cast<long long>(rb + t / 3) * p.w + (cb + t % 3)) * nvec);
+    for (int phy = 0; phy < f; ++phy) {
+      const int y = R * f + phy;
+      for (int phx = 0; phx < f; ++phx) {
+        const int x = Cc * f + phx;
+        const long long pix = (plane * H + y) * W + x;
+        if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
+        float acc[8];
+        const long long cls = static_cast<long long>(ycls0 + phy) * ncls + (xcls0 + phx);
+        cond_stencil(reinterpret_cast<const float4*>(table + cls * 9 * p.Cb) + cv * 2, p.Cb >> 2,
+                     tk, p.bdw, cv, acc);
+        gelu8(acc);
+        reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
+      }
+    }
+  }
+}
+
+// Interior cells, second layout: one thread = TWO neighbouring cells x 4 channels. The table
+// entries of a phase (read from the shared-memory slab) serve both cells, which halves the
+// shared-memory reads per output - the interior kernel is paced by those reads and by
+// instruction issue in about equal parts. A warp holds 4 cell pairs x 8 channel quads (32
+// channels): a token read and a row write are still 64 contiguous bytes per cell.
+__global__ void __launch_bounds__(256, 2)
+adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ table) {
+  extern __shared__ __align__(16) float slab[];
+  const int ncvg = p.Cb >> 5;
+  const int f = p.factor;
+  const int ncls = 3 * f;
+  const int H = p.h * f, W = p.w * f;
+  const long long gR0 = p.row0 / W / f;
+  const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
+  const long long n_cells = (gR1 - gR0 + 1) * p.w;
   const long long n_chunks = (n_cells + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM;
   const long long n_items = n_chunks * ncvg;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int cq = lane & 7;
   const int slab_vec = f * f * 9 * 8;                      // float4 count of a slab
   for (long long item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int cvg = static_cast<int>(item / n_chunks);
     const long long cell0 = (item % n_chunks) * COND_CELLS_PER_ITEM;
-    if constexpr (!BORDER) {
-      __syncthreads();                                     // previous item's readers are done
-      for (int v = threadIdx.x; v < slab_vec; v += blockDim.x) {
-        const int e = v >> 3;                              // (phase, k)
-        const int phase = e / 9, k = e - phase * 9;
-        const int cls = (f + phase / f) * ncls + (f + phase % f);
-        reinterpret_cast<float4*>(slab)[v] = __ldg(
-            reinterpret_cast<const float4*>(table + (static_cast<long long>(cls) * 9 + k) * p.Cb +
-                                            cvg * 32) + (v & 7));
-      }
-      __syncthreads();
+    __syncthreads();                                       // previous item's readers are done
+    for (int v = threadIdx.x; v < slab_vec; v += blockDim.x) {
+      const int e = v >> 3;                                // (phase, k)
+      const int phase = e / 9, k = e - phase * 9;
+      const int cls = (f + phase / f) * ncls + (f + phase % f);
+      reinterpret_cast<float4*>(slab)[v] = __ldg(
+          reinterpret_cast<const float4*>(table + (static_cast<long long>(cls) * 9 + k) * p.Cb +
+                                          cvg * 32) + (v & 7));
     }
-    const int cv = cvg * 4 + (lane & 3);
+    __syncthreads();
+    const int ch0 = cvg * 32 + 4 * cq;
+    float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.bdw != nullptr) bias = __ldg(reinterpret_cast<const float4*>(p.bdw + ch0));
     for (int pass = 0; pass < COND_CELLS_PER_ITEM / 64; ++pass) {
-      const long long cell = cell0 + pass * 64 + warp * 8 + (lane >> 2);
-      if (cell >= n_cells) continue;
-      long long plane;
-      int R, Cc;
-      if constexpr (BORDER) {
-        plane = plane0 + cell / ring;
-        long long k = cell % ring;
-        if (k < p.w) { R = 0; Cc = static_cast<int>(k); }
-        else if (k < 2LL * p.w) { R = p.h - 1; Cc = static_cast<int>(k - p.w); }
-        else { k -= 2LL * p.w; R = 1 + static_cast<int>(k >> 1); Cc = (k & 1) ? p.w - 1 : 0; }
-      } else {
+      float ta[9][4], tb[9][4];
+      long long pix_a = -1, pix_b = -1;     // first pixel of each cell; -1: the cell is skipped
+#pragma unroll
+      for (int s2 = 0; s2 < 2; ++s2) {
+        const long long cell = cell0 + pass * 64 + warp * 8 + 2 * (lane >> 3) + s2;
+        if (cell >= n_cells) continue;
         const long long gR = gR0 + cell / p.w;
-        Cc = static_cast<int>(cell % p.w);
-        plane = gR / p.h;
-        R = static_cast<int>(gR % p.h);
+        const int Cc = static_cast<int>(cell % p.w);
+        const long long plane = gR / p.h;
+        const int R = static_cast<int>(gR % p.h);
         if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
-      }
-      const int rb = R == 0 ? 0 : (R == p.h - 1 ? p.h - 3 : R - 1);
-      const int cb = Cc == 0 ? 0 : (Cc == p.w - 1 ? p.w - 3 : Cc - 1);
-      const int ycls0 = R == 0 ? 0 : (R == p.h - 1 ? 2 * f : f);
-      const int xcls0 = Cc == 0 ? 0 : (Cc == p.w - 1 ? 2 * f : f);
-      const uint4* base = reinterpret_cast<const uint4*>(p.tok + plane * p.h * p.w * p.Cb) + cv;
-      uint4 tk[9];
+        const __nv_bfloat16* base = p.tok + plane * p.h * p.w * p.Cb + ch0;
 #pragma unroll
-      for (int k = 0; k < 9; ++k)
-        tk[k] = __ldg(base + (static_cast<long long>(rb + k / 3) * p.w + (cb + k % 3)) * nvec);
-      float tf[9][8], bias[8];
-      if constexpr (!BORDER) {   // interior cells: tokens and bias to fp32 once per cell
-#pragma unroll
-        for (int k = 0; k < 9; ++k) unpack8(tk[k], tf[k]);
-        if (p.bdw != nullptr) {
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bdw) + cv * 2);
-          const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bdw) + cv * 2 + 1);
-          bias[0] = b0.x; bias[1] = b0.y; bias[2] = b0.z; bias[3] = b0.w;
-          bias[4] = b1.x; bias[5] = b1.y; bias[6] = b1.z; bias[7] = b1.w;
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) bias[c] = 0.f;
+        for (int k = 0; k < 9; ++k) {
+          const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(
+              base + (static_cast<long long>(R - 1 + k / 3) * p.w + (Cc - 1 + k % 3)) * p.Cb));
+          if (s2 == 0) {
+            ta[k][0] = bf16_lo(t2.x); ta[k][1] = bf16_hi(t2.x); ta[k][2] = bf16_lo(t2.y); ta[k][3] = bf16_hi(t2.y);
+          } else {
+            tb[k][0] = bf16_lo(t2.x); tb[k][1] = bf16_hi(t2.x); tb[k][2] = bf16_lo(t2.y); tb[k][3] = bf16_hi(t2.y);
+          }
         }
+        const long long pix0 = (plane * H + static_cast<long long>(R) * f) * W + static_cast<long long>(Cc) * f;
+        if (s2 == 0) pix_a = pix0; else pix_b = pix0;
+      }
+      if (pix_a < 0 && pix_b < 0) continue;
+      if (pix_a < 0) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) ta[k][c] = 0.f;
+      }
+      if (pix_b < 0) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tb[k][c] = 0.f;
       }
       for (int phy = 0; phy < f; ++phy) {
-        const int y = R * f + phy;
         for (int phx = 0; phx < f; ++phx) {
-          const int x = Cc * f + phx;
-          const long long pix = (plane * H + y) * W + x;
-          if (pix < p.row0 || pix >= p.row0 + p.n_rows) continue;
-          float acc[8];
-          if constexpr (!BORDER) {
-            cond_stencil_f(reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + (lane & 3) * 2,
-                           8, tf, bias, acc);
-          } else {
-            const long long cls = static_cast<long long>(ycls0 + phy) * ncls + (xcls0 + phx);
-            cond_stencil(reinterpret_cast<const float4*>(table + cls * 9 * p.Cb) + cv * 2, p.Cb >> 2,
-                         tk, p.bdw, cv, acc);
+          const float4* wv = reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + cq;
+          float a[4] = {bias.x, bias.y, bias.z, bias.w};
+          float b[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+          for (int k = 0; k < 9; ++k) {
+            const float4 w4 = wv[k * 8];
+            a[0] = fmaf(w4.x, ta[k][0], a[0]); a[1] = fmaf(w4.y, ta[k][1], a[1]);
+            a[2] = fmaf(w4.z, ta[k][2], a[2]); a[3] = fmaf(w4.w, ta[k][3], a[3]);
+            b[0] = fmaf(w4.x, tb[k][0], b[0]); b[1] = fmaf(w4.y, tb[k][1], b[1]);
+            b[2] = fmaf(w4.z, tb[k][2], b[2]); b[3] = fmaf(w4.w, tb[k][3], b[3]);
           }
-          gelu8(acc);
-          reinterpret_cast<uint4*>(p.out + (pix - p.row0) * p.Cb)[cv] = pack8(acc);
+          const long long off = static_cast<long long>(phy) * W + phx;
+          auto finish = [&](float (&v)[4], long long pix0) {
+            const long long pix = pix0 + off;
+            if (pix0 < 0 || pix < p.row0 || pix >= p.row0 + p.n_rows) return;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float x = v[c];
+              const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+              v[c] = 0.5f * x * (1.0f + fast_tanh(u));
+            }
+            uint2 o;
+            o.x = pack_bf16(v[0], v[1]);
+            o.y = pack_bf16(v[2], v[3]);
+            *reinterpret_cast<uint2*>(p.out + (pix - p.row0) * p.Cb + ch0) = o;
+          };
+          finish(a, pix_a);
+          finish(b, pix_b);
         }
       }
     }
@@ -509,18 +553,18 @@ inline int launch_adaln_cond(const AdalnCondParams& p, float* table, int sm_coun
     if (blocks > cap) blocks = cap;
     const int slab_bytes = p.factor * p.factor * 9 * 32 * 4;
     if (slab_bytes > 48 * 1024) {
-      cudaError_t ea = cudaFuncSetAttribute(adaln_cond_cells_kernel<false>,
+      cudaError_t ea = cudaFuncSetAttribute(adaln_cond_interior_kernel,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, slab_bytes);
       if (ea != cudaSuccess) return -static_cast<int>(ea) - 1000;
     }
-    adaln_cond_cells_kernel<false><<<static_cast<int>(blocks), 256, slab_bytes, stream>>>(p, table);
+    adaln_cond_interior_kernel<<<static_cast<int>(blocks), 256, slab_bytes, stream>>>(p, table);
     {
       const long long H = static_cast<long long>(p.h) * p.factor;
       const long long planes = (p.row0 + p.n_rows - 1) / (H * W) - p.row0 / (H * W) + 1;
       const long long ring = 2LL * p.w + 2LL * (p.h - 2);
-      long long bb = (planes * ring + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM * (p.Cb / 32);
+      long long bb = (planes * ring + COND_BORDER_CELLS_PER_ITEM - 1) / COND_BORDER_CELLS_PER_ITEM * (p.Cb / 32);
       if (bb > cap) bb = cap;
-      adaln_cond_cells_kernel<true><<<static_cast<int>(bb), 256, 0, stream>>>(p, table);
+      adaln_cond_border_kernel<<<static_cast<int>(bb), 256, 0, stream>>>(p, table);
     }
   } else {
     const long long total = p.n_rows * (p.Cb / 8);
