@@ -353,11 +353,9 @@ __device__ __forceinline__ void cond_stencil(const float4* tb, int stride, const
   }
 }
 
-// Cells of the outermost ring of every plane (first / last cell classes of the table), enumerated
-// densely. One thread: one cell (factor x factor pixels of one backbone token) x 8 channels; a
-// warp holds 8 consecutive ring cells x 4 consecutive channel vectors (32 channels). The ring is
-// 6 % of the cells of a 64 x 64 plane: its table entries are read from global memory (L2) and a
-// block takes only 64 cells, so that the few cells still spread over every SM.
+// The four corner cells of every plane (each has its own f x f block of table classes). One
+// thread: one cell (factor x factor pixels of one backbone token) x 8 channels, table entries
+// read from global memory (L2).
 constexpr int COND_CELLS_PER_ITEM = 256;   // interior kernel: cells a block walks per slab load
 constexpr int COND_BORDER_CELLS_PER_ITEM = 64;
 
@@ -370,7 +368,7 @@ adaln_cond_border_kernel(const AdalnCondParams p, const float* __restrict__ tabl
   const int H = p.h * f, W = p.w * f;
   const long long gR0 = p.row0 / W / f;
   const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
-  const long long ring = 2LL * p.w + 2LL * (p.h - 2);        // border cells of one plane
+  const long long ring = 4;                                  // the corner cells of one plane
   const long long plane0 = gR0 / p.h;
   const long long n_cells = (gR1 / p.h - plane0 + 1) * ring;
   const long long n_chunks = (n_cells + COND_BORDER_CELLS_PER_ITEM - 1) / COND_BORDER_CELLS_PER_ITEM;
@@ -383,11 +381,8 @@ adaln_cond_border_kernel(const AdalnCondParams p, const float* __restrict__ tabl
     if (cell >= n_cells) continue;
     const int cv = cvg * 4 + (lane & 3);
     const long long plane = plane0 + cell / ring;
-    long long k = cell % ring;
-    int R, Cc;
-    if (k < p.w) { R = 0; Cc = static_cast<int>(k); }
-    else if (k < 2LL * p.w) { R = p.h - 1; Cc = static_cast<int>(k - p.w); }
-    else { k -= 2LL * p.w; R = 1 + static_cast<int>(k >> 1); Cc = (k & 1) ? p.w - 1 : 0; }
+    const int k = static_cast<int>(cell % ring);
+    const int R = (k & 2) ? p.h - 1 : 0, Cc = (k & 1) ? p.w - 1 : 0;
     const int rb = R == 0 ? 0 : (R == p.h - 1 ? p.h - 3 : R - 1);
     const int cb = Cc == 0 ? 0 : (Cc == p.w - 1 ? p.w - 3 : Cc - 1);
     const int ycls0 = R == 0 ? 0 : (R == p.h - 1 ? 2 * f : f);
@@ -420,7 +415,7 @@ adaln_cond_border_kernel(const AdalnCondParams p, const float* __restrict__ tabl
 // instruction issue in about equal parts. A warp holds 4 cell pairs x 8 channel quads (32
 // channels): a token read and a row write are still 64 contiguous bytes per cell.
 __global__ void __launch_bounds__(256, 2)
-adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ table) {
+adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ table, int group0) {
   extern __shared__ __align__(16) float slab[];
   const int ncvg = p.Cb >> 5;
   const int f = p.factor;
@@ -428,7 +423,16 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
   const int H = p.h * f, W = p.w * f;
   const long long gR0 = p.row0 / W / f;
   const long long gR1 = (p.row0 + p.n_rows - 1) / W / f;
-  const long long n_cells = (gR1 - gR0 + 1) * p.w;
+  // blockIdx.y: which set of cells sharing one f x f block of table classes - 0: the interior,
+  // 1 / 2: first / last cell row without its corners, 3 / 4: first / last cell column without
+  // its corners (the four corner cells of a plane are left to the border kernel)
+  const int group = group0 + static_cast<int>(blockIdx.y);
+  const long long plane0 = gR0 / p.h;
+  const long long planes = gR1 / p.h - plane0 + 1;
+  const int per_plane = group == 0 ? 0 : (group <= 2 ? p.w - 2 : p.h - 2);
+  const long long n_cells = group == 0 ? (gR1 - gR0 + 1) * p.w : planes * per_plane;
+  const int ycls0 = group == 1 ? 0 : (group == 2 ? 2 * f : f);
+  const int xcls0 = group == 3 ? 0 : (group == 4 ? 2 * f : f);
   const long long n_chunks = (n_cells + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM;
   const long long n_items = n_chunks * ncvg;
   const int lane = threadIdx.x & 31;
@@ -442,7 +446,7 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
     for (int v = threadIdx.x; v < slab_vec; v += blockDim.x) {
       const int e = v >> 3;                                // (phase, k)
       const int phase = e / 9, k = e - phase * 9;
-      const int cls = (f + phase / f) * ncls + (f + phase % f);
+      const int cls = (ycls0 + phase / f) * ncls + (xcls0 + phase % f);
       reinterpret_cast<float4*>(slab)[v] = __ldg(
           reinterpret_cast<const float4*>(table + (static_cast<long long>(cls) * 9 + k) * p.Cb +
                                           cvg * 32) + (v & 7));
@@ -458,16 +462,28 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
       for (int s2 = 0; s2 < 2; ++s2) {
         const long long cell = cell0 + pass * 64 + warp * 8 + 2 * (lane >> 3) + s2;
         if (cell >= n_cells) continue;
-        const long long gR = gR0 + cell / p.w;
-        const int Cc = static_cast<int>(cell % p.w);
-        const long long plane = gR / p.h;
-        const int R = static_cast<int>(gR % p.h);
-        if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
+        long long plane;
+        int R, Cc;
+        if (group == 0) {
+          const long long gR = gR0 + cell / p.w;
+          Cc = static_cast<int>(cell % p.w);
+          plane = gR / p.h;
+          R = static_cast<int>(gR % p.h);
+          if (R < 1 || R > p.h - 2 || Cc < 1 || Cc > p.w - 2) continue;
+        } else {
+          plane = plane0 + cell / per_plane;
+          const int j = 1 + static_cast<int>(cell % per_plane);
+          R = group == 1 ? 0 : (group == 2 ? p.h - 1 : j);
+          Cc = group == 3 ? 0 : (group == 4 ? p.w - 1 : j);
+        }
+        // the 3 x 3 token block starts one cell before the cell, clamped into the plane
+        const int rb = R == 0 ? 0 : (R == p.h - 1 ? p.h - 3 : R - 1);
+        const int cb = Cc == 0 ? 0 : (Cc == p.w - 1 ? p.w - 3 : Cc - 1);
         const __nv_bfloat16* base = p.tok + plane * p.h * p.w * p.Cb + ch0;
 #pragma unroll
         for (int k = 0; k < 9; ++k) {
           const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(
-              base + (static_cast<long long>(R - 1 + k / 3) * p.w + (Cc - 1 + k % 3)) * p.Cb));
+              base + (static_cast<long long>(rb + k / 3) * p.w + (cb + k % 3)) * p.Cb));
           if (s2 == 0) {
             ta[k][0] = bf16_lo(t2.x); ta[k][1] = bf16_hi(t2.x); ta[k][2] = bf16_lo(t2.y); ta[k][3] = bf16_hi(t2.y);
           } else {
@@ -557,12 +573,16 @@ inline int launch_adaln_cond(const AdalnCondParams& p, float* table, int sm_coun
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, slab_bytes);
       if (ea != cudaSuccess) return -static_cast<int>(ea) - 1000;
     }
-    adaln_cond_interior_kernel<<<static_cast<int>(blocks), 256, slab_bytes, stream>>>(p, table);
+    adaln_cond_interior_kernel<<<static_cast<int>(blocks), 256, slab_bytes, stream>>>(p, table, 0);
     {
       const long long H = static_cast<long long>(p.h) * p.factor;
       const long long planes = (p.row0 + p.n_rows - 1) / (H * W) - p.row0 / (H * W) + 1;
-      const long long ring = 2LL * p.w + 2LL * (p.h - 2);
-      long long bb = (planes * ring + COND_BORDER_CELLS_PER_ITEM - 1) / COND_BORDER_CELLS_PER_ITEM * (p.Cb / 32);
+      // the first / last cell rows and columns (groups 1-4), then the four corners per plane
+      const long long edge = planes * ((p.w > p.h ? p.w : p.h) - 2);
+      long long be = (edge + COND_CELLS_PER_ITEM - 1) / COND_CELLS_PER_ITEM * (p.Cb / 32);
+      if (be > cap) be = cap;
+      adaln_cond_interior_kernel<<<dim3(static_cast<unsigned>(be), 4), 256, slab_bytes, stream>>>(p, table, 1);
+      long long bb = (planes * 4 + COND_BORDER_CELLS_PER_ITEM - 1) / COND_BORDER_CELLS_PER_ITEM * (p.Cb / 32);
       if (bb > cap) bb = cap;
       adaln_cond_border_kernel<<<static_cast<int>(bb), 256, 0, stream>>>(p, table);
     }
