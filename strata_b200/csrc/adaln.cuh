@@ -456,7 +456,7 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
     float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
     if (p.bdw != nullptr) bias = __ldg(reinterpret_cast<const float4*>(p.bdw + ch0));
     for (int pass = 0; pass < COND_CELLS_PER_ITEM / 64; ++pass) {
-      float ta[9][4], tb[9][4];
+      uint64_t ta[9][2], tb[9][2];   // fp32 pairs (channels 0-1, 2-3): the stencil runs on packed fp32x2
       long long pix_a = -1, pix_b = -1;     // first pixel of each cell; -1: the cell is skipped
 #pragma unroll
       for (int s2 = 0; s2 < 2; ++s2) {
@@ -485,9 +485,9 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
           const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(
               base + (static_cast<long long>(rb + k / 3) * p.w + (cb + k % 3)) * p.Cb));
           if (s2 == 0) {
-            ta[k][0] = bf16_lo(t2.x); ta[k][1] = bf16_hi(t2.x); ta[k][2] = bf16_lo(t2.y); ta[k][3] = bf16_hi(t2.y);
+            ta[k][0] = pack2(bf16_lo(t2.x), bf16_hi(t2.x)); ta[k][1] = pack2(bf16_lo(t2.y), bf16_hi(t2.y));
           } else {
-            tb[k][0] = bf16_lo(t2.x); tb[k][1] = bf16_hi(t2.x); tb[k][2] = bf16_lo(t2.y); tb[k][3] = bf16_hi(t2.y);
+            tb[k][0] = pack2(bf16_lo(t2.x), bf16_hi(t2.x)); tb[k][1] = pack2(bf16_lo(t2.y), bf16_hi(t2.y));
           }
         }
         const long long pix0 = (plane * H + static_cast<long long>(R) * f) * W + static_cast<long long>(Cc) * f;
@@ -496,38 +496,40 @@ adaln_cond_interior_kernel(const AdalnCondParams p, const float* __restrict__ ta
       if (pix_a < 0 && pix_b < 0) continue;
       if (pix_a < 0) {
 #pragma unroll
-        for (int k = 0; k < 9; ++k)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) ta[k][c] = 0.f;
+        for (int k = 0; k < 9; ++k) ta[k][0] = ta[k][1] = 0ull;
       }
       if (pix_b < 0) {
 #pragma unroll
-        for (int k = 0; k < 9; ++k)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tb[k][c] = 0.f;
+        for (int k = 0; k < 9; ++k) tb[k][0] = tb[k][1] = 0ull;
       }
       for (int phy = 0; phy < f; ++phy) {
         for (int phx = 0; phx < f; ++phx) {
           const float4* wv = reinterpret_cast<const float4*>(slab) + (phy * f + phx) * 72 + cq;
-          float a[4] = {bias.x, bias.y, bias.z, bias.w};
-          float b[4] = {bias.x, bias.y, bias.z, bias.w};
+          uint64_t a[2] = {pack2(bias.x, bias.y), pack2(bias.z, bias.w)};
+          uint64_t b[2] = {a[0], a[1]};
 #pragma unroll
           for (int k = 0; k < 9; ++k) {
             const float4 w4 = wv[k * 8];
-            a[0] = fmaf(w4.x, ta[k][0], a[0]); a[1] = fmaf(w4.y, ta[k][1], a[1]);
-            a[2] = fmaf(w4.z, ta[k][2], a[2]); a[3] = fmaf(w4.w, ta[k][3], a[3]);
-            b[0] = fmaf(w4.x, tb[k][0], b[0]); b[1] = fmaf(w4.y, tb[k][1], b[1]);
-            b[2] = fmaf(w4.z, tb[k][2], b[2]); b[3] = fmaf(w4.w, tb[k][3], b[3]);
+            const uint64_t w01 = pack2(w4.x, w4.y), w23 = pack2(w4.z, w4.w);
+            a[0] = ffma2(w01, ta[k][0], a[0]); a[1] = ffma2(w23, ta[k][1], a[1]);
+            b[0] = ffma2(w01, tb[k][0], b[0]); b[1] = ffma2(w23, tb[k][1], b[1]);
           }
           const long long off = static_cast<long long>(phy) * W + phx;
-          auto finish = [&](float (&v)[4], long long pix0) {
+          auto finish = [&](const uint64_t (&v2)[2], long long pix0) {
             const long long pix = pix0 + off;
             if (pix0 < 0 || pix < p.row0 || pix >= p.row0 + p.n_rows) return;
+            // tanh GELU, the polynomial part on packed fp32x2
+            const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+            const uint64_t K0 = pack2(k0, k0), K01 = pack2(k01, k01), HALF = pack2(0.5f, 0.5f);
+            float v[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const float x = v[c];
-              const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-              v[c] = 0.5f * x * (1.0f + fast_tanh(u));
+            for (int j = 0; j < 2; ++j) {
+              const uint64_t x = v2[j];
+              const uint64_t u = fmul2(x, ffma2(fmul2(x, x), K01, K0));
+              float u0, u1;
+              unpack2(u, u0, u1);
+              const uint64_t hx = fmul2(x, HALF);
+              unpack2(ffma2(hx, pack2(fast_tanh(u0), fast_tanh(u1)), hx), v[2 * j], v[2 * j + 1]);
             }
             uint2 o;
             o.x = pack_bf16(v[0], v[1]);
