@@ -608,6 +608,14 @@ def build_distributed_tile_halo_plan(grid_src: dict, num_elements: int, tile_siz
 
     face_xyz = _unit_f32(lon_faces, lat_faces).reshape(6, N * N, 3)
     face_trees = [spatial.KDTree(face_xyz[f]) for f in range(6)]
+    # One tree over all six faces finds the nearest face of a halo cell in a single query (a
+    # nearest-neighbour query against a face on the far side of the sphere walks most of that
+    # face's tree, and the reference's six queries per cell are what makes its plan slow). The
+    # reference's rule - lowest face among those at the minimum distance - is kept by looking at
+    # every neighbour at exactly that distance; the cell inside the face then comes from the
+    # face's own tree, as in the reference.
+    globe_tree = spatial.cKDTree(face_xyz.reshape(6 * N * N, 3))
+    k_face = min(8, 6 * N * N)
     tile_trees: dict = {}
 
     def tree_of_tile(g: int):
@@ -634,15 +642,15 @@ def build_distributed_tile_halo_plan(grid_src: dict, num_elements: int, tile_siz
         hl_lon = padded_lon[f, ti * T:ti * T + S, tj * T:tj * T + S].reshape(-1)[pos].astype(np.float32)
         hl_lat = padded_lat[f, ti * T:ti * T + S, tj * T:tj * T + S].reshape(-1)[pos].astype(np.float32)
         q32 = _unit_f32(hl_lon, hl_lat)
-        best_face = np.zeros(n_halo, np.int64)
-        best_dist = np.full(n_halo, np.inf)
-        nearest = np.zeros((6, n_halo), np.int64)
-        for face_id, tree in enumerate(face_trees):
-            d, nearest[face_id] = tree.query(q32, k=1)
-            closer = d < best_dist
-            best_dist[closer] = d[closer]
-            best_face[closer] = face_id
-        cell = nearest[best_face, np.arange(n_halo)]
+        gd, gi = globe_tree.query(q32, k=k_face)
+        if k_face == 1:
+            gd, gi = gd[:, None], gi[:, None]
+        cand = np.where(gd == gd[:, :1], gi // (N * N), 6)       # faces of the neighbours at the minimum
+        best_face = cand.min(axis=1).astype(np.int64)
+        cell = np.zeros(n_halo, np.int64)
+        for face_id in np.unique(best_face):
+            m = best_face == face_id
+            cell[m] = np.asarray(face_trees[face_id].query(q32[m], k=1)[1]).reshape(-1)
         src = best_face * tpd * tpd + (cell // N // T) * tpd + (cell % N) // T
         src_tile_id[g] = src
         q64 = _unit_f64(hl_lon, hl_lat)
