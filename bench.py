@@ -44,7 +44,7 @@ def flops_per_token(C, kernel, ratio=4.0):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/ (same workload, one launch each).
-NCU_TRAFFIC_BYTES = {"na3d_fwd": 1.292e9, "gemm_fc1_gelu": 1.288e9, "gemm_qkv_rope": 1.022e9}
+NCU_TRAFFIC_BYTES = {"na3d_fwd": 1.199e9, "gemm_fc1_gelu": 1.288e9, "gemm_qkv_rope": 1.022e9}
 
 
 def measured_peaks():
