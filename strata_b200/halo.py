@@ -339,7 +339,7 @@ class DistributedTilePlanHaloPadding(DistributedTileKNNHaloPadding):
         topo = TileTopology(plan.world_size, int(rank), plan.face_size, plan.tile_size,
                             plan.halo_width)
         idx, w = plan_gather_lists(plan, int(rank))
-        torch.nn.Module.__init__(self)
+        # (the KNN module's own constructor wants the lists of padded face grids; the plan brings its own)
         DistributedTileCopyHaloPadding.__init__(self, topology=topo, device=device, group=group, **kw)
         dev = self.src_a.device
         self.k = int(idx.shape[1])
