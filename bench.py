@@ -740,8 +740,8 @@ def pixel_stage_bench(torch, dev, iters=3):
             ("modulation GEMM (2^18 pixels)", lambda: ops.linear(cond, wts["w_mod"], wts["b_mod"], out=mod[:n]),
              "tensor", 2.0 * n * Cb * 6 * C),
             ("ln_modulate", lambda: ops.adaln_rows(x, shift=sl(0), scale=sl(1)), "hbm", M * C * 2 * 4),
-            ("qkv GEMM", lambda: ops.linear(xn, wts["w_qkv"], wts["b_qkv"], out=qkv), "hbm", M * C * 2 * 4),
-            ("qk_norm_rows", lambda: ops.qk_norm_rows_(qkv, C), "hbm", M * C * 2 * 4),
+            ("qkv GEMM + q/k norm", lambda: ops.qkv_rope(xn, wts["w_qkv"], wts["b_qkv"], 64, None, None,
+                                                         D * H * W, H * W, qk_norm=True), "hbm", M * C * 2 * 4),
             ("na3d 9x9x9", lambda: ops.na3d(q6[:, :, :, :, 0], q6[:, :, :, :, 1], q6[:, :, :, :, 2],
                                              c["kernel"]), "tensor", 4.0 * M * C * kd * kh * kw),
             ("proj GEMM", lambda: ops.linear(attn, wts["w_proj"], wts["b_proj"], out=y), "hbm", M * C * 2 * 2),

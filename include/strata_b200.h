@@ -67,7 +67,10 @@ int strata_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, c
  * pair p of a head rotates channels 2p, 2p+1); row m of x is token
  * (tile = m / tokens_per_tile, horizontal cell = m % hw). Column layout of qkv:
  * [q heads | k heads | v heads], each head head_dim wide (nn.Linear(C,3C) reshaped
- * [.., 3, heads, head_dim]). Pass rope_cs = NULL for no rotation.
+ * [.., 3, heads, head_dim]). Pass rope_cs = NULL for no rotation (with qk_norm set the norm is
+ * still fused - the epilogue then runs with an internal one-row table of identity rotations -
+ * except below C = 256, where a plain projection followed by strata_qk_norm_rows_bf16's kernel
+ * is faster).
  * Replaces attn.qkv + qk norm + stereographic/axial RoPE + head split of the block
  * (tables: screamcast/strata_wrappers.py:636-642). */
 int strata_qkv_rope_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,

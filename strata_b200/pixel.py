@@ -122,14 +122,12 @@ class StrataPixel3DBlock(nn.Module):
         D, H, W = grid
         sl = (lambda i: mod[:, i * C:(i + 1) * C]) if mod is not None else (lambda i: None)
         xn = ops.adaln_rows(x, shift=sl(0), scale=sl(1))
-        if rope_cs is not None:
-            # rotation (and the q/k norm) in the GEMM epilogue, as in the backbone blocks
+        if rope_cs is not None or self.qk_norm:
+            # rotation and / or the q/k norm in the GEMM epilogue, as in the backbone blocks
             qkv = ops.qkv_rope(xn, c["w_qkv"], c["b_qkv"], C // self.num_heads, None, None,
                                D * H * W, H * W, qk_norm=self.qk_norm, rope_cs=rope_cs)
         else:
             qkv = ops.linear(xn, c["w_qkv"], c["b_qkv"])
-            if self.qk_norm:
-                ops.qk_norm_rows_(qkv, C)
         q6 = qkv.view(n_tiles, D, H, W, 3, self.num_heads, C // self.num_heads)
         attn = ops.na3d(q6[:, :, :, :, 0], q6[:, :, :, :, 1], q6[:, :, :, :, 2], self.kernel)
         attn = attn.view(-1, C)
