@@ -504,6 +504,50 @@ class TileHaloPlan:
         return out
 
 
+def tile_halo_plan_from_reference(plan) -> TileHaloPlan:
+    """Dense tables from a plan in the reference's layout - e.g. one that the reference's own
+    `build_distributed_tile_halo_plan` produced with earth2grid's interpolator and saved - so
+    that its exact weights are used. `plan` needs the reference TileHaloPlan's attributes;
+    every `send_plans[src_rank][dst_tile]` entry needs `src_tile`, `dst_halo_positions` [n] and
+    a `regridder_state_dict` with "index" [n, k] (cells of the source tile, row-major) and
+    "weight" (or "weights") [n, k]."""
+    T, h, tpd = int(plan.tile_size), int(plan.halo_width), int(plan.tiles_per_dim)
+    total = 6 * tpd * tpd
+    pos = tile_halo_positions(T, h)
+    where = {int(pp): n for n, pp in enumerate(pos)}
+    src_tile_id = np.full((total, len(pos)), -1, np.int32)
+    knn_index = knn_weight = None
+    for by_dst in plan.send_plans.values():
+        for dst_tile, entries in by_dst.items():
+            g = tile_tuple_to_id(*dst_tile, tpd)
+            for e in entries:
+                sd = e.regridder_state_dict
+                index = np.asarray(sd["index"]).reshape(len(e.dst_halo_positions), -1)
+                weight = np.asarray(sd["weight"] if "weight" in sd else sd["weights"], np.float32
+                                    ).reshape(index.shape)
+                if knn_index is None:
+                    k = index.shape[1]
+                    knn_index = np.zeros((total, len(pos), k), np.int32)
+                    knn_weight = np.zeros((total, len(pos), k), np.float32)
+                rows = np.array([where[int(pp)] for pp in np.asarray(e.dst_halo_positions)], np.int64)
+                if (src_tile_id[g, rows] >= 0).any():
+                    raise ValueError(f"halo positions of tile {dst_tile} listed twice")
+                src_tile_id[g, rows] = tile_tuple_to_id(*e.src_tile, tpd)
+                knn_index[g, rows] = index
+                knn_weight[g, rows] = weight
+    if len(pos) and (knn_index is None or (src_tile_id < 0).any()):
+        raise ValueError("the plan does not cover every halo cell of every tile")
+    if knn_index is None:
+        knn_index = np.zeros((total, 0, 1), np.int32)
+        knn_weight = np.zeros((total, 0, 1), np.float32)
+    return TileHaloPlan(face_size=int(plan.face_size), tile_size=T, tiles_per_dim=tpd, halo_width=h,
+                        ne=int(plan.ne), npg=int(plan.npg), world_size=int(plan.world_size),
+                        tiles_per_rank=int(plan.tiles_per_rank), tile_to_rank=dict(plan.tile_to_rank),
+                        recv_counts=dict(plan.recv_counts), send_sizes=dict(plan.send_sizes),
+                        recv_sizes=dict(plan.recv_sizes), halo_positions=pos, src_tile_id=src_tile_id,
+                        knn_index=knn_index, knn_weight=knn_weight)
+
+
 def tile_id_to_tuple(tile_id: int, tiles_per_dim: int) -> tuple:
     """Linear tile id -> (face, ti, tj) (reference _tile_id_to_tuple, :174-181)."""
     face, rem = divmod(int(tile_id), tiles_per_dim * tiles_per_dim)

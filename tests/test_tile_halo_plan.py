@@ -16,8 +16,8 @@ import torch
 from oracle import halo_oracle as ho
 from strata_b200.rollout import equiangular_cubed_sphere_latlon
 from strata_b200.topology import (TileTopology, build_distributed_tile_halo_plan, build_tile_to_rank_map,
-                                  faces_to_unstructured, plan_gather_lists, tile_halo_positions,
-                                  tile_id_to_tuple, tile_tuple_to_id)
+                                  faces_to_unstructured, plan_gather_lists, tile_halo_plan_from_reference,
+                                  tile_halo_positions, tile_id_to_tuple, tile_tuple_to_id)
 from tests.test_halo_knn import _apply
 
 GOLD = Path(__file__).resolve().parent / "golden" / "tile_halo_plan.npz"
@@ -178,3 +178,28 @@ def test_rank_lists_together_equal_the_single_rank_lists(grid_src, ws):
     parts = [plan_gather_lists(many, r) for r in range(ws)]
     assert np.array_equal(np.concatenate([p[0] for p in parts]), i1)
     assert np.array_equal(np.concatenate([p[1] for p in parts]), w1)
+
+
+@pytest.mark.parametrize("ws", [1, 6])
+def test_plan_in_the_reference_layout_converts_to_the_same_tables(grid_src, ws):
+    # a plan handed over in the reference's nested layout (as the reference would build and save
+    # it, e.g. with earth2grid's own weights) gives the same dense tables
+    import types
+    plan = build_distributed_tile_halo_plan(grid_src, NE, TILE, HALO, num_pg_cells=NPG, world_size=ws)
+    nested = types.SimpleNamespace(**{k: getattr(plan, k) for k in (
+        "face_size", "tile_size", "tiles_per_dim", "halo_width", "ne", "npg", "world_size",
+        "tiles_per_rank", "tile_to_rank", "recv_counts", "send_sizes", "recv_sizes")},
+        send_plans=plan.send_plans)
+    back = tile_halo_plan_from_reference(nested)
+    assert np.array_equal(back.src_tile_id, plan.src_tile_id)
+    assert np.array_equal(back.knn_index, plan.knn_index)
+    assert np.array_equal(back.knn_weight, plan.knn_weight)
+    assert np.array_equal(back.halo_positions, plan.halo_positions)
+    # entries that miss a halo cell, or list one twice, are refused
+    first = next(iter(nested.send_plans[0].values()))
+    first.append(first[0])
+    with pytest.raises(ValueError, match="twice"):
+        tile_halo_plan_from_reference(nested)
+    first.pop(); first.pop(0)
+    with pytest.raises(ValueError, match="cover"):
+        tile_halo_plan_from_reference(nested)
