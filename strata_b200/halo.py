@@ -469,9 +469,23 @@ def kbd_window(padded_size: int, beta: float = 10 * np.pi) -> torch.Tensor:
     w1 = torch.tensor(kaiser_bessel_derived(padded_size, beta), dtype=torch.float32)
     return w1[None, :] * w1[:, None]
 
-def channel_chunked(fn, chunk: int = 32):
-    """Apply a halo module over channel chunks (the reference's rollout driver wraps its halo
-    exchange the same way: scripts/ace/run_screamcast_nudged.py:119-134)."""
-    def wrapped(x: torch.Tensor) -> torch.Tensor:
-        return torch.cat([fn(x[:, c:c + chunk]) for c in range(0, x.shape[1], chunk)], dim=1)
-    return wrapped
+def channel_chunked(fn_or_chunk, chunk: int = 32):
+    """Apply a halo module over chunks of dimension 1 and concatenate the results. Both call
+    forms work: the reference rollout driver's decorator factory, `channel_chunked(32)(halo)`
+    (scripts/ace/run_screamcast_nudged.py:119-134: a chunk <= 0 returns the function itself,
+    the wrapper keeps it as `__wrapped__`), and `channel_chunked(halo, 32)`."""
+    def decorate(fn, channel_chunk):
+        if channel_chunk <= 0:
+            return fn
+
+        def wrapped(x: torch.Tensor) -> torch.Tensor:
+            return torch.cat([fn(x[:, c:c + channel_chunk])
+                              for c in range(0, x.shape[1], channel_chunk)], dim=1)
+
+        wrapped.__wrapped__ = fn
+        return wrapped
+
+    if callable(fn_or_chunk):
+        return decorate(fn_or_chunk, int(chunk))
+    channel_chunk = int(fn_or_chunk)
+    return lambda fn: decorate(fn, channel_chunk)

@@ -75,3 +75,23 @@ def test_transpose_identity_and_round_trips():
 def test_window_shape_is_checked():
     with pytest.raises(ValueError):
         halo_adjoint_lists(TileTopology(1, 0, 8, 4, 1), np.ones((5, 5), np.float32))
+
+
+def test_channel_chunked_accepts_both_call_forms():
+    """`channel_chunked(32)(halo)` is the reference rollout driver's form
+    (scripts/ace/run_screamcast_nudged.py:119-134, 621); `channel_chunked(halo, 32)` the short one."""
+    import torch
+    from strata_b200.halo import channel_chunked
+    calls = []
+
+    def fn(x):
+        calls.append(x.shape[1])
+        return x * 2
+
+    x = torch.arange(2 * 7 * 3, dtype=torch.float32).reshape(2, 7, 3)
+    for wrapped in (channel_chunked(3)(fn), channel_chunked(fn, 3)):
+        calls.clear()
+        assert torch.equal(wrapped(x), x * 2)
+        assert calls == [3, 3, 1]
+        assert wrapped.__wrapped__ is fn
+    assert channel_chunked(0)(fn) is fn and channel_chunked(fn, -1) is fn

@@ -98,6 +98,28 @@ def test_shape_validation():
 
 
 
+def test_halo_modules_under_inference_mode_with_channel_chunks():
+    """The rollout loop pads, runs the network and un-pads under torch.inference_mode(), the halo
+    modules wrapped in channel chunks (scripts/ace/run_screamcast_nudged.py:452-477, 612-639)."""
+    from strata_b200.halo import (DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint,
+                                  channel_chunked, kbd_window)
+    fs, ts, hw = 16, 8, 2
+    t, to = _topos(fs, ts, hw)
+    x = torch.randn(2, 7, t.tiles_per_rank, ts, ts, generator=torch.Generator().manual_seed(5)).cuda()
+    mod = DistributedTileCopyHaloPadding(topology=t)
+    unpad = NormalizedCopyHaloAdjoint(mod, window=kbd_window(t.padded_tile_size))
+    want_pad = mod(x)
+    want_unpad = unpad(want_pad)
+    with torch.inference_mode():
+        got_pad = channel_chunked(3)(mod)(x)
+        got_unpad = channel_chunked(3)(unpad)(got_pad)
+        sliced = channel_chunked(mod, 2)(x[:, 1:6])            # a non-contiguous channel slice
+    mod.check_status()
+    assert torch.equal(got_pad, want_pad) and torch.equal(got_unpad, want_unpad)
+    assert torch.equal(sliced, want_pad[:, 1:6])
+    assert np.array_equal(want_pad.cpu().numpy(), ho.padded_local_tiles(x.cpu().numpy(), to))
+
+
 @pytest.mark.parametrize("window", ["ones", "kbd"])
 def test_halo_adjoint_bit_exact(window):
     from strata_b200.halo import DistributedTileCopyHaloPadding, NormalizedCopyHaloAdjoint, kbd_window
