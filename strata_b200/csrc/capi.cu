@@ -562,7 +562,7 @@ int strata_halo_gather_kv_bf16(void* qkv, const void* const* h_peer_qkv, int wor
   if (cells * world > 0x7fffffffLL) return STRATA_ERR_ARG;
   if (static_cast<long long>(tiles_per_rank) * D > 65535) return STRATA_ERR_UNSUPPORTED;
   const long long work = static_cast<long long>(P) * P - static_cast<long long>(T) * T;   // halo cells
-  long long bx = (work + 63) / 64;   // a block walks ~16 groups of four halo cells
+  long long bx = (work + 255) / 256;   // a block's eight warps take 32 halo cells each
   const long long cap = static_cast<long long>(sms) * 8;
   if (bx > cap) bx = cap;
   if (bx < 1) return STRATA_OK;   // no halo

@@ -257,8 +257,8 @@ halo_adjoint_fields_kernel(float* __restrict__ out, const PeerPtrs src,
 // frame; it is turned into the receiver's frame on the way by the per-cell delta rotation
 // dcs[tile, cell, pair] = (cos, sin)(theta_receiver - theta_sender) (IEEE half pairs), V is
 // copied. Corner-diagonal cells average their two (individually rotated) sources.
-// grid: x over groups of four halo cells (64 threads per cell), y over (tile, depth).
-__global__ void __launch_bounds__(256)
+// grid: x over groups of 256 halo cells (a warp takes 32 consecutive ones), y over (tile, depth).
+__global__ void __launch_bounds__(256, 3)
 halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
                       const int* __restrict__ src_a, const int* __restrict__ src_b,
                       const uint32_t* __restrict__ dcs_a, const uint32_t* __restrict__ dcs_b,
@@ -274,98 +274,116 @@ halo_gather_kv_kernel(__nv_bfloat16* __restrict__ qkv, const PeerPtrs src,
   // interior (2*halo rows of P cells), then the 2*halo side columns of the T interior rows
   const int n_strip = 2 * halo * P;
   const int n_halo = n_strip + 2 * halo * T;
-  // 64 threads share a halo cell: its decoding and the source rows are worked out once per
-  // cell, each thread then moves every 64th 16-byte vector of the cell's k|v channels
-  const int sub = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
+  // A warp takes 32 consecutive halo cells. Lane l works out cell l's position and source rows
+  // (a dozen integer divisions: done once per cell by one lane, all 32 cells side by side), then
+  // the whole warp moves the cells one after the other, every lane a 16-byte vector at a time,
+  // with the cell's addresses handed round by shuffles.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
   const bool failed = halo_exchange_failed();   // (read once: a volatile load per store halves the copy rate)
-  const int cells_per_iter = blockDim.x >> 6;
-  for (int hc = blockIdx.x * cells_per_iter + sub; hc < n_halo; hc += gridDim.x * cells_per_iter) {
-    int pi, pj;
-    if (hc < n_strip) {
-      const int row = hc / P;
-      pj = hc - row * P;
-      pi = row < halo ? row : row + T;
-    } else {
-      const int e = hc - n_strip;
-      const int row = e / (2 * halo);
-      const int col = e - row * 2 * halo;
-      pi = halo + row;
-      pj = col < halo ? col : col + T;
-    }
-    const int pc = pi * P + pj;
-    const int a = __ldg(src_a + tile * PP + pc);
-    const int b = __ldg(src_b + tile * PP + pc);
-    auto source_row = [&](int id) -> const __nv_bfloat16* {
-      const int rank = id / cells_per_rank;
-      const int local = id - rank * cells_per_rank;
-      const int st = local / TT;
-      const int sc = local - st * TT;
-      const int si = sc / T, sj = sc - si * T;
-      const long long row = ((static_cast<long long>(st) * D + d) * P + si + halo) * P + sj + halo;
-      return static_cast<const __nv_bfloat16*>(src.p[rank]) + row * ld + C;   // k|v start after q
-    };
-    const __nv_bfloat16* row_a = source_row(a);
-    const __nv_bfloat16* row_b = b >= 0 ? source_row(b) : nullptr;
-    const long long tab_row = (static_cast<long long>(tile) * PP + pc) * half;
-    __nv_bfloat16* out_row = qkv + ((static_cast<long long>(tile) * D + d) * PP + pc) * ld + C;
-    // x: eight bf16 of the source row; t4: the four (cos, sin) pairs of a K vector
-    auto rotate = [&](const uint4& x, const uint4& t4, bool is_k, float (&o)[8]) {
-      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-      if (is_k) {
-        const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 cs = __half22float2(*reinterpret_cast<const __half2*>(&tw[t]));
-          const float x0 = bf16_lo(w[t]), x1 = bf16_hi(w[t]);
-          o[2 * t] = x0 * cs.x - x1 * cs.y;
-          o[2 * t + 1] = x0 * cs.y + x1 * cs.x;
-        }
+  for (int base = (blockIdx.x * warps + warp) * 32; base < n_halo; base += gridDim.x * warps * 32) {
+    const int hc = base + lane;
+    const __nv_bfloat16* my_a = nullptr;
+    const __nv_bfloat16* my_b = nullptr;
+    int my_pc = 0;
+    if (hc < n_halo) {
+      int pi, pj;
+      if (hc < n_strip) {
+        const int row = hc / P;
+        pj = hc - row * P;
+        pi = row < halo ? row : row + T;
       } else {
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          o[2 * t] = bf16_lo(w[t]);
-          o[2 * t + 1] = bf16_hi(w[t]);
-        }
+        const int e = hc - n_strip;
+        const int row = e / (2 * halo);
+        const int col = e - row * 2 * halo;
+        pi = halo + row;
+        pj = col < halo ? col : col + T;
       }
-    };
-    auto table = [&](const uint32_t* tab, int v) {   // first channel pair of vector v: ((8v) % head_dim) / 2
-      return __ldg(reinterpret_cast<const uint4*>(tab + tab_row + (((v << 3) % head_dim) >> 1)));
-    };
-    // four vectors per thread and pass, all loads issued before the first use: the copy is
-    // bound by the bytes a thread keeps in flight
-    constexpr int UNROLL = 4;
-    for (int v0 = lane64; v0 < vpc; v0 += 64 * UNROLL) {
-      uint4 xa[UNROLL], ta[UNROLL];
+      my_pc = pi * P + pj;
+      const int a = __ldg(src_a + tile * PP + my_pc);
+      const int b = __ldg(src_b + tile * PP + my_pc);
+      auto source_row = [&](int id) -> const __nv_bfloat16* {
+        const int rank = id / cells_per_rank;
+        const int local = id - rank * cells_per_rank;
+        const int st = local / TT;
+        const int sc = local - st * TT;
+        const int si = sc / T, sj = sc - si * T;
+        const long long row = ((static_cast<long long>(st) * D + d) * P + si + halo) * P + sj + halo;
+        return static_cast<const __nv_bfloat16*>(src.p[rank]) + row * ld + C;   // k|v start after q
+      };
+      my_a = source_row(a);
+      if (b >= 0) my_b = source_row(b);
+    }
+    const int n_here = min(32, n_halo - base);
+    for (int c = 0; c < n_here; ++c) {
+      const __nv_bfloat16* row_a = reinterpret_cast<const __nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_a), c));
+      const __nv_bfloat16* row_b = reinterpret_cast<const __nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_b), c));
+      const int pc = __shfl_sync(0xffffffffu, my_pc, c);
+      const long long tab_row = (static_cast<long long>(tile) * PP + pc) * half;
+      __nv_bfloat16* out_row = qkv + ((static_cast<long long>(tile) * D + d) * PP + pc) * ld + C;
+      // x: eight bf16 of the source row; t4: the four (cos, sin) pairs of a K vector
+      auto rotate = [&](const uint4& x, const uint4& t4, bool is_k, float (&o)[8]) {
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+        if (is_k) {
+          const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int v = v0 + 64 * u;
-        if (v < vpc) {
-          xa[u] = *reinterpret_cast<const uint4*>(row_a + (v << 3));
-          if (v < kvec) ta[u] = table(dcs_a, v);
+          for (int t = 0; t < 4; ++t) {
+            const float2 cs = __half22float2(*reinterpret_cast<const __half2*>(&tw[t]));
+            const float x0 = bf16_lo(w[t]), x1 = bf16_hi(w[t]);
+            o[2 * t] = x0 * cs.x - x1 * cs.y;
+            o[2 * t + 1] = x0 * cs.y + x1 * cs.x;
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            o[2 * t] = bf16_lo(w[t]);
+            o[2 * t + 1] = bf16_hi(w[t]);
+          }
         }
-      }
+      };
+      auto table = [&](const uint32_t* tab, int v) {   // first channel pair of vector v: ((8v) % head_dim) / 2
+        return __ldg(reinterpret_cast<const uint4*>(tab + tab_row + (((v << 3) % head_dim) >> 1)));
+      };
+      // four vectors per lane and pass, all loads issued before the first use: the copy is
+      // bound by the bytes a thread keeps in flight
+      constexpr int UNROLL = 4;
+      for (int v0 = lane; v0 < vpc; v0 += 32 * UNROLL) {
+        uint4 xa[UNROLL], ta[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int v = v0 + 64 * u;
-        if (v >= vpc) continue;
-        float ra[8];
-        rotate(xa[u], ta[u], v < kvec, ra);
-        if (row_b != nullptr) {   // corner diagonal: the mean of two individually rotated sources
-          float rb[8];
-          const uint4 xb = *reinterpret_cast<const uint4*>(row_b + (v << 3));
-          uint4 tb = make_uint4(0u, 0u, 0u, 0u);
-          if (v < kvec) tb = table(dcs_b, v);
-          rotate(xb, tb, v < kvec, rb);
-#pragma unroll
-          for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < vpc) {
+            xa[u] = *reinterpret_cast<const uint4*>(row_a + (v << 3));
+            if (v < kvec) ta[u] = table(dcs_a, v);
+          }
         }
-        uint4 o4;
-        o4.x = pack_bf16(ra[0], ra[1]);
-        o4.y = pack_bf16(ra[2], ra[3]);
-        o4.z = pack_bf16(ra[4], ra[5]);
-        o4.w = pack_bf16(ra[6], ra[7]);
-        if (failed) o4 = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
-        *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + 32 * u;
+          if (v >= vpc) continue;
+          uint4 o4 = xa[u];   // V of a cell with one source is copied as it is
+          if (v < kvec || row_b != nullptr) {
+            float ra[8];
+            rotate(xa[u], ta[u], v < kvec, ra);
+            if (row_b != nullptr) {   // corner diagonal: the mean of two individually rotated sources
+              float rb[8];
+              const uint4 xb = *reinterpret_cast<const uint4*>(row_b + (v << 3));
+              uint4 tb = make_uint4(0u, 0u, 0u, 0u);
+              if (v < kvec) tb = table(dcs_b, v);
+              rotate(xb, tb, v < kvec, rb);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) ra[t] = (ra[t] + rb[t]) * 0.5f;
+            }
+            o4.x = pack_bf16(ra[0], ra[1]);
+            o4.y = pack_bf16(ra[2], ra[3]);
+            o4.z = pack_bf16(ra[4], ra[5]);
+            o4.w = pack_bf16(ra[6], ra[7]);
+          }
+          if (failed) o4 = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
+          *reinterpret_cast<uint4*>(out_row + (v << 3)) = o4;
+        }
       }
     }
   }
