@@ -417,8 +417,8 @@ int strata_halo_gather_tokens_bf16(void* out, const void* const* h_peer_src, int
   const int P = T + 2 * halo;
   const long long cells = static_cast<long long>(tiles_per_rank) * T * T;
   if (cells * world > 0x7fffffffLL) return STRATA_ERR_ARG;
-  const long long work = static_cast<long long>(P) * P * (C / 8);
-  long long bx = (work + 255) / 256;
+  const long long work = static_cast<long long>(P) * P;   // padded cells of one (tile, depth) slice
+  long long bx = (work + 255) / 256;                      // a block's eight warps take 32 cells each
   const long long cap = static_cast<long long>(sms) * 8;
   if (bx > cap) bx = cap;
   dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(tiles_per_rank * D));

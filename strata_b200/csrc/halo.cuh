@@ -43,7 +43,10 @@ __device__ __forceinline__ bool halo_exchange_failed() {
 constexpr uint32_t BF16_NAN2 = 0x7fc07fc0u;
 
 // Token layout: source buffers [tiles_per_rank, D, T*T, C] bf16, output [tiles_per_rank, D, P*P, C].
-// grid: x over (padded cell, 16-byte vector) pairs, y over (tile, depth).
+// grid: x over groups of 256 padded cells (a warp takes 32 consecutive ones: lane l works out
+// cell l's source rows - the integer divisions happen once per cell, 32 cells side by side -
+// then the warp moves the cells one after the other, a 16-byte vector per lane at a time),
+// y over (tile, depth).
 __global__ void __launch_bounds__(256)
 halo_gather_tokens_kernel(__nv_bfloat16* __restrict__ out, const PeerPtrs src,
                           const int* __restrict__ src_a, const int* __restrict__ src_b, int PP,
@@ -53,42 +56,70 @@ halo_gather_tokens_kernel(__nv_bfloat16* __restrict__ out, const PeerPtrs src,
   const int tile = blockIdx.y / D;
   const int d = blockIdx.y - tile * D;
   const bool failed = halo_exchange_failed();
-  const long long total = static_cast<long long>(PP) * vpc;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int pc = static_cast<int>(idx / vpc);
-    const int v = static_cast<int>(idx - static_cast<long long>(pc) * vpc);
-    if (only_halo) {
-      const int pi = pc / P, pj = pc - pi * P;
-      if (pi >= halo_lo && pi < halo_hi && pj >= halo_lo && pj < halo_hi) continue;
-    }
-    const int a = __ldg(src_a + tile * PP + pc);
-    const int b = __ldg(src_b + tile * PP + pc);
-    auto load = [&](int id) {
-      const int rank = id / cells_per_rank;
-      const int local = id - rank * cells_per_rank;
-      const int st = local / TT;
-      const int sc = local - st * TT;
-      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(src.p[rank]);
-      const long long off = ((static_cast<long long>(st) * D + d) * TT + sc) * C + (v << 3);
-      return *reinterpret_cast<const uint4*>(base + off);
-    };
-    uint4 r = load(a);
-    if (b >= 0) {
-      const uint4 s = load(b);
-      uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
-      const uint32_t* sw = reinterpret_cast<const uint32_t*>(&s);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        // sum rounded to bf16 first, then halved (exact)
-        const float lo = __bfloat162float(__float2bfloat16(bf16_lo(rw[t]) + bf16_lo(sw[t]))) * 0.5f;
-        const float hi = __bfloat162float(__float2bfloat16(bf16_hi(rw[t]) + bf16_hi(sw[t]))) * 0.5f;
-        rw[t] = pack_bf16(lo, hi);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  for (int base = (blockIdx.x * warps + warp) * 32; base < PP; base += gridDim.x * warps * 32) {
+    const int pc_l = base + lane;
+    const __nv_bfloat16* my_a = nullptr;   // nullptr: nothing to do for this cell
+    const __nv_bfloat16* my_b = nullptr;
+    if (pc_l < PP) {
+      bool skip = false;
+      if (only_halo) {
+        const int pi = pc_l / P, pj = pc_l - pi * P;
+        skip = pi >= halo_lo && pi < halo_hi && pj >= halo_lo && pj < halo_hi;
+      }
+      if (!skip) {
+        auto source_row = [&](int id) -> const __nv_bfloat16* {
+          const int rank = id / cells_per_rank;
+          const int local = id - rank * cells_per_rank;
+          const int st = local / TT;
+          const int sc = local - st * TT;
+          return static_cast<const __nv_bfloat16*>(src.p[rank]) +
+                 ((static_cast<long long>(st) * D + d) * TT + sc) * C;
+        };
+        my_a = source_row(__ldg(src_a + tile * PP + pc_l));
+        const int b = __ldg(src_b + tile * PP + pc_l);
+        if (b >= 0) my_b = source_row(b);
       }
     }
-    if (failed) r = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
-    const long long ooff = ((static_cast<long long>(tile) * D + d) * PP + pc) * C + (v << 3);
-    *reinterpret_cast<uint4*>(out + ooff) = r;
+    const int n_here = min(32, PP - base);
+    for (int c = 0; c < n_here; ++c) {
+      const __nv_bfloat16* row_a = reinterpret_cast<const __nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_a), c));
+      const __nv_bfloat16* row_b = reinterpret_cast<const __nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_b), c));
+      if (row_a == nullptr) continue;
+      __nv_bfloat16* out_row = out + ((static_cast<long long>(tile) * D + d) * PP + base + c) * C;
+      constexpr int UNROLL = 4;
+      for (int v0 = lane; v0 < vpc; v0 += 32 * UNROLL) {
+        uint4 x[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < vpc) x[u] = *reinterpret_cast<const uint4*>(row_a + (v << 3));
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + 32 * u;
+          if (v >= vpc) continue;
+          uint4 r = x[u];
+          if (row_b != nullptr) {
+            const uint4 s2 = *reinterpret_cast<const uint4*>(row_b + (v << 3));
+            uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+            const uint32_t* sw = reinterpret_cast<const uint32_t*>(&s2);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              // sum rounded to bf16 first, then halved (exact)
+              const float lo = __bfloat162float(__float2bfloat16(bf16_lo(rw[t]) + bf16_lo(sw[t]))) * 0.5f;
+              const float hi = __bfloat162float(__float2bfloat16(bf16_hi(rw[t]) + bf16_hi(sw[t]))) * 0.5f;
+              rw[t] = pack_bf16(lo, hi);
+            }
+          }
+          if (failed) r = make_uint4(BF16_NAN2, BF16_NAN2, BF16_NAN2, BF16_NAN2);
+          *reinterpret_cast<uint4*>(out_row + (v << 3)) = r;
+        }
+      }
+    }
   }
 }
 
