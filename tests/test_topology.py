@@ -110,3 +110,23 @@ def test_element_order_to_face_rasters(golden_dir):
         tp.unstructured_to_6faces(u[:, :-1], ne=3, npg=2)
     with pytest.raises(ValueError, match="Expected last 3 dims"):
         tp.faces_to_unstructured(faces[:, :5], ne=3, npg=2)
+
+
+def test_reference_module_names_resolve_to_this_package():
+    """`screamcast.distributed_halo`, `.distributed_cubesphere_transforms` and
+    `.cubesphere_transforms` each have a module of the same name here that carries the same
+    public names (a caller switches by changing the import line)."""
+    from strata_b200 import (cubesphere_transforms, distributed_cubesphere_transforms,
+                             distributed_halo, halo, topology)
+    assert distributed_halo.TileTopology is topology.TileTopology
+    assert distributed_halo.DistributedTileKNNHaloPadding_AllGather is halo.DistributedTileKNNHaloPadding
+    assert distributed_halo.NormalizedHaloAdjoint is halo.NormalizedHaloAdjoint
+    assert hasattr(distributed_halo.DistributedTileKNNHaloPadding_AllGather, "from_padded_face_grid")
+    assert distributed_cubesphere_transforms.DistributedTileKNNHaloPadding is halo.DistributedTilePlanHaloPadding
+    assert (distributed_cubesphere_transforms.build_distributed_tile_halo_plan
+            is topology.build_distributed_tile_halo_plan)
+    assert distributed_cubesphere_transforms._tile_id_to_tuple(37, 4) == (2, 1, 1)
+    assert distributed_cubesphere_transforms._tile_tuple_to_id(2, 1, 1, 4) == 37
+    for name in ("reorder_cubesphere_to_2d_tensor", "reorder_2d_tensor_to_cubesphere",
+                 "unstructured_to_6faces", "faces_to_unstructured"):
+        assert getattr(cubesphere_transforms, name) is getattr(topology, name)
