@@ -130,3 +130,18 @@ def test_reference_module_names_resolve_to_this_package():
     for name in ("reorder_cubesphere_to_2d_tensor", "reorder_2d_tensor_to_cubesphere",
                  "unstructured_to_6faces", "faces_to_unstructured"):
         assert getattr(cubesphere_transforms, name) is getattr(topology, name)
+
+
+def test_model_side_reference_module_names_resolve_to_this_package():
+    """`screamcast.strata_wrappers`, `.tile_geometry`, `.wind_rotation`, `.dealias` and
+    `.checkpoint_compat` have namesakes here with the same public names."""
+    from strata_b200 import (checkpoint_compat, dealias, strata, strata_wrappers, tile_geometry,
+                             wind_rotation, wrappers)
+    assert strata_wrappers.StrataBackboneModel is wrappers.StrataBackboneModel
+    assert strata_wrappers.StrataModel is wrappers.StrataModel
+    assert strata_wrappers.remap_legacy_state_dict is checkpoint_compat.remap_legacy_state_dict
+    assert tile_geometry.TileGeometry is wrappers.TileGeometry
+    assert tile_geometry.mean_longitude is wrappers.mean_longitude
+    for name in ("local_basis_ENR", "forward_uv_to_tile", "inverse_tile_to_uv"):
+        assert getattr(wind_rotation, name) is getattr(wrappers, name)
+    assert dealias.DealiasedPatchEmbed3D is strata.DealiasedPatchEmbed3D
